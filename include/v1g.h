@@ -1,0 +1,237 @@
+/*
+ * v1g.h - C ABI of the B200 (sm_100a) implementation of the per-timestep core of the V1 GLIF3
+ * model: event-driven spike -> synaptic-current scatter, double-alpha PSC update, GLIF3
+ * membrane / after-spike-current / refractory / threshold update, and their BPTT gradients.
+ *
+ * The reference (JavierGalvan9/V1_GLIF_model) has no FFI: its operator interface for this path
+ * is a set of Python callables over TensorFlow tensors in v1_model_utils/models.py.  Each entry
+ * point below names the callable (file:line in the reference tree) it stands in for.  Plain
+ * pointers and sizes only.  Unless a parameter says "host", pointers are DEVICE pointers on the
+ * GPU that was current when the handle was created.  Every call returns 0 on success or a
+ * negative V1G_E* code and never aborts; v1g_last_error() gives the message.  A handle is not
+ * thread-safe; use one per GPU.  `stream` is a cudaStream_t passed as void*.
+ *
+ * Tensor layouts at this boundary are the reference's own:
+ *   z_buf[B, D*N]   block d-1 (columns (d-1)*N .. d*N) holds the spikes emitted d steps ago
+ *   psc, psc_rise, rec_inputs [B, N*R]  index n*R + r      asc[B, N*2]  index n*2 + k
+ *   i_flat[B*N, R]  row b*N + n
+ *   weights / weight gradients of a source: dense [nnz] in the order of the `indices` rows given
+ *   to v1g_set_connectivity (the reference's post-major synapse order, load_sparse.py:15-22)
+ */
+#ifndef V1G_H_
+#define V1G_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define V1G_OK 0
+#define V1G_EINVAL (-1)   /* bad argument (the reference raises ValueError, models.py:299-315) */
+#define V1G_ECUDA (-2)    /* a CUDA runtime call failed */
+#define V1G_ENOMEM (-3)   /* device allocation failed */
+#define V1G_ETIMEOUT (-4) /* a bounded device-side wait gave up; results are invalid */
+#define V1G_ESTATE (-5)   /* call order violated (e.g. backward without a saved forward) */
+#define V1G_ERANGE (-6)   /* size beyond a stated maximum */
+
+/* synaptic sources of the cell */
+#define V1G_SRC_REC 0 /* recurrent, delays folded into the presynaptic column (models.py:633-640) */
+#define V1G_SRC_LGN 1 /* LGN input, no delay (models.py:707-738) */
+#define V1G_SRC_BKG 2 /* background Poisson nodes, no delay, scaled by count (models.py:740-773) */
+
+#define V1G_FLAG_HARD_RESET 1   /* models.py:1020-1023 */
+#define V1G_FLAG_PSEUDO_GAUSS 2 /* models.py:36-50, 1106-1107 */
+
+#define V1G_MAX_BATCH 8
+#define V1G_MAX_RECEPTORS 8
+#define V1G_MAX_DELAY 8
+
+typedef struct V1GHandle V1GHandle;
+
+/* Scalars of V1Column.__init__ (models.py:451-476). */
+typedef struct V1GConfig {
+  int32_t n_neurons;   /* N */
+  int32_t n_receptors; /* R = n_syn_basis (models.py:520), <= V1G_MAX_RECEPTORS */
+  int32_t n_syn_types; /* S = rows of synaptic_basis_weights (models.py:620-622), <= 256 */
+  int32_t max_delay;   /* D in steps (models.py:529-539), <= V1G_MAX_DELAY */
+  int32_t n_lgn;
+  int32_t n_bkg;
+  int32_t flags;
+  float dt;
+  float dampening_factor;           /* amplitude of the pseudo-derivative */
+  float recurrent_dampening;        /* models.py:1081 */
+  float voltage_gradient_dampening; /* models.py:1010 */
+  float gauss_std;
+  float pseudo_width; /* support half-width of the triangular pseudo-derivative; reference = 1 */
+  float lr_scale;     /* models.py:1097 */
+} V1GConfig;
+
+/* Cell state, reference layouts and dtypes (models.py:1030-1056).  r is int8. */
+typedef struct V1GState {
+  float* z_buf;    /* [B, D*N] */
+  float* v;        /* [B, N]   */
+  int8_t* r;       /* [B, N]   */
+  float* asc;      /* [B, N*2] */
+  float* psc_rise; /* [B, N*R] */
+  float* psc;      /* [B, N*R] */
+} V1GState;
+
+/* In-kernel loss specification of the training rollout (BASELINE configurations 2 and 4).
+ *   rate     : rate_cost * mean_n (mean_{b,t} z[b,t,n] - target[n])^2, target in spikes/step
+ *   voltage  : voltage_cost * mean_{b,t,n} (relu(v-1)^2 + relu(v_lo[n]-v)^2)
+ *   synchrony: sync_cost * (mean_b Fano_b - fano_target)^2, Fano_b = var/mean over bins of the
+ *              population spike count in bins of sync_bin steps (loss_functions.py:964-981)
+ * All costs are multiplied by loss_scale (1/replicas, multi_training.py:427-429). */
+typedef struct V1GLossSpec {
+  const float* rate_target; /* [N] device, may be NULL when rate_cost == 0 */
+  const float* v_lo;        /* [N] device, lower voltage bound in scaled units */
+  float rate_cost;
+  float voltage_cost;
+  float sync_cost;
+  float fano_target;
+  int32_t sync_bin;
+  float loss_scale;
+} V1GLossSpec;
+
+/* Event counters of the last rollout (for the roofline's algorithmic bytes). */
+typedef struct V1GCounters {
+  unsigned long long spikes;     /* V1 spikes emitted */
+  unsigned long long rec_rows;   /* active recurrent source rows walked (spike x delay buckets) */
+  unsigned long long rec_events; /* recurrent synapse events delivered */
+  unsigned long long lgn_rows;
+  unsigned long long lgn_events;
+  unsigned long long bkg_rows;
+  unsigned long long bkg_events;
+  unsigned long long bwd_rows;   /* rows walked by the backward spike-gradient gather */
+  unsigned long long bwd_events; /* synapses visited by it */
+  unsigned long long dw_events;  /* weight-gradient synapse events */
+} V1GCounters;
+
+/* ---- life cycle ------------------------------------------------------------------------ */
+
+/* V1Column.__init__ scalars (models.py:451-541). */
+int v1g_create(const V1GConfig* cfg, V1GHandle** out);
+int v1g_destroy(V1GHandle* h);
+const char* v1g_last_error(const V1GHandle* h);
+/* Library build tag, usable without a GPU. */
+const char* v1g_version(void);
+
+/* Connectivity of one source.  indices_host[nnz,2] = (post, pre) int64 on the HOST exactly as
+ * V1Column stores them (recurrent: pre already holds pre + N*(delay_steps-1), models.py:633-639),
+ * syn_ids_host[nnz] on the host.  n_source_cols = D*N (REC), n_lgn, n_bkg.  Builds the
+ * presynaptic CSR of make_pre_ind_table (models.py:299-373; same stable order inside a row) and
+ * the post-major gather table.  Out-of-range indices -> V1G_EINVAL (models.py:308-314). */
+int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz, const int64_t* indices_host,
+                         const uint8_t* syn_ids_host, int64_t n_source_cols);
+
+/* make_pre_ind_table + _validate_inputs (models.py:299-373) on the host, no GPU needed:
+ * order[nnz] lists positions of indices_host[nnz,2] grouped by presynaptic column (column 1),
+ * original order kept inside a group; row_splits[n_source_cols+1].  V1G_EINVAL for
+ * n_source_cols <= 0 or an out-of-range presynaptic index (the reference raises ValueError). */
+int v1g_build_pre_ind_table(int64_t nnz, const int64_t* indices_host, int64_t n_source_cols,
+                            int64_t* order_host, int64_t* row_splits_host);
+
+/* Read back the presynaptic table: order[nnz] (positions into the caller's synapse arrays) and
+ * row_splits[n_source_cols+1], both HOST int64, numbered exactly like the RaggedTensor of
+ * make_pre_ind_table (models.py:343-373). */
+int v1g_get_pre_ind_table(V1GHandle* h, int source, int64_t* order_host, int64_t* row_splits_host);
+
+/* Per-neuron constants precomputed by V1Column.__init__ (models.py:482-526, 574-611); HOST
+ * pointers.  decay[N], current_factor[N], asc_decay[N*2], asc_amps[N*2], t_ref_steps[N] int32,
+ * syn_decay[R], psc_initial[R], basis[S*R].  Kernels never recompute an exponential. */
+int v1g_set_neuron_params(V1GHandle* h, const float* decay, const float* current_factor,
+                          const float* asc_decay, const float* asc_amps,
+                          const int32_t* t_ref_steps, const float* syn_decay,
+                          const float* psc_initial, const float* basis);
+
+/* Weights of a source in the caller's synapse order; device pointer.  Stands in for the
+ * variable read in calculate_synaptic_currents and refresh_recurrent_weight_shadow
+ * (models.py:663-682, 966-976). */
+int v1g_set_weights(V1GHandle* h, int source, const float* w, void* stream);
+
+/* ---- operator level (one TensorFlow-level callable each) ---------------------------------- */
+
+/* tf.where(x > 0) (models.py:128, 826, 890): row-major coordinates of the positive entries of
+ * x[n_rows, n_cols] (float32) as int64 pairs coords[cap,2]; *count gets the number found (device
+ * int32).  Entries beyond cap are dropped, count still reports the true number. */
+int v1g_compact_spikes(V1GHandle* h, const float* x, int32_t n_rows, int64_t n_cols,
+                       int64_t* coords, int64_t cap, int32_t* count, void* stream);
+
+/* calculate_synaptic_currents forward (models.py:103-169), calculate_input_current_from_spikes
+ * (models.py:814-863) and calculate_noise_current with given counts (models.py:890-940).
+ * x[B, n_source_cols] float32: spikes (REC, LGN) or Poisson counts as floats (BKG).
+ * i_flat[B*N, R] is overwritten. */
+int v1g_syn_currents_fwd(V1GHandle* h, int source, const float* x, int32_t batch, float* i_flat,
+                         void* stream);
+
+/* Gradient of the above (models.py:174-261): dy[B*N,R] -> d_x[B, n_source_cols] (nullable;
+ * dense over ALL synapses, no dampening applied) and d_w[nnz] in the caller's synapse order
+ * (nullable; event-driven, overwritten). */
+int v1g_syn_currents_bwd(V1GHandle* h, int source, const float* x, const float* dy, int32_t batch,
+                         float* d_x, float* d_w, void* stream);
+
+/* One dense update + spike + refractory gating + buffer shift: update_psc, _dense_update_impl,
+ * spike_function and the tail of V1Column.call (models.py:979-1028, 1099-1117).
+ * rec_inputs[B, N*R] already holds (i_rec + i_lgn + i_bkg) * lr_scale.  `in` and `out` must not
+ * alias.  z_out[B,N] float32 0/1 (nullable). */
+int v1g_step_fwd(V1GHandle* h, int32_t batch, const V1GState* in, const float* rec_inputs,
+                 V1GState* out, float* z_out, void* stream);
+
+/* Adjoint of v1g_step_fwd.  g_out holds dL/d(new state) (r ignored), g_z / g_v_out the
+ * gradients of the two outputs (nullable), new_v / new_r the forward results.  Writes
+ * dL/d(old state) to g_in and dL/d rec_inputs to g_rec_inputs.  Stop-gradients and
+ * straight-through factors as in models.py:994, 1010-1018, 58-64. */
+int v1g_step_bwd(V1GHandle* h, int32_t batch, const V1GState* g_out, const float* g_z,
+                 const float* g_v_out, const float* new_v, const int8_t* new_r, V1GState* g_in,
+                 float* g_rec_inputs, void* stream);
+
+/* ---- fused rollout (the Keras RNN loop over V1Column.call, models.py:1317-1322) ----------- */
+
+/* T steps from `state` (updated in place; NULL pointers inside mean zero state and nothing is
+ * written back).  x[B,T,n_lgn] uint8 LGN spikes, bkg_counts[B,T,n_bkg] int32 Poisson counts.
+ * z_out[B,T,N] uint8 and v_out[B,T,N] float32 are optional.  save_for_bwd != 0 keeps v and the
+ * spike/refractory bits of every step inside the handle for v1g_rollout_bwd. */
+int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x,
+                    const int32_t* bkg_counts, V1GState* state, uint8_t* z_out, float* v_out,
+                    int32_t save_for_bwd, void* stream);
+
+/* Same through HOST buffers: copies x and bkg_counts to the device, runs the rollout from the
+ * zero state, copies z_out (uint8, nullable) and v_out (nullable) back.  The end-to-end form a
+ * forward-only evaluation (osi_dsi_estimator.py:280-305) uses. */
+int v1g_rollout_fwd_host(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x_host,
+                         const int32_t* bkg_counts_host, uint8_t* z_out_host, float* v_out_host,
+                         int32_t save_for_bwd, void* stream);
+
+/* BPTT over the saved rollout (tape.gradient in multi_training.py:493).  The loss is the
+ * in-kernel specification plus optional explicit gradients g_z[B,T,N], g_v[B,T,N] (nullable).
+ * Weight gradients are ACCUMULATED into d_w_* (caller zeroes them), each in its source's synapse
+ * order; any may be NULL.  loss_out[4] (device, nullable) = total, rate, voltage, synchrony. */
+int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const float* g_z, const float* g_v,
+                    float* d_w_rec, float* d_w_lgn, float* d_w_bkg, float* loss_out, void* stream);
+
+/* ExponentiatedAdam.update_step, dense branch (optimizers.py:353-376) followed by the
+ * SignedConstraint (models.py:419-427).  positive[n] uint8 is the sign mask fixed at
+ * construction; step is the 1-based iteration; grad is multiplied by grad_scale first. */
+int v1g_expadam_update(float* w, const float* grad, float* m, float* v, const uint8_t* positive,
+                       int64_t n, float lr, float beta1, float beta2, float eps, int64_t step,
+                       float grad_scale, void* stream);
+
+int v1g_get_counters(V1GHandle* h, V1GCounters* out_host);
+
+/* Waits for `stream` and returns the device-side status of the launches since the last call:
+ * V1G_ETIMEOUT if a bounded grid-barrier wait inside a rollout kernel gave up (the kernel then
+ * returned early and its outputs are invalid).  The reference has no counterpart; a TensorFlow
+ * op reports errors by raising from session.run. */
+int v1g_synchronize(V1GHandle* h, void* stream);
+
+/* Tuning knobs, mainly for tests: "rollout_chunk" (neurons per thread block in the rollout
+ * kernels, multiple of 32, 0 = automatic), "state_in_global" (1 = keep the rollout state in
+ * global memory even when it fits in shared memory), "spin_limit" (iterations a grid-barrier wait
+ * may spin before giving up).  No counterpart in the reference. */
+int v1g_set_option(V1GHandle* h, const char* name, long long value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* V1G_H_ */

@@ -1,0 +1,107 @@
+"""ctypes binding of ``libv1g.so`` (declarations follow ``include/v1g.h``).
+
+There is no CPU fallback: if the library is missing, :func:`load` raises with the build command.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libv1g.so")
+
+OK, EINVAL, ECUDA, ENOMEM, ETIMEOUT, ESTATE, ERANGE = 0, -1, -2, -3, -4, -5, -6
+SRC_REC, SRC_LGN, SRC_BKG = 0, 1, 2
+FLAG_HARD_RESET, FLAG_PSEUDO_GAUSS = 1, 2
+MAX_BATCH = 8
+
+
+class V1GConfig(C.Structure):
+    _fields_ = [("n_neurons", C.c_int32), ("n_receptors", C.c_int32), ("n_syn_types", C.c_int32),
+                ("max_delay", C.c_int32), ("n_lgn", C.c_int32), ("n_bkg", C.c_int32),
+                ("flags", C.c_int32), ("dt", C.c_float), ("dampening_factor", C.c_float),
+                ("recurrent_dampening", C.c_float), ("voltage_gradient_dampening", C.c_float),
+                ("gauss_std", C.c_float), ("pseudo_width", C.c_float), ("lr_scale", C.c_float)]
+
+
+class V1GState(C.Structure):
+    _fields_ = [("z_buf", C.c_void_p), ("v", C.c_void_p), ("r", C.c_void_p), ("asc", C.c_void_p),
+                ("psc_rise", C.c_void_p), ("psc", C.c_void_p)]
+
+
+class V1GLossSpec(C.Structure):
+    _fields_ = [("rate_target", C.c_void_p), ("v_lo", C.c_void_p), ("rate_cost", C.c_float),
+                ("voltage_cost", C.c_float), ("sync_cost", C.c_float), ("fano_target", C.c_float),
+                ("sync_bin", C.c_int32), ("loss_scale", C.c_float)]
+
+
+class V1GCounters(C.Structure):
+    _fields_ = [(n, C.c_ulonglong) for n in
+                ("spikes", "rec_rows", "rec_events", "lgn_rows", "lgn_events", "bkg_rows",
+                 "bkg_events", "bwd_rows", "bwd_events", "dw_events")]
+
+
+_P = C.c_void_p
+# name -> (restype, argtypes); every symbol include/v1g.h declares
+SIGNATURES = {
+    "v1g_create": (C.c_int, [C.POINTER(V1GConfig), C.POINTER(_P)]),
+    "v1g_destroy": (C.c_int, [_P]),
+    "v1g_last_error": (C.c_char_p, [_P]),
+    "v1g_version": (C.c_char_p, []),
+    "v1g_set_connectivity": (C.c_int, [_P, C.c_int, C.c_int64, _P, _P, C.c_int64]),
+    "v1g_build_pre_ind_table": (C.c_int, [C.c_int64, _P, C.c_int64, _P, _P]),
+    "v1g_get_pre_ind_table": (C.c_int, [_P, C.c_int, _P, _P]),
+    "v1g_set_neuron_params": (C.c_int, [_P] * 9),
+    "v1g_set_weights": (C.c_int, [_P, C.c_int, _P, _P]),
+    "v1g_compact_spikes": (C.c_int, [_P, _P, C.c_int32, C.c_int64, _P, C.c_int64, _P, _P]),
+    "v1g_syn_currents_fwd": (C.c_int, [_P, C.c_int, _P, C.c_int32, _P, _P]),
+    "v1g_syn_currents_bwd": (C.c_int, [_P, C.c_int, _P, _P, C.c_int32, _P, _P, _P]),
+    "v1g_step_fwd": (C.c_int, [_P, C.c_int32, C.POINTER(V1GState), _P, C.POINTER(V1GState), _P, _P]),
+    "v1g_step_bwd": (C.c_int, [_P, C.c_int32, C.POINTER(V1GState), _P, _P, _P, _P,
+                               C.POINTER(V1GState), _P, _P]),
+    "v1g_rollout_fwd": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, C.POINTER(V1GState), _P, _P,
+                                  C.c_int32, _P]),
+    "v1g_rollout_fwd_host": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P, _P, C.c_int32, _P]),
+    "v1g_rollout_bwd": (C.c_int, [_P, C.POINTER(V1GLossSpec), _P, _P, _P, _P, _P, _P, _P]),
+    "v1g_expadam_update": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64, C.c_float, C.c_float,
+                                     C.c_float, C.c_float, C.c_int64, C.c_float, _P]),
+    "v1g_get_counters": (C.c_int, [_P, C.POINTER(V1GCounters)]),
+    "v1g_synchronize": (C.c_int, [_P, _P]),
+    "v1g_set_option": (C.c_int, [_P, C.c_char_p, C.c_longlong]),
+}
+
+_lib = None
+
+
+def load():
+    """Open ``libv1g.so`` and attach the prototypes; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m v1_glif_model_b200.build` "
+            "(nvcc, sm_100a). There is no CPU fallback.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export the symbol
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+class V1GError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"libv1g error {code}: {msg}")
+        self.code = code
+
+
+def check(handle, rc):
+    """Map a status code to the exception the reference would raise (ValueError for bad input)."""
+    if rc == OK:
+        return
+    msg = load().v1g_last_error(handle).decode(errors="replace")
+    if rc == EINVAL:
+        raise ValueError(msg)
+    raise V1GError(rc, msg)

@@ -1,0 +1,148 @@
+// Internal definitions shared by the translation units of libv1g.so (not part of the C ABI).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+#include <vector>
+
+#include "v1g.h"
+
+#define V1G_NSRC 3
+
+// Device-side status word values (written by kernels, read by v1g_synchronize).
+#define V1G_DEV_OK 0
+#define V1G_DEV_BARRIER_TIMEOUT 1
+
+// One synaptic source: presynaptic CSR (scatter / transposed gather) + post-major gather table.
+struct V1GSource {
+  int64_t nnz = 0;
+  int64_t n_cols = 0;  // columns of the reference's dense_shape[1] (D*N for REC)
+  int n_src = 0;       // source neurons (N for REC, n_lgn, n_bkg)
+  int delays = 1;      // delay buckets per source neuron (D for REC, else 1)
+  // presynaptic CSR, rows numbered src*delays + (d-1): the `delays` buckets of one source neuron
+  // are contiguous, each bucket holding the same entries in the same order as row
+  // src + n_src*(d-1) of the reference's pre_ind_table
+  int32_t* rowptr = nullptr;  // [n_cols + 1]
+  int32_t* post = nullptr;    // [nnz]
+  float* w = nullptr;         // [nnz] weights in CSR order
+  uint8_t* sid = nullptr;     // [nnz]
+  int32_t* perm = nullptr;    // [nnz] CSR position -> position in the caller's arrays
+  // post-major table in the caller's order (the reference sorts synapses by post, so this is a
+  // plain row pointer over the caller's arrays)
+  int32_t* in_ptr = nullptr;  // [N + 1]
+  int32_t* in_pre = nullptr;  // [nnz] source column of each synapse, caller's order
+  uint8_t* in_sid = nullptr;  // [nnz]
+  float* w_ref = nullptr;     // [nnz] weights, caller's order
+  // only when the caller's arrays are not grouped by post: the gather table is a stable sort by
+  // post, in_perm maps its positions to the caller's, w_in holds the weights in table order
+  int32_t* in_perm = nullptr;
+  float* w_in = nullptr;
+  bool post_sorted = false;
+  const float* gather_w() const { return in_perm ? w_in : w_ref; }
+  // host copy of the reference-numbered table for v1g_get_pre_ind_table
+  std::vector<int32_t> order_host;
+  std::vector<int64_t> row_splits_host;
+  std::vector<int32_t> in_ptr_host;  // host copy of in_ptr
+};
+
+struct V1GHandle {
+  V1GConfig cfg;
+  int device = 0;
+  int n_sms = 0;
+  int smem_optin = 0;
+  mutable std::string err;
+  V1GSource src[V1G_NSRC];
+  bool params_set = false;
+  // per-neuron constants (device)
+  float *decay = nullptr, *cf = nullptr, *asc_decay = nullptr, *asc_amps = nullptr;
+  int32_t* tref = nullptr;
+  float* basis = nullptr;  // [S*R]
+  float syn_decay[V1G_MAX_RECEPTORS], psc_initial[V1G_MAX_RECEPTORS];
+  // straight-through factors computed in fp32 exactly as the reference does
+  float vd_keep = 1.f, vd_drop = 0.f;  // (1-d), d of the voltage self-loop
+  float rec_grad_factor = 1.f;         // 1 - clip(1 - recurrent_dampening)
+
+  // ---- scratch (grown on demand, freed in v1g_destroy) ----
+  int32_t* seg_counts = nullptr;  // compaction: per-segment counts / offsets
+  int64_t seg_cap = 0;
+  int64_t* coords = nullptr;  // op-level active list (row, col)
+  int64_t coords_cap = 0;
+  int32_t* d_count = nullptr;  // device int for counts
+  int32_t* h_count = nullptr;  // pinned host mirror
+  uint32_t* lgn_entries = nullptr;
+  int64_t lgn_entries_cap = 0;
+  int32_t* lgn_offsets = nullptr;  // [T*B*nseg + 1]
+  int64_t lgn_offsets_cap = 0;
+  int lgn_nseg = 0;
+  float* ring = nullptr;  // current ring [K][B][R][Np]
+  int64_t ring_cap = 0;
+  float* state_ws = nullptr;  // rollout state when it does not fit in shared memory
+  int64_t state_ws_cap = 0;
+  unsigned long long* barrier = nullptr;  // [0] = barrier counter
+  int32_t* dev_status = nullptr;          // device status word
+  unsigned long long* counters = nullptr;  // V1GCounters on the device
+  // saved forward for BPTT
+  float* tape_v = nullptr;    // [T][B][N]
+  uint8_t* tape_zr = nullptr;  // [T][B][N] bit0 spike, bit1 refractory
+  int64_t tape_cap = 0;
+  int tape_B = 0, tape_T = 0;
+  bool tape_valid = false;
+  const int32_t* tape_counts = nullptr;  // caller's bkg counts of the saved rollout
+  // backward scratch
+  float* dy_ring = nullptr;
+  int64_t dy_ring_cap = 0;
+  float* dw_csr[V1G_NSRC] = {nullptr, nullptr, nullptr};
+  float* loss_scratch = nullptr;  // rate sums [N], pop counts [B][T], bin grads, partial losses
+  int64_t loss_scratch_cap = 0;
+  // staging for the host-buffer entry point
+  uint8_t* stage_x = nullptr;
+  int32_t* stage_counts = nullptr;
+  uint8_t* stage_z = nullptr;
+  float* stage_v = nullptr;
+  int64_t stage_x_cap = 0, stage_counts_cap = 0, stage_z_cap = 0, stage_v_cap = 0;
+  // tuning (tests shrink these to exercise multi-block paths on tiny nets)
+  int opt_chunk = 0;          // neurons per block in the rollout kernels (0 = auto)
+  int opt_force_global = 0;   // keep rollout state in global memory even if it fits on chip
+  long long opt_spin_limit = 40000000LL;
+};
+
+int v1g_fail(const V1GHandle* h, int code, const char* fmt, ...);
+
+#define V1G_CUDA(h, call)                                                              \
+  do {                                                                                 \
+    cudaError_t e_ = (call);                                                           \
+    if (e_ != cudaSuccess)                                                             \
+      return v1g_fail(h, e_ == cudaErrorMemoryAllocation ? V1G_ENOMEM : V1G_ECUDA,     \
+                      "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, \
+                      __LINE__);                                                       \
+  } while (0)
+
+// Grow-only device buffer helper: keeps contents undefined after growth.
+template <typename T>
+int v1g_reserve(V1GHandle* h, T** p, int64_t* cap, int64_t need) {
+  if (need <= *cap && *p) return V1G_OK;
+  if (*p) {
+    V1G_CUDA(h, cudaFree(*p));
+    *p = nullptr;
+    *cap = 0;
+  }
+  if (need < 1) need = 1;
+  V1G_CUDA(h, cudaMalloc((void**)p, (size_t)need * sizeof(T)));
+  *cap = need;
+  return V1G_OK;
+}
+
+// ---- ordered compaction (v1g_compact.cu) ----
+// Input viewed as [n_rows][n_cols]; positives are listed in output order.  time_major_T > 0:
+// rows are (b, t) = (row / T, row % T) and the output is ordered (t, b, col); otherwise (row, col).
+// offsets[] gets the exclusive scan per (ordered) segment, offsets[n_segments] the total.
+enum V1GCompactKind { V1G_COMPACT_F32_COORDS = 0, V1G_COMPACT_U8_PACKED = 1 };
+#define V1G_SEG 4096
+int v1g_compact_count_scan(V1GHandle* h, int kind, const void* x, int n_rows, int64_t n_cols,
+                           int time_major_T, int32_t* offsets, int64_t* n_segments_out,
+                           cudaStream_t st);
+int v1g_compact_fill(V1GHandle* h, int kind, const void* x, int n_rows, int64_t n_cols,
+                     int time_major_T, const int32_t* offsets, void* out, int64_t cap,
+                     cudaStream_t st);

@@ -1,0 +1,615 @@
+// Fused forward rollout: T steps of V1Column.call (models.py:1059-1135) in ONE persistent
+// cooperative kernel, one thread block per SM.
+//
+// Each block owns a contiguous slice of neurons for all batch rows and keeps their state
+// (v, r, asc, psc_rise, psc, the last D spike bits) in shared memory for the whole rollout.
+// Synaptic currents travel through a ring of K = D+1 future-step accumulators in global memory
+// (L2-resident): a spike emitted at step t by neuron n adds w*basis[sid,:] of every outgoing
+// synapse with delay d into slot (t+d) mod K, so the block that computed the spike scatters it
+// immediately ("scatter on emit") and one grid barrier per step is enough.  LGN events of step
+// t+1 (compacted ahead of time into a time-major list) are scattered during step t; background
+// input is gathered per post-synaptic neuron from the step's Poisson counts (no atomics).
+//
+// Time step t of a block:
+//   dense   : read+clear ring slot t%K, gather background, PSC/ASC/membrane/refractory/threshold
+//             update, write v and z, push own spikes to a shared-memory list
+//   scatter : one warp per listed spike walks the D contiguous delay buckets of the neuron's CSR
+//             row; warps also share the LGN events of step t+1
+//   barrier : bounded spin on a monotonically increasing counter
+#include <algorithm>
+
+#include "v1g_rollout_common.cuh"
+
+namespace {
+
+struct FwdArgs {
+  int N, D, K, B, T, Np, chunk, chunkP, S, n_bkg;
+  int state_in_smem, bkg_in_smem, bkg_cap;
+  // connectivity
+  const int32_t *rec_rowptr, *rec_post;
+  const float* rec_w;
+  const uint8_t* rec_sid;
+  const int32_t *lgn_rowptr, *lgn_post;
+  const float* lgn_w;
+  const uint8_t* lgn_sid;
+  const int32_t *bkg_inptr, *bkg_inpre;
+  const float* bkg_w;
+  const uint8_t* bkg_insid;
+  // neuron constants
+  const float *decay, *cf, *asc_decay, *asc_amps, *basis;
+  const int32_t* tref;
+  float sd[V1G_MAX_RECEPTORS], pinit[V1G_MAX_RECEPTORS], dtsd[V1G_MAX_RECEPTORS];
+  float lr_scale, vd_keep, vd_drop;
+  int hard_reset;
+  // inputs
+  const int32_t* lgn_off;  // exclusive offsets per (t, b, seg) segment
+  const uint32_t* lgn_entries;
+  int lgn_nseg;
+  const int32_t* bkg_counts;  // [B][T][n_bkg]
+  // state (reference layouts, all NULL = zero state / no write-back)
+  V1GState st;
+  float* state_ws;
+  // outputs
+  uint8_t* z_out;
+  float* v_out;
+  float* tape_v;
+  uint8_t* tape_zr;
+  // plumbing
+  float* ring;
+  unsigned long long* barrier;
+  int32_t* status;
+  unsigned long long* counters;
+  long long spin_limit;
+};
+
+constexpr int NT = 768;
+
+template <int R_>
+__global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int NW = NT / 32;
+  const int B = a.B, D = a.D, K = a.K, N = a.N, Np = a.Np, chunkP = a.chunkP;
+  const int n0 = blockIdx.x * a.chunk;
+  const int cn = min(a.chunk, N - n0);
+  const int items = B * cn;
+
+  // ---- carve shared memory ----
+  unsigned char* sp_ = smem_raw;
+  auto take = [&](size_t bytes) {
+    unsigned char* p = sp_;
+    sp_ += (bytes + 15) & ~(size_t)15;
+    return p;
+  };
+  float* c_decay = (float*)take(sizeof(float) * chunkP);
+  float* c_cf = (float*)take(sizeof(float) * chunkP);
+  float* c_ad0 = (float*)take(sizeof(float) * chunkP);
+  float* c_ad1 = (float*)take(sizeof(float) * chunkP);
+  float* c_am0 = (float*)take(sizeof(float) * chunkP);
+  float* c_am1 = (float*)take(sizeof(float) * chunkP);
+  int* c_tref = (int*)take(sizeof(int) * chunkP);
+  int* c_bkptr = (int*)take(sizeof(int) * (chunkP + 1));
+  float* basis_s = (float*)take(sizeof(float) * a.S * R_);
+  uint32_t* spk_list = (uint32_t*)take(sizeof(uint32_t) * B * chunkP);
+  int* s_cnt = (int*)take(sizeof(int) * 2 * B * a.n_bkg);
+  int* s_misc = (int*)take(sizeof(int) * 4);  // [0] spike count, [1] abort flag
+  int* bk_pre_s = nullptr;
+  float* bk_w_s = nullptr;
+  uint8_t* bk_sid_s = nullptr;
+  if (a.bkg_in_smem) {
+    bk_pre_s = (int*)take(sizeof(int) * a.bkg_cap);
+    bk_w_s = (float*)take(sizeof(float) * a.bkg_cap);
+    bk_sid_s = (uint8_t*)take(a.bkg_cap);
+  }
+  float *S_v, *S_a0, *S_a1, *S_p, *S_pr;
+  uint8_t *S_r, *S_hist;
+  {
+    const size_t plane = (size_t)B * chunkP;
+    float* base;
+    if (a.state_in_smem) {
+      base = (float*)take(sizeof(float) * plane * (3 + 2 * R_) + 2 * plane);
+    } else {
+      const size_t slab = plane * (3 + 2 * R_) + (2 * plane + 3) / 4;
+      base = a.state_ws + (size_t)blockIdx.x * slab;
+    }
+    S_v = base;
+    S_a0 = S_v + plane;
+    S_a1 = S_a0 + plane;
+    S_p = S_a1 + plane;
+    S_pr = S_p + plane * R_;
+    S_r = (uint8_t*)(S_pr + plane * R_);
+    S_hist = S_r + plane;
+  }
+
+  // ---- load constants, background table, state ----
+  for (int k = tid; k < cn; k += NT) {
+    const int n = n0 + k;
+    c_decay[k] = a.decay[n];
+    c_cf[k] = a.cf[n];
+    c_ad0[k] = a.asc_decay[2 * n];
+    c_ad1[k] = a.asc_decay[2 * n + 1];
+    c_am0[k] = a.asc_amps[2 * n];
+    c_am1[k] = a.asc_amps[2 * n + 1];
+    c_tref[k] = a.tref[n];
+  }
+  const int bk_base = a.bkg_inptr[n0];
+  for (int k = tid; k <= cn; k += NT) c_bkptr[k] = a.bkg_inptr[n0 + k] - bk_base;
+  for (int i = tid; i < a.S * R_; i += NT) basis_s[i] = a.basis[i];
+  const int* bk_pre = a.bkg_inpre + bk_base;
+  const float* bk_w = a.bkg_w + bk_base;
+  const uint8_t* bk_sid = a.bkg_insid + bk_base;
+  if (a.bkg_in_smem) {
+    const int m = a.bkg_inptr[n0 + cn] - bk_base;
+    for (int j = tid; j < m; j += NT) {
+      bk_pre_s[j] = bk_pre[j];
+      bk_w_s[j] = bk_w[j];
+      bk_sid_s[j] = bk_sid[j];
+    }
+    bk_pre = bk_pre_s;
+    bk_w = bk_w_s;
+    bk_sid = bk_sid_s;
+  }
+  const bool have_state = a.st.v != nullptr;
+  for (int i = tid; i < items; i += NT) {
+    const int b = i / cn, k = i - b * cn, n = n0 + k;
+    const int si = b * chunkP + k;
+    const int64_t g = (int64_t)b * N + n;
+    unsigned hist = 0;
+    if (have_state) {
+      S_v[si] = a.st.v[g];
+      S_r[si] = (uint8_t)a.st.r[g];
+      S_a0[si] = a.st.asc[2 * g];
+      S_a1[si] = a.st.asc[2 * g + 1];
+      for (int r = 0; r < R_; ++r) {
+        S_p[(r * B + b) * chunkP + k] = a.st.psc[g * R_ + r];
+        S_pr[(r * B + b) * chunkP + k] = a.st.psc_rise[g * R_ + r];
+      }
+      for (int d = 0; d < D; ++d)
+        if (a.st.z_buf[((int64_t)b * D + d) * N + n] > 0.f) hist |= 1u << d;
+    } else {
+      S_v[si] = 0.f;
+      S_r[si] = 0;
+      S_a0[si] = 0.f;
+      S_a1[si] = 0.f;
+      for (int r = 0; r < R_; ++r) {
+        S_p[(r * B + b) * chunkP + k] = 0.f;
+        S_pr[(r * B + b) * chunkP + k] = 0.f;
+      }
+    }
+    S_hist[si] = (uint8_t)hist;
+  }
+  if (tid == 0) {
+    s_misc[0] = 0;
+    s_misc[1] = 0;
+  }
+  // background counts of step 0
+  for (int i = tid; i < B * a.n_bkg; i += NT) {
+    const int b = i / a.n_bkg, j = i - b * a.n_bkg;
+    s_cnt[i] = a.bkg_counts[((int64_t)b * a.T) * a.n_bkg + j];
+  }
+  __syncthreads();
+
+  unsigned long long c_spikes = 0, c_rec_ev = 0, c_lgn_rows = 0, c_lgn_ev = 0, c_bkg_ev = 0,
+                     c_bkg_rows = 0;
+
+  // Walk the D contiguous delay buckets of neuron n for a spike of batch row b emitted at step
+  // te (te < 0: pending spike of the initial z_buf); deliveries before step 0 are dropped.
+  auto walk_rec = [&](int b, int n, int te) {
+    int rp = 0;
+    if (lane <= D) rp = a.rec_rowptr[(int64_t)n * D + lane];
+    int bound[V1G_MAX_DELAY + 1];
+#pragma unroll
+    for (int d = 0; d <= V1G_MAX_DELAY; ++d) bound[d] = __shfl_sync(0xffffffffu, rp, d <= D ? d : 0);
+    const int j0 = bound[0], j1 = __shfl_sync(0xffffffffu, rp, D);
+    const int tk = ((te % K) + K) % K;
+    for (int j = j0 + lane; j < j1; j += 32) {
+      int d = 1;
+#pragma unroll
+      for (int q = 1; q < V1G_MAX_DELAY; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
+      if (te + d < 0) continue;
+      int slot = tk + d;
+      if (slot >= K) slot -= K;
+      const float wv = a.rec_w[j];
+      const float* bs = basis_s + (int)a.rec_sid[j] * R_;
+      float* dst = a.ring + ((int64_t)(slot * B + b) * R_) * Np + a.rec_post[j];
+#pragma unroll
+      for (int r = 0; r < R_; ++r) {
+        const float c = wv * bs[r];
+        if (c != 0.f) atomicAdd(dst + (int64_t)r * Np, c);
+      }
+    }
+    if (lane == 0) c_rec_ev += (unsigned long long)(j1 - j0);
+  };
+  // LGN events of step tt into its slot; shared by all warps of the grid.
+  auto scatter_lgn = [&](int tt) {
+    const int seg_per_t = B * a.lgn_nseg;
+    const int e0 = a.lgn_off[(int64_t)tt * seg_per_t], e1 = a.lgn_off[(int64_t)(tt + 1) * seg_per_t];
+    const int slot = tt % K;
+    const int gw = blockIdx.x * NW + warp, gnw = gridDim.x * NW;
+    for (int e = e0 + gw; e < e1; e += gnw) {
+      const uint32_t ent = a.lgn_entries[e];
+      const int b = ent >> 24, u = ent & 0xffffff;
+      const int j0 = a.lgn_rowptr[u], j1 = a.lgn_rowptr[u + 1];
+      for (int j = j0 + lane; j < j1; j += 32) {
+        const float wv = a.lgn_w[j];
+        const float* bs = basis_s + (int)a.lgn_sid[j] * R_;
+        float* dst = a.ring + ((int64_t)(slot * B + b) * R_) * Np + a.lgn_post[j];
+#pragma unroll
+        for (int r = 0; r < R_; ++r) {
+          const float c = wv * bs[r];
+          if (c != 0.f) atomicAdd(dst + (int64_t)r * Np, c);
+        }
+      }
+      if (lane == 0) {
+        c_lgn_rows += 1;
+        c_lgn_ev += (unsigned long long)(j1 - j0);
+      }
+    }
+  };
+
+  // ---- prologue: pending deliveries of the initial spike buffer, LGN events of step 0 ----
+  if (have_state) {
+    for (int i = warp; i < items; i += NW) {
+      const int b = i / cn, k = i - b * cn;
+      const unsigned hist = S_hist[b * chunkP + k];
+      for (int d = 0; d < D; ++d)
+        if (hist & (1u << d)) walk_rec(b, n0 + k, -(d + 1));
+    }
+  }
+  if (a.T > 0) scatter_lgn(0);
+  unsigned long long bar_target = gridDim.x;
+  bool ok = v1g_grid_barrier(a.barrier, bar_target, a.spin_limit, a.status, &s_misc[1]);
+
+  const unsigned hist_mask = (1u << D) - 1u;
+  auto load_ring = [&](int i, int slot, float (&I)[R_]) {
+    const int b = i / cn, k = i - b * cn;
+    const float* src = a.ring + ((int64_t)(slot * B + b) * R_) * Np + n0 + k;
+#pragma unroll
+    for (int r = 0; r < R_; ++r) I[r] = __ldcg(src + (int64_t)r * Np);
+  };
+
+  for (int t = 0; t < a.T && ok; ++t) {
+    const int slot = t % K;
+    const int* cnt_t = s_cnt + (t & 1) * B * a.n_bkg;
+    // prefetch next step's background counts into registers (stored after the dense phase)
+    int cnt_next[2] = {0, 0};
+    if (t + 1 < a.T) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int i = tid + q * NT;
+        if (i < B * a.n_bkg) {
+          const int b = i / a.n_bkg, j = i - b * a.n_bkg;
+          cnt_next[q] = a.bkg_counts[((int64_t)b * a.T + t + 1) * a.n_bkg + j];
+        }
+      }
+    }
+    if (blockIdx.x == 0)
+      for (int i = tid; i < B * a.n_bkg; i += NT) c_bkg_rows += cnt_t[i] > 0 ? 1 : 0;
+
+    // ---------------- dense phase ----------------
+    float I[R_], In[R_];
+    int i = tid;
+    if (i < items) load_ring(i, slot, I);
+    while (i < items) {
+      const int inext = i + NT;
+      if (inext < items) load_ring(inext, slot, In);
+      const int b = i / cn, k = i - b * cn, n = n0 + k;
+      const int si = b * chunkP + k;
+      {
+        float* dst = a.ring + ((int64_t)(slot * B + b) * R_) * Np + n;
+#pragma unroll
+        for (int r = 0; r < R_; ++r) __stcg(dst + (int64_t)r * Np, 0.f);
+      }
+      // background gather (models.py:890-934 in post-major form)
+      float G[R_];
+#pragma unroll
+      for (int r = 0; r < R_; ++r) G[r] = 0.f;
+      for (int j = c_bkptr[k]; j < c_bkptr[k + 1]; ++j) {
+        const int cnt = cnt_t[b * a.n_bkg + bk_pre[j]];
+        if (cnt > 0) {
+          const float wc = bk_w[j] * (float)cnt;
+          const float* bs = basis_s + (int)bk_sid[j] * R_;
+#pragma unroll
+          for (int r = 0; r < R_; ++r) G[r] += wc * bs[r];
+          c_bkg_ev += 1;
+        }
+      }
+      const unsigned hist = S_hist[si];
+      const float prev_z = (hist & 1u) ? 1.f : 0.f;
+      float csum = 0.f;
+#pragma unroll
+      for (int r = 0; r < R_; ++r) {
+        const float tot = (I[r] + G[r]) * a.lr_scale;
+        const int pi = (r * B + b) * chunkP + k;
+        const float pr = S_pr[pi], p = S_p[pi];
+        S_pr[pi] = pr * a.sd[r] + tot * a.pinit[r];
+        S_p[pi] = p * a.sd[r] + a.dtsd[r] * pr;
+        csum = (r == 0) ? p : csum + p;
+      }
+      const float a0 = S_a0[si], a1 = S_a1[si];
+      S_a0[si] = c_ad0[k] * a0 + prev_z * c_am0[k];
+      S_a1[si] = c_ad1[k] * a1 + prev_z * c_am1[k];
+      const float c1 = csum + (a0 + a1);
+      const float v = S_v[si];
+      const float dv = v * a.vd_keep + v * a.vd_drop;
+      float nv = (c_decay[k] * dv + c_cf[k] * c1) - prev_z;
+      int nr = (int)S_r[si] + ((hist & 1u) ? c_tref[k] : 0) - 1;
+      nr = nr > 0 ? nr : 0;
+      if (a.hard_reset && nr > 0) nv = 0.f;
+      const bool z = ((nv - 1.f) > 0.f) && (nr == 0);
+      S_v[si] = nv;
+      S_r[si] = (uint8_t)nr;
+      S_hist[si] = (uint8_t)(((hist << 1) | (z ? 1u : 0u)) & hist_mask);
+      if (a.z_out) __stcs(a.z_out + ((int64_t)b * a.T + t) * N + n, (uint8_t)(z ? 1 : 0));
+      if (a.v_out) __stcs(a.v_out + ((int64_t)b * a.T + t) * N + n, nv);
+      if (a.tape_v) {
+        const int64_t ti = ((int64_t)t * B + b) * N + n;
+        __stcs(a.tape_v + ti, nv);
+        __stcs(a.tape_zr + ti, (uint8_t)((z ? 1 : 0) | (nr > 0 ? 2 : 0)));
+      }
+      if (z) spk_list[atomicAdd(&s_misc[0], 1)] = ((uint32_t)b << 24) | (uint32_t)k;
+#pragma unroll
+      for (int r = 0; r < R_; ++r) I[r] = In[r];
+      i = inext;
+    }
+    // publish next step's counts
+    {
+      int* cnt_n = s_cnt + ((t + 1) & 1) * B * a.n_bkg;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int ii = tid + q * NT;
+        if (ii < B * a.n_bkg) cnt_n[ii] = cnt_next[q];
+      }
+    }
+    __syncthreads();
+    // ---------------- scatter phase ----------------
+    const int nspk = s_misc[0];
+    for (int e = warp; e < nspk; e += NW) {
+      const uint32_t ent = spk_list[e];
+      walk_rec((int)(ent >> 24), n0 + (int)(ent & 0xffffff), t);
+    }
+    if (tid == 0) c_spikes += (unsigned long long)nspk;
+    if (t + 1 < a.T) scatter_lgn(t + 1);
+    __syncthreads();  // everyone has read s_misc[0] before it is cleared
+    if (tid == 0) s_misc[0] = 0;
+    bar_target += gridDim.x;
+    ok = v1g_grid_barrier(a.barrier, bar_target, a.spin_limit, a.status, &s_misc[1]);
+  }
+
+  // ---- write the state back in the reference layouts ----
+  if (have_state && ok) {
+    for (int i = tid; i < items; i += NT) {
+      const int b = i / cn, k = i - b * cn, n = n0 + k;
+      const int si = b * chunkP + k;
+      const int64_t g = (int64_t)b * N + n;
+      a.st.v[g] = S_v[si];
+      a.st.r[g] = (int8_t)S_r[si];
+      a.st.asc[2 * g] = S_a0[si];
+      a.st.asc[2 * g + 1] = S_a1[si];
+      for (int r = 0; r < R_; ++r) {
+        a.st.psc[g * R_ + r] = S_p[(r * B + b) * chunkP + k];
+        a.st.psc_rise[g * R_ + r] = S_pr[(r * B + b) * chunkP + k];
+      }
+      const unsigned hist = S_hist[si];
+      for (int d = 0; d < D; ++d) a.st.z_buf[((int64_t)b * D + d) * N + n] = (hist >> d) & 1u ? 1.f : 0.f;
+    }
+  }
+  // ---- event counters ----
+  c_rec_ev = v1g_warp_sum(c_rec_ev);
+  c_lgn_rows = v1g_warp_sum(c_lgn_rows);
+  c_lgn_ev = v1g_warp_sum(c_lgn_ev);
+  c_bkg_ev = v1g_warp_sum(c_bkg_ev);
+  c_bkg_rows = v1g_warp_sum(c_bkg_rows);
+  if (lane == 0) {
+    V1GCounters* c = (V1GCounters*)a.counters;
+    if (c_rec_ev) atomicAdd(&c->rec_events, c_rec_ev);
+    if (c_lgn_rows) atomicAdd(&c->lgn_rows, c_lgn_rows);
+    if (c_lgn_ev) atomicAdd(&c->lgn_events, c_lgn_ev);
+    if (c_bkg_ev) atomicAdd(&c->bkg_events, c_bkg_ev);
+    if (c_bkg_rows) atomicAdd(&c->bkg_rows, c_bkg_rows);
+    if (tid == 0 && c_spikes) {
+      atomicAdd(&c->spikes, c_spikes);
+      atomicAdd(&c->rec_rows, c_spikes * (unsigned long long)D);
+    }
+  }
+}
+
+template <int R_>
+int launch_fwd(V1GHandle* h, const FwdArgs& a, int grid, size_t smem, cudaStream_t st) {
+  auto kern = rollout_fwd_kernel<R_>;
+  V1G_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int per_sm = 0;
+  V1G_CUDA(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, smem));
+  if (per_sm < 1 || grid > per_sm * h->n_sms)
+    return v1g_fail(h, V1G_ERANGE, "rollout grid of %d blocks cannot be co-resident (%d per SM)", grid, per_sm);
+  void* args[] = {(void*)&a};
+  V1G_CUDA(h, cudaLaunchCooperativeKernel((void*)kern, dim3(grid), dim3(NT), args, smem, st));
+  return V1G_OK;
+}
+
+}  // namespace
+
+// Sizes the per-block slice, decides where state and the background table live, and returns the
+// dynamic shared-memory bytes.  Shared by the forward and backward rollouts.
+size_t v1g_plan_rollout(const V1GHandle* h, int B, int per_item_floats, int per_item_bytes,
+                        int fixed_per_neuron_bytes, V1GRolloutPlan* p) {
+  const int N = h->cfg.n_neurons;
+  int chunk = h->opt_chunk > 0 ? h->opt_chunk : (N + h->n_sms - 1) / h->n_sms;
+  if (h->opt_chunk == 0 && chunk < 32) chunk = 32;
+  if (chunk > N) chunk = N;
+  p->chunk = chunk;
+  p->grid = (N + chunk - 1) / chunk;
+  p->chunkP = (chunk + 31) & ~31;
+  const size_t plane = (size_t)B * p->chunkP;
+  p->state_bytes = plane * per_item_floats * sizeof(float) + plane * per_item_bytes;
+  p->fixed_bytes = (size_t)p->chunkP * fixed_per_neuron_bytes + 64 * 16;
+  return p->fixed_bytes;
+}
+
+extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x,
+                               const int32_t* bkg_counts, V1GState* state, uint8_t* z_out,
+                               float* v_out, int32_t save_for_bwd, void* stream) {
+  if (!h) return V1G_EINVAL;
+  if (!h->params_set) return v1g_fail(h, V1G_ESTATE, "neuron parameters not set");
+  for (int s = 0; s < V1G_NSRC; ++s)
+    if (!h->src[s].rowptr) return v1g_fail(h, V1G_ESTATE, "connectivity of source %d not set", s);
+  if (batch <= 0 || batch > V1G_MAX_BATCH)
+    return v1g_fail(h, V1G_ERANGE, "batch=%d outside 1..%d", batch, V1G_MAX_BATCH);
+  if (n_steps < 0 || !x || !bkg_counts) return v1g_fail(h, V1G_EINVAL, "v1g_rollout_fwd: bad argument");
+  if (state && !(state->z_buf && state->v && state->r && state->asc && state->psc_rise && state->psc))
+    return v1g_fail(h, V1G_EINVAL, "v1g_rollout_fwd: state has null members");
+  cudaStream_t st = (cudaStream_t)stream;
+  const V1GConfig& c = h->cfg;
+  const int N = c.n_neurons, R = c.n_receptors, D = c.max_delay, K = D + 1, B = batch, T = n_steps;
+  h->tape_valid = false;
+  if (T == 0) return V1G_OK;
+  int rc;
+
+  // ---- LGN events: ordered compaction of x[B,T,n_lgn] into a time-major list ----
+  const int nseg = (c.n_lgn + V1G_SEG - 1) / V1G_SEG;
+  const int64_t nsegs = (int64_t)B * T * nseg;
+  if ((rc = v1g_reserve(h, &h->lgn_offsets, &h->lgn_offsets_cap, nsegs + 1))) return rc;
+  if ((rc = v1g_compact_count_scan(h, V1G_COMPACT_U8_PACKED, x, B * T, c.n_lgn, T, h->lgn_offsets,
+                                   nullptr, st)))
+    return rc;
+  V1G_CUDA(h, cudaMemcpyAsync(h->h_count, h->d_count, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  V1G_CUDA(h, cudaStreamSynchronize(st));
+  const int64_t n_lgn_events = h->h_count[0];
+  if ((rc = v1g_reserve(h, &h->lgn_entries, &h->lgn_entries_cap, n_lgn_events + 1))) return rc;
+  if ((rc = v1g_compact_fill(h, V1G_COMPACT_U8_PACKED, x, B * T, c.n_lgn, T, h->lgn_offsets,
+                             h->lgn_entries, n_lgn_events, st)))
+    return rc;
+  h->lgn_nseg = nseg;
+
+  // ---- plan ----
+  V1GRolloutPlan plan;
+  v1g_plan_rollout(h, B, 3 + 2 * R, 2, 0, &plan);
+  const int Np = (N + 31) & ~31;
+  const V1GSource& bk = h->src[V1G_SRC_BKG];
+  // largest background in-synapse count of any block slice
+  int bkg_cap = 0;
+  for (int g = 0; g < plan.grid; ++g) {
+    const int a0 = g * plan.chunk, a1 = std::min(N, a0 + plan.chunk);
+    bkg_cap = std::max(bkg_cap, bk.in_ptr_host[a1] - bk.in_ptr_host[a0]);
+  }
+  auto al = [](size_t b) { return (b + 15) & ~(size_t)15; };
+  size_t smem = 7 * al(sizeof(float) * plan.chunkP) + al(sizeof(int) * (plan.chunkP + 1)) +
+                al(sizeof(float) * c.n_syn_types * R) + al(sizeof(uint32_t) * B * plan.chunkP) +
+                al(sizeof(int) * 2 * B * c.n_bkg) + al(sizeof(int) * 4);
+  const size_t bkg_bytes = al(sizeof(int) * bkg_cap) + al(sizeof(float) * bkg_cap) + al(bkg_cap);
+  const size_t state_bytes = al(plan.state_bytes);
+  const size_t limit = (size_t)h->smem_optin;
+  int state_in_smem = 0, bkg_in_smem = 0;
+  if (!h->opt_force_global && smem + state_bytes <= limit) {
+    state_in_smem = 1;
+    smem += state_bytes;
+  }
+  if (smem + bkg_bytes <= limit) {
+    bkg_in_smem = 1;
+    smem += bkg_bytes;
+  }
+  if (smem > limit) return v1g_fail(h, V1G_ERANGE, "rollout needs %zu B of shared memory per block", smem);
+  if (!state_in_smem) {
+    const size_t plane = (size_t)B * plan.chunkP;
+    const size_t slab = plane * (3 + 2 * R) + (2 * plane + 3) / 4;
+    if ((rc = v1g_reserve(h, &h->state_ws, &h->state_ws_cap, (int64_t)(slab * plan.grid)))) return rc;
+  }
+  const int64_t ring_elems = (int64_t)K * B * R * Np;
+  if ((rc = v1g_reserve(h, &h->ring, &h->ring_cap, ring_elems))) return rc;
+  if (save_for_bwd) {
+    const int64_t need = (int64_t)T * B * N;
+    if (need > h->tape_cap || !h->tape_v) {
+      if (h->tape_v) cudaFree(h->tape_v);
+      if (h->tape_zr) cudaFree(h->tape_zr);
+      h->tape_v = nullptr;
+      h->tape_zr = nullptr;
+      h->tape_cap = 0;
+      V1G_CUDA(h, cudaMalloc((void**)&h->tape_v, (size_t)need * sizeof(float)));
+      V1G_CUDA(h, cudaMalloc((void**)&h->tape_zr, (size_t)need));
+      h->tape_cap = need;
+    }
+  }
+  V1G_CUDA(h, cudaMemsetAsync(h->ring, 0, (size_t)ring_elems * sizeof(float), st));
+  V1G_CUDA(h, cudaMemsetAsync(h->barrier, 0, sizeof(unsigned long long), st));
+  V1G_CUDA(h, cudaMemsetAsync(h->counters, 0, sizeof(V1GCounters), st));
+
+  FwdArgs a;
+  a.N = N; a.D = D; a.K = K; a.B = B; a.T = T; a.Np = Np;
+  a.chunk = plan.chunk; a.chunkP = plan.chunkP; a.S = c.n_syn_types; a.n_bkg = c.n_bkg;
+  a.state_in_smem = state_in_smem; a.bkg_in_smem = bkg_in_smem; a.bkg_cap = bkg_cap;
+  const V1GSource& rs = h->src[V1G_SRC_REC];
+  const V1GSource& ls = h->src[V1G_SRC_LGN];
+  a.rec_rowptr = rs.rowptr; a.rec_post = rs.post; a.rec_w = rs.w; a.rec_sid = rs.sid;
+  a.lgn_rowptr = ls.rowptr; a.lgn_post = ls.post; a.lgn_w = ls.w; a.lgn_sid = ls.sid;
+  a.bkg_inptr = bk.in_ptr; a.bkg_inpre = bk.in_pre; a.bkg_w = bk.gather_w(); a.bkg_insid = bk.in_sid;
+  a.decay = h->decay; a.cf = h->cf; a.asc_decay = h->asc_decay; a.asc_amps = h->asc_amps;
+  a.basis = h->basis; a.tref = h->tref;
+  for (int r = 0; r < V1G_MAX_RECEPTORS; ++r) {
+    a.sd[r] = r < R ? h->syn_decay[r] : 0.f;
+    a.pinit[r] = r < R ? h->psc_initial[r] : 0.f;
+    a.dtsd[r] = c.dt * a.sd[r];
+  }
+  a.lr_scale = c.lr_scale; a.vd_keep = h->vd_keep; a.vd_drop = h->vd_drop;
+  a.hard_reset = (c.flags & V1G_FLAG_HARD_RESET) ? 1 : 0;
+  a.lgn_off = h->lgn_offsets; a.lgn_entries = h->lgn_entries; a.lgn_nseg = nseg;
+  a.bkg_counts = bkg_counts;
+  if (state) a.st = *state; else a.st = V1GState{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  a.state_ws = h->state_ws;
+  a.z_out = z_out; a.v_out = v_out;
+  a.tape_v = save_for_bwd ? h->tape_v : nullptr;
+  a.tape_zr = save_for_bwd ? h->tape_zr : nullptr;
+  a.ring = h->ring; a.barrier = h->barrier; a.status = h->dev_status; a.counters = h->counters;
+  a.spin_limit = h->opt_spin_limit;
+  if (2 * NT < B * c.n_bkg)
+    return v1g_fail(h, V1G_ERANGE, "batch*n_bkg=%d exceeds %d", B * c.n_bkg, 2 * NT);
+
+  switch (R) {
+    case 1: rc = launch_fwd<1>(h, a, plan.grid, smem, st); break;
+    case 2: rc = launch_fwd<2>(h, a, plan.grid, smem, st); break;
+    case 3: rc = launch_fwd<3>(h, a, plan.grid, smem, st); break;
+    case 4: rc = launch_fwd<4>(h, a, plan.grid, smem, st); break;
+    case 5: rc = launch_fwd<5>(h, a, plan.grid, smem, st); break;
+    case 6: rc = launch_fwd<6>(h, a, plan.grid, smem, st); break;
+    case 7: rc = launch_fwd<7>(h, a, plan.grid, smem, st); break;
+    default: rc = launch_fwd<8>(h, a, plan.grid, smem, st); break;
+  }
+  if (rc) return rc;
+  if (save_for_bwd) {
+    h->tape_valid = true;
+    h->tape_B = B;
+    h->tape_T = T;
+    h->tape_counts = bkg_counts;
+  }
+  return V1G_OK;
+}
+
+extern "C" int v1g_rollout_fwd_host(V1GHandle* h, int32_t batch, int32_t n_steps,
+                                    const uint8_t* x_host, const int32_t* bkg_counts_host,
+                                    uint8_t* z_out_host, float* v_out_host, int32_t save_for_bwd,
+                                    void* stream) {
+  if (!h) return V1G_EINVAL;
+  if (batch <= 0 || n_steps < 0 || !x_host || !bkg_counts_host)
+    return v1g_fail(h, V1G_EINVAL, "v1g_rollout_fwd_host: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  const V1GConfig& c = h->cfg;
+  const int64_t nx = (int64_t)batch * n_steps * c.n_lgn, nc = (int64_t)batch * n_steps * c.n_bkg;
+  const int64_t no = (int64_t)batch * n_steps * c.n_neurons;
+  int rc;
+  if ((rc = v1g_reserve(h, &h->stage_x, &h->stage_x_cap, nx))) return rc;
+  if ((rc = v1g_reserve(h, &h->stage_counts, &h->stage_counts_cap, nc))) return rc;
+  if (z_out_host && (rc = v1g_reserve(h, &h->stage_z, &h->stage_z_cap, no))) return rc;
+  if (v_out_host && (rc = v1g_reserve(h, &h->stage_v, &h->stage_v_cap, no))) return rc;
+  V1G_CUDA(h, cudaMemcpyAsync(h->stage_x, x_host, (size_t)nx, cudaMemcpyHostToDevice, st));
+  V1G_CUDA(h, cudaMemcpyAsync(h->stage_counts, bkg_counts_host, (size_t)nc * sizeof(int32_t),
+                              cudaMemcpyHostToDevice, st));
+  if ((rc = v1g_rollout_fwd(h, batch, n_steps, h->stage_x, h->stage_counts, nullptr,
+                            z_out_host ? h->stage_z : nullptr, v_out_host ? h->stage_v : nullptr,
+                            save_for_bwd, st)))
+    return rc;
+  if (z_out_host)
+    V1G_CUDA(h, cudaMemcpyAsync(z_out_host, h->stage_z, (size_t)no, cudaMemcpyDeviceToHost, st));
+  if (v_out_host)
+    V1G_CUDA(h, cudaMemcpyAsync(v_out_host, h->stage_v, (size_t)no * sizeof(float),
+                                cudaMemcpyDeviceToHost, st));
+  return v1g_synchronize(h, st);
+}
