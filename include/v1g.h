@@ -231,6 +231,12 @@ int v1g_synchronize(V1GHandle* h, void* stream);
  * may spin before giving up).  No counterpart in the reference. */
 int v1g_set_option(V1GHandle* h, const char* name, long long value);
 
+/* With option "phase_timers" = 1 the rollout kernels record, per thread block, the nanoseconds
+ * spent in their dense, scatter and barrier phases and in total; this copies up to max_blocks
+ * records of 4 values to the host.  A profiling aid with no counterpart in the reference. */
+int v1g_get_phase_times(V1GHandle* h, unsigned long long* out_host, int32_t max_blocks,
+                        int32_t* n_blocks);
+
 #ifdef __cplusplus
 }
 #endif

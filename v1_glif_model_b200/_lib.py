@@ -8,7 +8,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libv1g.so")
+LIB_PATH = os.environ.get("V1G_LIB", os.path.join(HERE, "libv1g.so"))
 
 OK, EINVAL, ECUDA, ENOMEM, ETIMEOUT, ESTATE, ERANGE = 0, -1, -2, -3, -4, -5, -6
 SRC_REC, SRC_LGN, SRC_BKG = 0, 1, 2
@@ -68,6 +68,7 @@ SIGNATURES = {
     "v1g_get_counters": (C.c_int, [_P, C.POINTER(V1GCounters)]),
     "v1g_synchronize": (C.c_int, [_P, _P]),
     "v1g_set_option": (C.c_int, [_P, C.c_char_p, C.c_longlong]),
+    "v1g_get_phase_times": (C.c_int, [_P, _P, C.c_int32, C.POINTER(C.c_int32)]),
 }
 
 _lib = None

@@ -76,7 +76,7 @@ extern "C" int v1g_create(const V1GConfig* cfg, V1GHandle** out) {
   };
   chk(cudaMalloc((void**)&h->d_count, 4 * sizeof(int32_t)));
   chk(cudaMallocHost((void**)&h->h_count, 4 * sizeof(int32_t)));
-  chk(cudaMalloc((void**)&h->barrier, 4 * sizeof(unsigned long long)));
+  chk(cudaMalloc((void**)&h->barrier, 8 * 16 * sizeof(unsigned long long)));
   chk(cudaMalloc((void**)&h->dev_status, 4 * sizeof(int32_t)));
   chk(cudaMalloc((void**)&h->counters, sizeof(V1GCounters)));
   if (rc == V1G_OK) {
@@ -137,6 +137,7 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   cudaFree(h->stage_counts);
   cudaFree(h->stage_z);
   cudaFree(h->stage_v);
+  cudaFree(h->phase_ns);
   delete h;
   return V1G_OK;
 }
@@ -370,6 +371,16 @@ extern "C" int v1g_get_counters(V1GHandle* h, V1GCounters* out_host) {
   return V1G_OK;
 }
 
+extern "C" int v1g_get_phase_times(V1GHandle* h, unsigned long long* out_host, int32_t max_blocks,
+                                   int32_t* n_blocks) {
+  if (!h || !out_host || !n_blocks) return V1G_EINVAL;
+  const int n = std::min<int>(h->phase_grid, max_blocks);
+  *n_blocks = n;
+  if (n > 0 && h->phase_ns)
+    V1G_CUDA(h, cudaMemcpy(out_host, h->phase_ns, sizeof(unsigned long long) * 4 * n, cudaMemcpyDeviceToHost));
+  return V1G_OK;
+}
+
 extern "C" int v1g_set_option(V1GHandle* h, const char* name, long long value) {
   if (!h || !name) return V1G_EINVAL;
   if (!strcmp(name, "rollout_chunk")) {
@@ -378,6 +389,10 @@ extern "C" int v1g_set_option(V1GHandle* h, const char* name, long long value) {
     h->opt_chunk = (int)value;
   } else if (!strcmp(name, "state_in_global")) {
     h->opt_force_global = value != 0;
+  } else if (!strcmp(name, "force_smem_kernel")) {
+    h->opt_force_smem_kernel = value != 0;
+  } else if (!strcmp(name, "phase_timers")) {
+    h->opt_phase_timers = value != 0;
   } else if (!strcmp(name, "spin_limit")) {
     if (value < 1) return v1g_fail(h, V1G_EINVAL, "spin_limit must be >= 1");
     h->opt_spin_limit = value;

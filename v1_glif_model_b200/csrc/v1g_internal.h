@@ -105,7 +105,12 @@ struct V1GHandle {
   // tuning (tests shrink these to exercise multi-block paths on tiny nets)
   int opt_chunk = 0;          // neurons per block in the rollout kernels (0 = auto)
   int opt_force_global = 0;   // keep rollout state in global memory even if it fits on chip
-  long long opt_spin_limit = 40000000LL;
+  long long opt_spin_limit = 4000000LL;
+  int opt_force_smem_kernel = 0;  // never pick the register-resident forward kernel
+  int opt_phase_timers = 0;   // record per-block phase times of the rollout kernels
+  unsigned long long* phase_ns = nullptr;
+  int64_t phase_ns_cap = 0;
+  int phase_grid = 0;
 };
 
 int v1g_fail(const V1GHandle* h, int code, const char* fmt, ...);

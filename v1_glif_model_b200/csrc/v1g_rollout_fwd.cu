@@ -18,49 +18,9 @@
 //   barrier : bounded spin on a monotonically increasing counter
 #include <algorithm>
 
-#include "v1g_rollout_common.cuh"
+#include "v1g_rollout_fwd.cuh"
 
 namespace {
-
-struct FwdArgs {
-  int N, D, K, B, T, Np, chunk, chunkP, S, n_bkg;
-  int state_in_smem, bkg_in_smem, bkg_cap;
-  // connectivity
-  const int32_t *rec_rowptr, *rec_post;
-  const float* rec_w;
-  const uint8_t* rec_sid;
-  const int32_t *lgn_rowptr, *lgn_post;
-  const float* lgn_w;
-  const uint8_t* lgn_sid;
-  const int32_t *bkg_inptr, *bkg_inpre;
-  const float* bkg_w;
-  const uint8_t* bkg_insid;
-  // neuron constants
-  const float *decay, *cf, *asc_decay, *asc_amps, *basis;
-  const int32_t* tref;
-  float sd[V1G_MAX_RECEPTORS], pinit[V1G_MAX_RECEPTORS], dtsd[V1G_MAX_RECEPTORS];
-  float lr_scale, vd_keep, vd_drop;
-  int hard_reset;
-  // inputs
-  const int32_t* lgn_off;  // exclusive offsets per (t, b, seg) segment
-  const uint32_t* lgn_entries;
-  int lgn_nseg;
-  const int32_t* bkg_counts;  // [B][T][n_bkg]
-  // state (reference layouts, all NULL = zero state / no write-back)
-  V1GState st;
-  float* state_ws;
-  // outputs
-  uint8_t* z_out;
-  float* v_out;
-  float* tape_v;
-  uint8_t* tape_zr;
-  // plumbing
-  float* ring;
-  unsigned long long* barrier;
-  int32_t* status;
-  unsigned long long* counters;
-  long long spin_limit;
-};
 
 constexpr int NT = 768;
 
@@ -92,7 +52,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
   float* basis_s = (float*)take(sizeof(float) * a.S * R_);
   uint32_t* spk_list = (uint32_t*)take(sizeof(uint32_t) * B * chunkP);
   int* s_cnt = (int*)take(sizeof(int) * 2 * B * a.n_bkg);
-  int* s_misc = (int*)take(sizeof(int) * 4);  // [0] spike count, [1] abort flag
+  int* s_misc = (int*)take(sizeof(int) * 4);  // [1] abort flag, [2],[3] spike counts (double buffer)
   int* bk_pre_s = nullptr;
   float* bk_w_s = nullptr;
   uint8_t* bk_sid_s = nullptr;
@@ -181,70 +141,20 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
   if (tid == 0) {
     s_misc[0] = 0;
     s_misc[1] = 0;
-  }
-  // background counts of step 0
-  for (int i = tid; i < B * a.n_bkg; i += NT) {
-    const int b = i / a.n_bkg, j = i - b * a.n_bkg;
-    s_cnt[i] = a.bkg_counts[((int64_t)b * a.T) * a.n_bkg + j];
+    s_misc[2] = 0;
+    s_misc[3] = 0;
   }
   __syncthreads();
 
   unsigned long long c_spikes = 0, c_rec_ev = 0, c_lgn_rows = 0, c_lgn_ev = 0, c_bkg_ev = 0,
                      c_bkg_rows = 0;
 
-  // Walk the D contiguous delay buckets of neuron n for a spike of batch row b emitted at step
-  // te (te < 0: pending spike of the initial z_buf); deliveries before step 0 are dropped.
   auto walk_rec = [&](int b, int n, int te) {
-    int rp = 0;
-    if (lane <= D) rp = a.rec_rowptr[(int64_t)n * D + lane];
-    int bound[V1G_MAX_DELAY + 1];
-#pragma unroll
-    for (int d = 0; d <= V1G_MAX_DELAY; ++d) bound[d] = __shfl_sync(0xffffffffu, rp, d <= D ? d : 0);
-    const int j0 = bound[0], j1 = __shfl_sync(0xffffffffu, rp, D);
-    const int tk = ((te % K) + K) % K;
-    for (int j = j0 + lane; j < j1; j += 32) {
-      int d = 1;
-#pragma unroll
-      for (int q = 1; q < V1G_MAX_DELAY; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
-      if (te + d < 0) continue;
-      int slot = tk + d;
-      if (slot >= K) slot -= K;
-      const float wv = a.rec_w[j];
-      const float* bs = basis_s + (int)a.rec_sid[j] * R_;
-      float* dst = a.ring + ((int64_t)(slot * B + b) * R_) * Np + a.rec_post[j];
-#pragma unroll
-      for (int r = 0; r < R_; ++r) {
-        const float c = wv * bs[r];
-        if (c != 0.f) atomicAdd(dst + (int64_t)r * Np, c);
-      }
-    }
-    if (lane == 0) c_rec_ev += (unsigned long long)(j1 - j0);
+    v1g_walk_rec<R_>(a, basis_s, lane, b, a.rec_rowptr + (int64_t)n * D, te, c_rec_ev);
   };
-  // LGN events of step tt into its slot; shared by all warps of the grid.
   auto scatter_lgn = [&](int tt) {
-    const int seg_per_t = B * a.lgn_nseg;
-    const int e0 = a.lgn_off[(int64_t)tt * seg_per_t], e1 = a.lgn_off[(int64_t)(tt + 1) * seg_per_t];
-    const int slot = tt % K;
-    const int gw = blockIdx.x * NW + warp, gnw = gridDim.x * NW;
-    for (int e = e0 + gw; e < e1; e += gnw) {
-      const uint32_t ent = a.lgn_entries[e];
-      const int b = ent >> 24, u = ent & 0xffffff;
-      const int j0 = a.lgn_rowptr[u], j1 = a.lgn_rowptr[u + 1];
-      for (int j = j0 + lane; j < j1; j += 32) {
-        const float wv = a.lgn_w[j];
-        const float* bs = basis_s + (int)a.lgn_sid[j] * R_;
-        float* dst = a.ring + ((int64_t)(slot * B + b) * R_) * Np + a.lgn_post[j];
-#pragma unroll
-        for (int r = 0; r < R_; ++r) {
-          const float c = wv * bs[r];
-          if (c != 0.f) atomicAdd(dst + (int64_t)r * Np, c);
-        }
-      }
-      if (lane == 0) {
-        c_lgn_rows += 1;
-        c_lgn_ev += (unsigned long long)(j1 - j0);
-      }
-    }
+    v1g_scatter_lgn<R_>(a, basis_s, lane, blockIdx.x * NW + warp, gridDim.x * NW, tt, c_lgn_rows,
+                        c_lgn_ev);
   };
 
   // ---- prologue: pending deliveries of the initial spike buffer, LGN events of step 0 ----
@@ -257,73 +167,116 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
     }
   }
   if (a.T > 0) scatter_lgn(0);
-  unsigned long long bar_target = gridDim.x;
-  bool ok = v1g_grid_barrier(a.barrier, bar_target, a.spin_limit, a.status, &s_misc[1]);
+  __syncthreads();
+  if (tid == 0) v1g_arrive(v1g_phase_counter(a.barrier, 0));  // phase 0: prologue done
 
   const unsigned hist_mask = (1u << D) - 1u;
-  auto load_ring = [&](int i, int slot, float (&I)[R_]) {
-    const int b = i / cn, k = i - b * cn;
+  const unsigned long long G = gridDim.x;
+  const int nb = B * a.n_bkg;
+  auto load_ring = [&](int b, int k, int slot, float (&I)[R_]) {
     const float* src = a.ring + ((int64_t)(slot * B + b) * R_) * Np + n0 + k;
 #pragma unroll
     for (int r = 0; r < R_; ++r) I[r] = __ldcg(src + (int64_t)r * Np);
   };
+  // total input of step s for item (b,k): ring slot (cleared on the way) + background gather
+  auto finish_input = [&](int b, int k, int slot, const int* cnt_s, float (&I)[R_]) {
+    float* dst = a.ring + ((int64_t)(slot * B + b) * R_) * Np + n0 + k;
+#pragma unroll
+    for (int r = 0; r < R_; ++r) __stcg(dst + (int64_t)r * Np, 0.f);
+    float Gs[R_];
+#pragma unroll
+    for (int r = 0; r < R_; ++r) Gs[r] = 0.f;
+    const int j1 = c_bkptr[k + 1];
+    for (int j = c_bkptr[k]; j < j1; ++j) {
+      const int cnt = cnt_s[b * a.n_bkg + bk_pre[j]];
+      if (cnt > 0) {
+        const float wc = bk_w[j] * (float)cnt;
+        const float* bs = basis_s + (int)bk_sid[j] * R_;
+#pragma unroll
+        for (int r = 0; r < R_; ++r) Gs[r] += wc * bs[r];
+        c_bkg_ev += 1;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R_; ++r) I[r] = (I[r] + Gs[r]) * a.lr_scale;
+  };
 
+  unsigned long long ph_dense = 0, ph_scatter = 0, ph_barrier = 0;
+  const bool prof = a.phase_ns != nullptr && tid == 0;
+  const unsigned long long ph_start = prof ? gtime() : 0;
+  unsigned long long seen = 0;  // thread 0: last value read from the barrier counter
+  bool ok = true;
+
+  // The currents delivered at step s enter psc_rise(s), reach psc(s+1) and the membrane only at
+  // s+2, so iteration t (which produces v(t), z(t)) consumes ring slot t-2: it needs every block
+  // to have finished iteration t-3, not t-1.  Blocks therefore synchronise through a LAGGED
+  // counter and almost never wait.  On entry to iteration t the block holds psc(t-2) in S_p and
+  // psc_rise(t-3) in S_pr (for t >= 2; the first two iterations start from the given state).
   for (int t = 0; t < a.T && ok; ++t) {
-    const int slot = t % K;
-    const int* cnt_t = s_cnt + (t & 1) * B * a.n_bkg;
-    // prefetch next step's background counts into registers (stored after the dense phase)
+    const unsigned long long ph0 = prof ? gtime() : 0;
+    if (tid == 0) {
+      if (t >= 2) {
+        // every block must have finished iteration t-3 (phase t-2)
+        const unsigned long long target = v1g_phase_target(t - 2, G);
+        if (seen < target)
+          seen = v1g_wait(v1g_phase_counter(a.barrier, t - 2), target, a.spin_limit, a.status);
+        if (seen < target) s_misc[1] = 1;
+      }
+    }
+    __syncthreads();
+    if (s_misc[1]) {
+      ok = false;
+      break;
+    }
+    // iteration t-1 of this block is complete: arrive at phase t
+    if (tid == 0 && t >= 1) v1g_arrive(v1g_phase_counter(a.barrier, t));
+    const unsigned long long ph1 = prof ? gtime() : 0;
+    const bool consume = t >= 2;
+    const int slot = consume ? (t - 2) % K : 0;
+    const int* cnt_s = s_cnt + (t & 1) * nb;  // counts of step t-2
+    // prefetch the counts of step t-1 (used by iteration t+1)
     int cnt_next[2] = {0, 0};
-    if (t + 1 < a.T) {
+    if (t >= 1 && t + 1 < a.T + 2) {
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         const int i = tid + q * NT;
-        if (i < B * a.n_bkg) {
+        if (i < nb) {
           const int b = i / a.n_bkg, j = i - b * a.n_bkg;
-          cnt_next[q] = a.bkg_counts[((int64_t)b * a.T + t + 1) * a.n_bkg + j];
+          cnt_next[q] = a.bkg_counts[((int64_t)b * a.T + (t - 1)) * a.n_bkg + j];
         }
       }
     }
-    if (blockIdx.x == 0)
-      for (int i = tid; i < B * a.n_bkg; i += NT) c_bkg_rows += cnt_t[i] > 0 ? 1 : 0;
+    if (blockIdx.x == 0 && consume)
+      for (int i = tid; i < nb; i += NT) c_bkg_rows += cnt_s[i] > 0 ? 1 : 0;
+    int* nspk_p = &s_misc[2 + (t & 1)];
 
     // ---------------- dense phase ----------------
     float I[R_], In[R_];
-    int i = tid;
-    if (i < items) load_ring(i, slot, I);
-    while (i < items) {
-      const int inext = i + NT;
-      if (inext < items) load_ring(inext, slot, In);
-      const int b = i / cn, k = i - b * cn, n = n0 + k;
+    int b = 0, k = tid;
+    while (k >= cn && b < B) { k -= cn; ++b; }
+    if (consume && b < B) load_ring(b, k, slot, I);
+    while (b < B) {
+      int bn = b, kn = k + NT;
+      while (kn >= cn && bn < B) { kn -= cn; ++bn; }
+      if (consume && bn < B) load_ring(bn, kn, slot, In);
+      const int n = n0 + k;
       const int si = b * chunkP + k;
-      {
-        float* dst = a.ring + ((int64_t)(slot * B + b) * R_) * Np + n;
-#pragma unroll
-        for (int r = 0; r < R_; ++r) __stcg(dst + (int64_t)r * Np, 0.f);
-      }
-      // background gather (models.py:890-934 in post-major form)
-      float G[R_];
-#pragma unroll
-      for (int r = 0; r < R_; ++r) G[r] = 0.f;
-      for (int j = c_bkptr[k]; j < c_bkptr[k + 1]; ++j) {
-        const int cnt = cnt_t[b * a.n_bkg + bk_pre[j]];
-        if (cnt > 0) {
-          const float wc = bk_w[j] * (float)cnt;
-          const float* bs = basis_s + (int)bk_sid[j] * R_;
-#pragma unroll
-          for (int r = 0; r < R_; ++r) G[r] += wc * bs[r];
-          c_bkg_ev += 1;
-        }
-      }
+      if (consume) finish_input(b, k, slot, cnt_s, I);
       const unsigned hist = S_hist[si];
       const float prev_z = (hist & 1u) ? 1.f : 0.f;
       float csum = 0.f;
 #pragma unroll
       for (int r = 0; r < R_; ++r) {
-        const float tot = (I[r] + G[r]) * a.lr_scale;
         const int pi = (r * B + b) * chunkP + k;
-        const float pr = S_pr[pi], p = S_p[pi];
-        S_pr[pi] = pr * a.sd[r] + tot * a.pinit[r];
-        S_p[pi] = p * a.sd[r] + a.dtsd[r] * pr;
+        float pr = S_pr[pi], p = S_p[pi];
+        if (consume) {
+          pr = pr * a.sd[r] + I[r] * a.pinit[r];  // psc_rise(t-2)
+          S_pr[pi] = pr;
+        }
+        if (t >= 1) {
+          p = p * a.sd[r] + a.dtsd[r] * pr;  // psc(t-1)
+          S_p[pi] = p;
+        }
         csum = (r == 0) ? p : csum + p;
       }
       const float a0 = S_a0[si], a1 = S_a1[si];
@@ -347,33 +300,90 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
         __stcs(a.tape_v + ti, nv);
         __stcs(a.tape_zr + ti, (uint8_t)((z ? 1 : 0) | (nr > 0 ? 2 : 0)));
       }
-      if (z) spk_list[atomicAdd(&s_misc[0], 1)] = ((uint32_t)b << 24) | (uint32_t)k;
+      if (z) spk_list[atomicAdd(nspk_p, 1)] = ((uint32_t)b << 24) | (uint32_t)k;
 #pragma unroll
       for (int r = 0; r < R_; ++r) I[r] = In[r];
-      i = inext;
+      b = bn;
+      k = kn;
     }
-    // publish next step's counts
     {
-      int* cnt_n = s_cnt + ((t + 1) & 1) * B * a.n_bkg;
+      int* cnt_n = s_cnt + ((t + 1) & 1) * nb;
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         const int ii = tid + q * NT;
-        if (ii < B * a.n_bkg) cnt_n[ii] = cnt_next[q];
+        if (ii < nb) cnt_n[ii] = cnt_next[q];
       }
     }
     __syncthreads();
+    const unsigned long long ph2 = prof ? gtime() : 0;
     // ---------------- scatter phase ----------------
-    const int nspk = s_misc[0];
+    if (tid == 0) {
+      // early poll of the phase the next iteration waits for
+      seen = (t >= 1) ? v1g_ld_acquire(v1g_phase_counter(a.barrier, t - 1)) : 0;
+      s_misc[2 + ((t + 1) & 1)] = 0;
+    }
+    const int nspk = *nspk_p;
     for (int e = warp; e < nspk; e += NW) {
       const uint32_t ent = spk_list[e];
       walk_rec((int)(ent >> 24), n0 + (int)(ent & 0xffffff), t);
     }
     if (tid == 0) c_spikes += (unsigned long long)nspk;
     if (t + 1 < a.T) scatter_lgn(t + 1);
-    __syncthreads();  // everyone has read s_misc[0] before it is cleared
-    if (tid == 0) s_misc[0] = 0;
-    bar_target += gridDim.x;
-    ok = v1g_grid_barrier(a.barrier, bar_target, a.spin_limit, a.status, &s_misc[1]);
+    if (prof) {
+      const unsigned long long ph3 = gtime();
+      ph_barrier += ph1 - ph0;
+      ph_dense += ph2 - ph1;
+      ph_scatter += ph3 - ph2;
+    }
+  }
+  // ---- full barrier, then bring psc / psc_rise up to step T-1 ----
+  __syncthreads();
+  if (tid == 0) {
+    if (ok && a.T >= 1) v1g_arrive(v1g_phase_counter(a.barrier, a.T));
+    const unsigned long long target = v1g_phase_target(a.T, G);
+    if (ok) {
+      seen = v1g_wait(v1g_phase_counter(a.barrier, a.T), target, a.spin_limit, a.status);
+      if (seen < target) s_misc[1] = 1;
+    }
+  }
+  __syncthreads();
+  ok = ok && !s_misc[1];
+  if (ok && a.T >= 1) {
+    // remaining input steps: T-2 (if any) and T-1
+    for (int s = max(a.T - 2, 0); s < a.T; ++s) {
+      __syncthreads();
+      const int slot = s % K;
+      for (int i = tid; i < nb; i += NT) {
+        const int b = i / a.n_bkg, j = i - b * a.n_bkg;
+        s_cnt[i] = a.bkg_counts[((int64_t)b * a.T + s) * a.n_bkg + j];
+      }
+      __syncthreads();
+      if (blockIdx.x == 0)
+        for (int i = tid; i < nb; i += NT) c_bkg_rows += s_cnt[i] > 0 ? 1 : 0;
+      for (int i = tid; i < items; i += NT) {
+        const int b = i / cn, k = i - b * cn;
+        float I[R_];
+        load_ring(b, k, slot, I);
+        finish_input(b, k, slot, s_cnt, I);
+#pragma unroll
+        for (int r = 0; r < R_; ++r) {
+          const int pi = (r * B + b) * chunkP + k;
+          float pr = S_pr[pi];
+          // psc(s) needs psc_rise(s-1): advance psc first unless it is already at step s
+          if (s == a.T - 1 && a.T >= 1) S_p[pi] = S_p[pi] * a.sd[r] + a.dtsd[r] * pr;
+          pr = pr * a.sd[r] + I[r] * a.pinit[r];
+          S_pr[pi] = pr;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (prof) {
+    unsigned long long* o = a.phase_ns + 4 * blockIdx.x;
+    o[0] = ph_dense;
+    o[1] = ph_scatter;
+    o[2] = ph_barrier;
+    o[3] = gtime() - ph_start;
   }
 
   // ---- write the state back in the reference layouts ----
@@ -460,7 +470,7 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
     return v1g_fail(h, V1G_EINVAL, "v1g_rollout_fwd: state has null members");
   cudaStream_t st = (cudaStream_t)stream;
   const V1GConfig& c = h->cfg;
-  const int N = c.n_neurons, R = c.n_receptors, D = c.max_delay, K = D + 1, B = batch, T = n_steps;
+  const int N = c.n_neurons, R = c.n_receptors, D = c.max_delay, K = D + 6, B = batch, T = n_steps;
   h->tape_valid = false;
   if (T == 0) return V1G_OK;
   int rc;
@@ -530,7 +540,7 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
     }
   }
   V1G_CUDA(h, cudaMemsetAsync(h->ring, 0, (size_t)ring_elems * sizeof(float), st));
-  V1G_CUDA(h, cudaMemsetAsync(h->barrier, 0, sizeof(unsigned long long), st));
+  V1G_CUDA(h, cudaMemsetAsync(h->barrier, 0, V1G_BARRIER_BYTES, st));
   V1G_CUDA(h, cudaMemsetAsync(h->counters, 0, sizeof(V1GCounters), st));
 
   FwdArgs a;
@@ -560,9 +570,24 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
   a.tape_zr = save_for_bwd ? h->tape_zr : nullptr;
   a.ring = h->ring; a.barrier = h->barrier; a.status = h->dev_status; a.counters = h->counters;
   a.spin_limit = h->opt_spin_limit;
+  a.phase_ns = nullptr;
+  if (h->opt_phase_timers) {
+    if ((rc = v1g_reserve(h, &h->phase_ns, &h->phase_ns_cap, (int64_t)4 * plan.grid))) return rc;
+    V1G_CUDA(h, cudaMemsetAsync(h->phase_ns, 0, sizeof(unsigned long long) * 4 * plan.grid, st));
+    a.phase_ns = h->phase_ns;
+    h->phase_grid = plan.grid;
+  }
   if (2 * NT < B * c.n_bkg)
     return v1g_fail(h, V1G_ERANGE, "batch*n_bkg=%d exceeds %d", B * c.n_bkg, 2 * NT);
 
+  // Register-resident kernel when the slice fits one neuron per thread and the (R, B) pair is
+  // instantiated; the shared-memory kernel otherwise.
+  const bool reg_ok = !h->opt_force_smem_kernel && !h->opt_force_global && plan.chunk <= V1G_NT_REG &&
+                      (R == 4 || R == 5) && B <= 6 &&
+                      v1g_fwd_reg_smem(h, B, plan.chunkP, bkg_cap) <= limit;
+  if (reg_ok) {
+    rc = v1g_launch_fwd_reg(h, a, R, plan.grid, v1g_fwd_reg_smem(h, B, plan.chunkP, bkg_cap), st);
+  } else
   switch (R) {
     case 1: rc = launch_fwd<1>(h, a, plan.grid, smem, st); break;
     case 2: rc = launch_fwd<2>(h, a, plan.grid, smem, st); break;

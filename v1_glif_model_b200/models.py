@@ -204,6 +204,14 @@ class V1Column:
         self._check(self._lib.v1g_get_counters(self._libh, C.byref(c)))
         return {n: int(getattr(c, n)) for n, _ in c._fields_}
 
+    def phase_times(self):
+        """Per-block (dense, scatter, barrier, total) nanoseconds of the last rollout kernel
+        (needs ``set_option('phase_timers', 1)``)."""
+        buf = np.zeros((1024, 4), dtype=np.uint64)
+        n = C.c_int32(0)
+        self._check(self._lib.v1g_get_phase_times(self._libh, buf.ctypes.data, 1024, C.byref(n)))
+        return buf[:n.value]
+
     def pre_ind_table(self, source=_lib.SRC_REC):
         """``(order, row_splits)`` of a source as built inside the library."""
         nnz = {0: self.recurrent_indices, 1: self.input_indices, 2: self.bkg_input_indices}[source].shape[0]
