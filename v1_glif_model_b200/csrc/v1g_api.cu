@@ -187,6 +187,8 @@ extern "C" int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz,
   }
   V1GSource& s = h->src[source];
   free_source(s);
+  cudaFree(h->dw_csr[source]);
+  h->dw_csr[source] = nullptr;
   s.nnz = nnz;
   s.n_cols = n_source_cols;
   s.n_src = (int)n_src;

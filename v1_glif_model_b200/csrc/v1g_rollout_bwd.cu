@@ -1,5 +1,664 @@
+// Fused backward rollout (BPTT): the reverse sweep over the T steps saved by v1g_rollout_fwd, in
+// ONE persistent cooperative kernel with the same neuron slicing as the forward kernels.
+//
+// Adjoint recursion (g_* = dL/d(state after step t); reference: the custom gradients at
+// models.py:58-64, 174-261 and the stop-gradients / straight-through factors at :994, 1010-1018,
+// 1081), processed for t = T-1 .. 0:
+//   g_z   = dl/dz(t) + rec_factor * sum over the out-synapses j of neuron n (delay d_j) of
+//           w_j * sum_r basis[sid_j, r] * dy(t + d_j)[b, post_j, r]
+//   g_v'  = dl/dv(t) + g_v + [r(t) == 0] * g_z * pseudo(v(t) - 1)        (hard reset: 0 if r(t) > 0)
+//   g_v  <- decay * (1 - d_v) * g_v'              g_asc_k <- asc_decay_k * g_asc_k + cf * g_v'
+//   g_p  <- sd * g_p + cf * g_v'                  g_pr   <- sd * g_pr + dt * sd * g_p(old)
+//   dy(t)[b, n, r] = lr_scale * psc_initial_r * g_pr(t)
+//   dW_rec[j] += sum_b z(t)[b, n] * sum_r basis[sid_j, r] * dy(t + d_j)[b, post_j, r]   (no dampening)
+//   dW_lgn[j] += sum_b x(t)[b, pre_j] * (same with dy(t))      dW_bkg[j] += sum_b count(t)[b, pre_j] * (...)
+//
+// dy(t) only depends on g_pr(t+1) and g_p(t+1), which are final once step t+2 has been processed,
+// so the block that owns neuron n publishes dy(t-2) while it processes step t.  A block at step t
+// reads dy(t+1 .. t+D) of arbitrary neurons, i.e. values published at steps >= t+3: like the
+// forward sweep, blocks synchronise through a lagged per-phase counter and rarely wait.
+//
+// What is published is Q, a ring over K = D+6 steps with a 16- or 32-byte row per (neuron, channel):
+//   projected mode (S <= 8 synapse types): Q[slot][n][s][b] = sum_r basis[s, r] * dy[b, n, r]; a
+//       synapse then needs ONE sector, Q[slot][post][sid][0..B)
+//   raw mode: Q[slot][n][r][b] = dy[b, n, r]; the consumer contracts with basis[sid, :] (R sectors)
+// The gather walks every neuron's CSR row (all synapses, every step: the pseudo-derivative is
+// non-zero for non-spiking neurons), one warp per row, except rows whose B batch entries are all
+// refractory / outside the pseudo-derivative's support and did not spike (exactly zero result).
+#include <algorithm>
+
 #include "v1g_rollout_common.cuh"
-extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec*, const float*, const float*,
-                               float*, float*, float*, float*, void*) {
-  return v1g_fail(h, V1G_ESTATE, "backward rollout: work in progress");
+
+namespace {
+
+struct BwdArgs {
+  int N, D, K, B, T, Np, chunk, chunkP, S, C, n_bkg, state_in_smem;
+  const int32_t *rec_rowptr, *rec_post;
+  const float* rec_w;
+  const uint8_t* rec_sid;
+  const int32_t *lgn_rowptr, *lgn_post;
+  const uint8_t* lgn_sid;
+  const int32_t *bkg_inptr, *bkg_inpre;
+  const uint8_t* bkg_insid;
+  const float *decay, *cf, *asc_decay, *basis;
+  float sd[V1G_MAX_RECEPTORS], pinit[V1G_MAX_RECEPTORS], dtsd[V1G_MAX_RECEPTORS];
+  float lr_scale, vd_keep, rec_factor, damp, width, gauss_std;
+  int gauss, hard_reset;
+  // saved forward
+  const float* tape_v;
+  const uint8_t* tape_zr;
+  const int32_t* lgn_off;
+  const uint32_t* lgn_entries;
+  int lgn_nseg;
+  const int32_t* bkg_counts;
+  // loss
+  const float* rate_coef;  // [N] dL/dz contribution of the rate term, or NULL
+  const float* sgrad;      // [B][nbins] dL/d(bin count), or NULL
+  int sync_bin, nbins;
+  float volt_coef;  // voltage_cost * loss_scale / (B*T*N); gradient is 2*volt_coef*(...)
+  const float* v_lo;
+  const float *g_z, *g_v;  // explicit [B,T,N] gradients, nullable
+  // outputs (accumulated)
+  float *dw_rec, *dw_lgn, *dw_bkg;  // CSR order, CSR order, gather-table order
+  float* loss_acc;                  // [4]; [2] += voltage loss
+  // plumbing
+  float* Q;
+  float* state_ws;
+  unsigned long long* barrier;
+  int32_t* status;
+  unsigned long long* counters;
+  long long spin_limit;
+  unsigned long long* phase_ns;
+};
+
+constexpr int NT = 512;
+constexpr int NW = NT / 32;
+
+__device__ __forceinline__ unsigned long long gtime_b() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ float pseudo_h(float vs, const BwdArgs& a) {
+  if (a.gauss) return expf(-(vs * vs) / (a.gauss_std * a.gauss_std)) * a.damp;
+  float x = fabsf(vs);
+  if (a.width != 1.f) x = x / a.width;
+  return a.damp * fmaxf(1.f - x, 0.f);
+}
+
+template <int BP_>
+__device__ __forceinline__ void load_row(const float* p, float (&q)[BP_]) {
+  const float4 a = __ldcg((const float4*)p);
+  q[0] = a.x; q[1] = a.y; q[2] = a.z; q[3] = a.w;
+  if (BP_ == 8) {
+    const float4 b = __ldcg((const float4*)p + 1);
+    q[4] = b.x; q[5] = b.y; q[6] = b.z; q[7] = b.w;
+  }
+}
+
+template <int R_, int BP_, bool PROJ>
+__global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int B = a.B, D = a.D, K = a.K, N = a.N, Np = a.Np, chunkP = a.chunkP, T = a.T, C = a.C;
+  const int n0 = blockIdx.x * a.chunk;
+  const int cn = min(a.chunk, N - n0);
+  const int nb = B * a.n_bkg;
+
+  unsigned char* sp_ = smem_raw;
+  auto take = [&](size_t bytes) {
+    unsigned char* p = sp_;
+    sp_ += (bytes + 15) & ~(size_t)15;
+    return p;
+  };
+  const size_t plane = (size_t)B * chunkP;
+  float* basis_s = (float*)take(sizeof(float) * a.S * R_);
+  float* gz_s = (float*)take(sizeof(float) * plane);   // gathered spike gradient [b][k]
+  float* tv_s = (float*)take(sizeof(float) * plane);   // v(t) of the step [b][k]
+  uint8_t* tz_s = (uint8_t*)take(plane);               // spike / refractory bits of the step
+  uint8_t* need_s = (uint8_t*)take(chunkP);            // row must be walked
+  uint8_t* zmask_s = (uint8_t*)take(chunkP);           // batch rows that spiked at this step
+  int* s_cnt = (int*)take(sizeof(int) * nb);
+  int* s_misc = (int*)take(sizeof(int) * 4);
+  float* base;
+  if (a.state_in_smem)
+    base = (float*)take(sizeof(float) * plane * (3 + 2 * R_));
+  else
+    base = a.state_ws + (size_t)blockIdx.x * plane * (3 + 2 * R_);
+  float* G_v = base;
+  float* G_a0 = G_v + plane;
+  float* G_a1 = G_a0 + plane;
+  float* G_p = G_a1 + plane;       // [r][b][k]
+  float* G_pr = G_p + plane * R_;  // [r][b][k]
+
+  for (int i = tid; i < a.S * R_; i += NT) basis_s[i] = a.basis[i];
+  for (int i = tid; i < (int)plane * (3 + 2 * R_); i += NT) base[i] = 0.f;
+  if (tid < 4) s_misc[tid] = 0;
+  __syncthreads();
+  if (tid == 0) v1g_arrive(v1g_phase_counter(a.barrier, 0));
+
+  const unsigned long long G = gridDim.x;
+  unsigned long long seen = 0;
+  bool ok = true;
+  float volt_loss = 0.f;
+  unsigned long long c_rows = 0, c_events = 0, c_dw = 0;
+  unsigned long long ph_a = 0, ph_b = 0, ph_c = 0;
+  const bool prof = a.phase_ns != nullptr && tid == 0;
+  const unsigned long long ph_start = prof ? gtime_b() : 0;
+  const int gw = blockIdx.x * NW + warp, gnw = gridDim.x * NW;
+
+  // weight gradient of the LGN events of step tt from Q(tt)
+  auto lgn_dw = [&](int tt) {
+    const int seg_per_t = B * a.lgn_nseg;
+    const int e0 = a.lgn_off[(int64_t)tt * seg_per_t], e1 = a.lgn_off[(int64_t)(tt + 1) * seg_per_t];
+    const float* Qs = a.Q + (int64_t)(tt % K) * Np * C * BP_;
+    for (int e = e0 + gw; e < e1; e += gnw) {
+      const uint32_t ent = a.lgn_entries[e];
+      const int b = ent >> 24, u = ent & 0xffffff;
+      const int j0 = a.lgn_rowptr[u], j1 = a.lgn_rowptr[u + 1];
+      for (int j = j0 + lane; j < j1; j += 32) {
+        const int post = a.lgn_post[j], sid = a.lgn_sid[j];
+        float val;
+        if (PROJ) {
+          val = __ldcg(Qs + ((int64_t)post * C + sid) * BP_ + b);
+        } else {
+          val = 0.f;
+#pragma unroll
+          for (int r = 0; r < R_; ++r)
+            val += __ldcg(Qs + ((int64_t)post * C + r) * BP_ + b) * basis_s[sid * R_ + r];
+        }
+        atomicAdd(a.dw_lgn + j, val);
+      }
+      if (lane == 0) c_dw += (unsigned long long)(j1 - j0);
+    }
+  };
+
+  for (int it = 0; it < T && ok; ++it) {
+    const int t = T - 1 - it;
+    const unsigned long long ph0 = prof ? gtime_b() : 0;
+    if (tid == 0 && it >= 2) {
+      // every block must have finished iteration it-3 (phase it-2): Q(t+1 .. t+D) is complete
+      const unsigned long long target = v1g_phase_target(it - 2, G);
+      if (seen < target)
+        seen = v1g_wait(v1g_phase_counter(a.barrier, it - 2), target, a.spin_limit, a.status);
+      if (seen < target) s_misc[1] = 1;
+    }
+    __syncthreads();
+    if (s_misc[1]) {
+      ok = false;
+      break;
+    }
+    if (tid == 0 && it >= 1) v1g_arrive(v1g_phase_counter(a.barrier, it));
+
+    // ---------------- phase A: this step's tape, row flags, counts of step t-2 ----------------
+    for (int k = tid; k < cn; k += NT) {
+      const int n = n0 + k;
+      unsigned zm = 0, need = 0;
+      for (int b = 0; b < B; ++b) {
+        const int64_t ti = ((int64_t)t * B + b) * N + n;
+        const float v = __ldcs(a.tape_v + ti);
+        const unsigned zr = __ldcs(a.tape_zr + ti);
+        tv_s[b * chunkP + k] = v;
+        tz_s[b * chunkP + k] = (uint8_t)zr;
+        zm |= (zr & 1u) << b;
+        if (!(zr & 2u) && pseudo_h(v - 1.f, a) != 0.f) need = 1;
+      }
+      zmask_s[k] = (uint8_t)zm;
+      need_s[k] = (uint8_t)(need | (zm ? 1u : 0u));
+    }
+    if (t >= 2)
+      for (int i = tid; i < nb; i += NT) {
+        const int b = i / a.n_bkg, j = i - b * a.n_bkg;
+        s_cnt[i] = a.bkg_counts[((int64_t)b * T + (t - 2)) * a.n_bkg + j];
+      }
+    __syncthreads();
+    const unsigned long long ph1 = prof ? gtime_b() : 0;
+
+    // ---------------- phase B: gather over the out-synapses of every needed neuron ----------------
+    if (tid == 0) seen = (it >= 1) ? v1g_ld_acquire(v1g_phase_counter(a.barrier, it - 1)) : 0;
+    const int tk = t % K;
+    for (int k = warp; k < cn; k += NW) {
+      if (!need_s[k]) {
+        if (lane < B) gz_s[lane * chunkP + k] = 0.f;
+        continue;
+      }
+      const unsigned zm = zmask_s[k];
+      int rp = 0;
+      if (lane <= D) rp = a.rec_rowptr[(int64_t)(n0 + k) * D + lane];
+      int bound[V1G_MAX_DELAY + 1];
+#pragma unroll
+      for (int d = 0; d <= V1G_MAX_DELAY; ++d) bound[d] = __shfl_sync(0xffffffffu, rp, d <= D ? d : 0);
+      const int j0 = bound[0], j1 = __shfl_sync(0xffffffffu, rp, D);
+      float acc[BP_];
+#pragma unroll
+      for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
+      for (int j = j0 + lane; j < j1; j += 32) {
+        int d = 1;
+#pragma unroll
+        for (int q = 1; q < V1G_MAX_DELAY; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
+        if (t + d >= T) continue;  // no step after the rollout's end
+        int slot = tk + d;
+        if (slot >= K) slot -= K;
+        const int post = a.rec_post[j], sid = a.rec_sid[j];
+        const float w = a.rec_w[j];
+        const float* Qp = a.Q + ((int64_t)slot * Np + post) * C * BP_;
+        float pj[BP_];
+        if (PROJ) {
+          load_row<BP_>(Qp + sid * BP_, pj);
+        } else {
+#pragma unroll
+          for (int b = 0; b < BP_; ++b) pj[b] = 0.f;
+#pragma unroll
+          for (int r = 0; r < R_; ++r) {
+            float q[BP_];
+            load_row<BP_>(Qp + r * BP_, q);
+            const float bs = basis_s[sid * R_ + r];
+#pragma unroll
+            for (int b = 0; b < BP_; ++b) pj[b] += q[b] * bs;
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < BP_; ++b) acc[b] += w * pj[b];
+        if (zm) {
+          float dwv = 0.f;
+#pragma unroll
+          for (int b = 0; b < BP_; ++b)
+            if (zm & (1u << b)) dwv += pj[b];
+          a.dw_rec[j] += dwv;  // this lane is the only writer of synapse j at this step
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < BP_; ++b)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[b] += __shfl_xor_sync(0xffffffffu, acc[b], o);
+      float mine = 0.f;
+#pragma unroll
+      for (int b = 0; b < BP_; ++b)
+        if (lane == b) mine = acc[b];
+      if (lane < B) gz_s[lane * chunkP + k] = mine;
+      if (lane == 0) {
+        c_rows += (unsigned long long)D;
+        c_events += (unsigned long long)(j1 - j0);
+        if (zm) c_dw += (unsigned long long)(j1 - j0) * __popc(zm);
+      }
+    }
+    if (t + 1 < T) lgn_dw(t + 1);
+    __syncthreads();
+    const unsigned long long ph2 = prof ? gtime_b() : 0;
+
+    // ---------------- phase C: dense adjoint, publish Q(t-2), background weight gradient ----------------
+    const int bin = (a.sgrad && a.sync_bin > 0 && t / a.sync_bin < a.nbins) ? t / a.sync_bin : -1;
+    float* Qw = a.Q + (int64_t)((t + K - 2) % K) * Np * C * BP_;
+    for (int k = tid; k < cn; k += NT) {
+      const int n = n0 + k;
+      const float k_decay = a.decay[n], k_cf = a.cf[n];
+      const float k_ad0 = a.asc_decay[2 * n], k_ad1 = a.asc_decay[2 * n + 1];
+      const float rc = a.rate_coef ? a.rate_coef[n] : 0.f;
+      const float vlo = a.v_lo ? a.v_lo[n] : 0.f;
+      const int bj0 = a.bkg_inptr[n], bj1 = a.bkg_inptr[n + 1];
+      for (int b = 0; b < B; ++b) {
+        const int si = b * chunkP + k;
+        const float v = tv_s[si];
+        const unsigned zr = tz_s[si];
+        const bool free_ = !(zr & 2u);
+        const int64_t oi = ((int64_t)b * T + t) * N + n;
+        float gz = rc + (bin >= 0 ? a.sgrad[b * a.nbins + bin] : 0.f) + (a.g_z ? a.g_z[oi] : 0.f);
+        gz += a.rec_factor * gz_s[si];
+        float gv = G_v[si] + (a.g_v ? a.g_v[oi] : 0.f);
+        if (a.volt_coef != 0.f) {
+          const float hi = fmaxf(v - 1.f, 0.f), lo = fmaxf(vlo - v, 0.f);
+          gv += 2.f * a.volt_coef * (hi - lo);
+          volt_loss += hi * hi + lo * lo;
+        }
+        if (free_) gv += gz * pseudo_h(v - 1.f, a);
+        if (a.hard_reset && !free_) gv = 0.f;
+        G_v[si] = k_decay * a.vd_keep * gv;
+        const float gc1 = k_cf * gv;
+        G_a0[si] = k_ad0 * G_a0[si] + gc1;
+        G_a1[si] = k_ad1 * G_a1[si] + gc1;
+        float dyv[R_];
+#pragma unroll
+        for (int r = 0; r < R_; ++r) {
+          const int pi = (r * B + b) * chunkP + k;
+          const float gp = G_p[pi], gpr = G_pr[pi];
+          const float gp1 = a.sd[r] * gp + gc1;                // g_p(t-1)
+          const float gpr1 = a.sd[r] * gpr + a.dtsd[r] * gp;   // g_pr(t-1)
+          G_p[pi] = gp1;
+          G_pr[pi] = gpr1;
+          const float gpr2 = a.sd[r] * gpr1 + a.dtsd[r] * gp1;  // g_pr(t-2)
+          dyv[r] = (gpr2 * a.pinit[r]) * a.lr_scale;
+        }
+        if (t >= 2) {
+          float* qd = Qw + (int64_t)n * C * BP_ + b;
+          if (PROJ) {
+            for (int c = 0; c < C; ++c) {
+              float s = 0.f;
+#pragma unroll
+              for (int r = 0; r < R_; ++r) s += basis_s[c * R_ + r] * dyv[r];
+              __stcg(qd + c * BP_, s);
+            }
+          } else {
+#pragma unroll
+            for (int r = 0; r < R_; ++r) __stcg(qd + r * BP_, dyv[r]);
+          }
+          // background weight gradient of step t-2 (gather-table order, this thread owns j)
+          for (int j = bj0; j < bj1; ++j) {
+            const int cnt = s_cnt[b * a.n_bkg + a.bkg_inpre[j]];
+            if (cnt > 0) {
+              const float* bs = basis_s + (int)a.bkg_insid[j] * R_;
+              float s = 0.f;
+#pragma unroll
+              for (int r = 0; r < R_; ++r) s += dyv[r] * bs[r];
+              a.dw_bkg[j] += s * (float)cnt;
+            }
+          }
+        }
+      }
+    }
+    if (prof) {
+      const unsigned long long ph3 = gtime_b();
+      ph_a += ph1 - ph0;
+      ph_b += ph2 - ph1;
+      ph_c += ph3 - ph2;
+    }
+  }
+  // ---- full barrier, then the LGN events of step 0 (Q(0) was published at step 2) ----
+  __syncthreads();
+  if (tid == 0) {
+    if (ok && T >= 1) v1g_arrive(v1g_phase_counter(a.barrier, T));
+    const unsigned long long target = v1g_phase_target(T, G);
+    if (ok) {
+      seen = v1g_wait(v1g_phase_counter(a.barrier, T), target, a.spin_limit, a.status);
+      if (seen < target) s_misc[1] = 1;
+    }
+  }
+  __syncthreads();
+  ok = ok && !s_misc[1];
+  if (ok && T >= 1) lgn_dw(0);
+
+  if (prof) {
+    unsigned long long* o = a.phase_ns + 4 * blockIdx.x;
+    o[0] = ph_c;  // dense adjoint
+    o[1] = ph_b;  // gather
+    o[2] = ph_a;  // wait + tape
+    o[3] = gtime_b() - ph_start;
+  }
+  // voltage loss and counters
+  for (int o = 16; o > 0; o >>= 1) volt_loss += __shfl_down_sync(0xffffffffu, volt_loss, o);
+  c_rows = v1g_warp_sum(c_rows);
+  c_events = v1g_warp_sum(c_events);
+  c_dw = v1g_warp_sum(c_dw);
+  if (lane == 0) {
+    if (volt_loss != 0.f) atomicAdd(a.loss_acc + 2, volt_loss * a.volt_coef);
+    V1GCounters* c = (V1GCounters*)a.counters;
+    if (c_rows) atomicAdd(&c->bwd_rows, c_rows);
+    if (c_events) atomicAdd(&c->bwd_events, c_events);
+    if (c_dw) atomicAdd(&c->dw_events, c_dw);
+  }
+}
+
+// ---- loss preparation over the saved spikes ------------------------------------------------
+
+// spike_count[n] += spikes of neuron n (all b, t); popcount[t*B + b] = population spikes
+__global__ void __launch_bounds__(256) spike_stats_kernel(const uint8_t* __restrict__ zr, int T,
+                                                          int B, int N, int* __restrict__ spike_count,
+                                                          int* __restrict__ popcount) {
+  const int64_t row = blockIdx.x;  // t*B + b
+  const uint8_t* p = zr + row * N;
+  int cnt = 0;
+  for (int n = threadIdx.x; n < N; n += blockDim.x)
+    if (p[n] & 1) {
+      ++cnt;
+      atomicAdd(spike_count + n, 1);
+    }
+  __shared__ int ws[8];
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_down_sync(0xffffffffu, cnt, o);
+  if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int s = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += ws[w];
+    popcount[row] = s;
+  }
+}
+
+// rate_coef[n] = rate_cost*ls*2*(m_n - target_n)/(N*B*T); loss[1] = rate loss
+__global__ void __launch_bounds__(256) rate_loss_kernel(const int* __restrict__ spike_count,
+                                                        const float* __restrict__ target, int N,
+                                                        float inv_bt, float cost, float* rate_coef,
+                                                        float* loss) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  float l = 0.f;
+  if (n < N) {
+    const float m = (float)spike_count[n] * inv_bt;
+    const float dlt = m - target[n];
+    rate_coef[n] = cost * 2.f * dlt / (float)N * inv_bt;
+    l = dlt * dlt;
+  }
+  __shared__ float ws[8];
+  for (int o = 16; o > 0; o >>= 1) l += __shfl_down_sync(0xffffffffu, l, o);
+  if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = l;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += ws[w];
+    atomicAdd(loss + 1, cost * s / (float)N);
+  }
+}
+
+// Fano-factor loss of the population spike count in bins of `bin` steps (one block).
+// sgrad[b*nbins + k] = dL/d(count of bin k, row b); loss[3] = synchrony loss.
+__global__ void __launch_bounds__(256) sync_loss_kernel(const int* __restrict__ popcount, int T, int B,
+                                                        int bin, int nbins, float cost, float target,
+                                                        float* __restrict__ sgrad, float* loss) {
+  extern __shared__ float sh[];  // counts [B*nbins], then mean[B], var[B], fano[B]
+  float* cnt = sh;
+  float* mean = sh + B * nbins;
+  float* var = mean + B;
+  float* fano = var + B;
+  for (int i = threadIdx.x; i < B * nbins; i += blockDim.x) {
+    const int b = i / nbins, k = i - b * nbins;
+    int s = 0;
+    for (int q = 0; q < bin; ++q) s += popcount[(k * bin + q) * B + b];
+    cnt[i] = (float)s;
+  }
+  __syncthreads();
+  if (threadIdx.x < B) {
+    const int b = threadIdx.x;
+    float m = 0.f;
+    for (int k = 0; k < nbins; ++k) m += cnt[b * nbins + k];
+    m /= (float)nbins;
+    float v = 0.f;
+    for (int k = 0; k < nbins; ++k) {
+      const float d = cnt[b * nbins + k] - m;
+      v += d * d;
+    }
+    v /= (float)nbins;
+    mean[b] = m;
+    var[b] = v;
+    fano[b] = v / fmaxf(m, 1e-7f);
+  }
+  __syncthreads();
+  float fbar = 0.f;
+  for (int b = 0; b < B; ++b) fbar += fano[b];
+  fbar /= (float)B;
+  const float dl_df = cost * 2.f * (fbar - target) / (float)B;
+  for (int i = threadIdx.x; i < B * nbins; i += blockDim.x) {
+    const int b = i / nbins;
+    const float m = mean[b], v = var[b];
+    const float dv = 2.f * (cnt[i] - m) / (float)nbins;
+    float df;
+    if (m > 1e-7f)
+      df = dv / m - v / (m * m) / (float)nbins;
+    else
+      df = dv / 1e-7f;
+    sgrad[i] = dl_df * df;
+  }
+  if (threadIdx.x == 0) atomicAdd(loss + 3, cost * (fbar - target) * (fbar - target));
+}
+
+__global__ void __launch_bounds__(256) permute_add_kernel(const float* __restrict__ src,
+                                                          const int32_t* __restrict__ perm,
+                                                          float* __restrict__ dst, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) dst[perm ? perm[i] : i] += src[i];
+}
+
+__global__ void finish_loss_kernel(float* acc, float* out) {
+  if (threadIdx.x == 0) {
+    acc[0] = acc[1] + acc[2] + acc[3];
+    if (out)
+      for (int i = 0; i < 4; ++i) out[i] = acc[i];
+  }
+}
+
+template <int R_, int BP_, bool PROJ>
+int launch_bwd(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream_t st) {
+  auto kern = rollout_bwd_kernel<R_, BP_, PROJ>;
+  V1G_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int per_sm = 0;
+  V1G_CUDA(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, smem));
+  if (per_sm < 1 || grid > per_sm * h->n_sms)
+    return v1g_fail(h, V1G_ERANGE, "rollout grid of %d blocks cannot be co-resident (%d per SM)", grid, per_sm);
+  void* args[] = {(void*)&a};
+  V1G_CUDA(h, cudaLaunchCooperativeKernel((void*)kern, dim3(grid), dim3(NT), args, smem, st));
+  return V1G_OK;
+}
+
+template <int R_>
+int launch_bwd_r(V1GHandle* h, const BwdArgs& a, int BP, bool proj, int grid, size_t smem,
+                 cudaStream_t st) {
+  if (BP == 4) return proj ? launch_bwd<R_, 4, true>(h, a, grid, smem, st) : launch_bwd<R_, 4, false>(h, a, grid, smem, st);
+  return proj ? launch_bwd<R_, 8, true>(h, a, grid, smem, st) : launch_bwd<R_, 8, false>(h, a, grid, smem, st);
+}
+
+}  // namespace
+
+extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const float* g_z,
+                               const float* g_v, float* d_w_rec, float* d_w_lgn, float* d_w_bkg,
+                               float* loss_out, void* stream) {
+  if (!h) return V1G_EINVAL;
+  if (!h->tape_valid)
+    return v1g_fail(h, V1G_ESTATE, "v1g_rollout_bwd needs a preceding v1g_rollout_fwd with save_for_bwd");
+  cudaStream_t st = (cudaStream_t)stream;
+  const V1GConfig& c = h->cfg;
+  const int N = c.n_neurons, R = c.n_receptors, D = c.max_delay, K = D + 6, S = c.n_syn_types;
+  const int B = h->tape_B, T = h->tape_T;
+  if (R != 4 && R != 5)
+    return v1g_fail(h, V1G_ERANGE, "backward rollout is built for 4 or 5 receptor channels, got %d", R);
+  V1GLossSpec ls;
+  if (loss) ls = *loss; else ls = V1GLossSpec{nullptr, nullptr, 0.f, 0.f, 0.f, 1.f, 50, 1.f};
+  if (ls.rate_cost != 0.f && !ls.rate_target) return v1g_fail(h, V1G_EINVAL, "rate_cost without rate_target");
+  const bool proj = S <= 8;
+  const int C = proj ? S : R;
+  const int BP = B <= 4 ? 4 : 8;
+  const int Np = (N + 31) & ~31;
+  int rc;
+
+  V1GRolloutPlan plan;
+  v1g_plan_rollout(h, B, 3 + 2 * R, 0, 0, &plan);
+  auto al = [](size_t b) { return (b + 15) & ~(size_t)15; };
+  const size_t plane = (size_t)B * plan.chunkP;
+  size_t smem = al(sizeof(float) * S * R) + 2 * al(sizeof(float) * plane) + al(plane) +
+                2 * al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 4);
+  const size_t state_bytes = al(sizeof(float) * plane * (3 + 2 * R));
+  int state_in_smem = 0;
+  if (!h->opt_force_global && smem + state_bytes <= (size_t)h->smem_optin) {
+    state_in_smem = 1;
+    smem += state_bytes;
+  }
+  if (smem > (size_t)h->smem_optin)
+    return v1g_fail(h, V1G_ERANGE, "backward rollout needs %zu B of shared memory per block", smem);
+  if (!state_in_smem)
+    if ((rc = v1g_reserve(h, &h->state_ws, &h->state_ws_cap, (int64_t)(plane * (3 + 2 * R) * plan.grid)))) return rc;
+
+  // scratch: Q ring, CSR-order weight gradients, loss tables
+  const int64_t q_elems = (int64_t)K * Np * C * BP;
+  if ((rc = v1g_reserve(h, &h->dy_ring, &h->dy_ring_cap, q_elems))) return rc;
+  const int nbins = (ls.sync_cost != 0.f && ls.sync_bin > 0) ? T / ls.sync_bin : 0;
+  // loss scratch layout (floats): acc[4] | rate_coef[N] | sgrad[B*nbins] | spike_count[N] (int) | popcount[T*B] (int)
+  const int64_t ls_elems = 4 + (int64_t)N + (int64_t)B * std::max(nbins, 1) + N + (int64_t)T * B;
+  if ((rc = v1g_reserve(h, &h->loss_scratch, &h->loss_scratch_cap, ls_elems))) return rc;
+  float* acc = h->loss_scratch;
+  float* rate_coef = acc + 4;
+  float* sgrad = rate_coef + N;
+  int* spike_count = (int*)(sgrad + (int64_t)B * std::max(nbins, 1));
+  int* popcount = spike_count + N;
+  for (int s = 0; s < V1G_NSRC; ++s) {
+    const int64_t nnz = std::max<int64_t>(h->src[s].nnz, 1);
+    if (!h->dw_csr[s]) V1G_CUDA(h, cudaMalloc((void**)&h->dw_csr[s], (size_t)nnz * sizeof(float)));
+    V1G_CUDA(h, cudaMemsetAsync(h->dw_csr[s], 0, (size_t)nnz * sizeof(float), st));
+  }
+  V1G_CUDA(h, cudaMemsetAsync(h->loss_scratch, 0, (size_t)ls_elems * sizeof(float), st));
+  V1G_CUDA(h, cudaMemsetAsync(h->dy_ring, 0, (size_t)q_elems * sizeof(float), st));
+  V1G_CUDA(h, cudaMemsetAsync(h->barrier, 0, V1G_BARRIER_BYTES, st));
+
+  const bool want_rate = ls.rate_cost != 0.f, want_sync = nbins >= 1;
+  if (want_rate || want_sync) {
+    spike_stats_kernel<<<(unsigned)(T * B), 256, 0, st>>>(h->tape_zr, T, B, N, spike_count, popcount);
+    if (want_rate)
+      rate_loss_kernel<<<(N + 255) / 256, 256, 0, st>>>(spike_count, ls.rate_target, N,
+                                                       1.f / ((float)B * (float)T),
+                                                       ls.rate_cost * ls.loss_scale, rate_coef, acc);
+    if (want_sync)
+      sync_loss_kernel<<<1, 256, sizeof(float) * (B * nbins + 3 * B), st>>>(
+          popcount, T, B, ls.sync_bin, nbins, ls.sync_cost * ls.loss_scale, ls.fano_target, sgrad, acc);
+    V1G_CUDA(h, cudaGetLastError());
+  }
+
+  BwdArgs a;
+  a.N = N; a.D = D; a.K = K; a.B = B; a.T = T; a.Np = Np;
+  a.chunk = plan.chunk; a.chunkP = plan.chunkP; a.S = S; a.C = C; a.n_bkg = c.n_bkg;
+  a.state_in_smem = state_in_smem;
+  const V1GSource& rs = h->src[V1G_SRC_REC];
+  const V1GSource& lsrc = h->src[V1G_SRC_LGN];
+  const V1GSource& bk = h->src[V1G_SRC_BKG];
+  a.rec_rowptr = rs.rowptr; a.rec_post = rs.post; a.rec_w = rs.w; a.rec_sid = rs.sid;
+  a.lgn_rowptr = lsrc.rowptr; a.lgn_post = lsrc.post; a.lgn_sid = lsrc.sid;
+  a.bkg_inptr = bk.in_ptr; a.bkg_inpre = bk.in_pre; a.bkg_insid = bk.in_sid;
+  a.decay = h->decay; a.cf = h->cf; a.asc_decay = h->asc_decay; a.basis = h->basis;
+  for (int r = 0; r < V1G_MAX_RECEPTORS; ++r) {
+    a.sd[r] = r < R ? h->syn_decay[r] : 0.f;
+    a.pinit[r] = r < R ? h->psc_initial[r] : 0.f;
+    a.dtsd[r] = c.dt * a.sd[r];
+  }
+  a.lr_scale = c.lr_scale; a.vd_keep = h->vd_keep; a.rec_factor = h->rec_grad_factor;
+  a.damp = c.dampening_factor; a.width = c.pseudo_width; a.gauss_std = c.gauss_std;
+  a.gauss = (c.flags & V1G_FLAG_PSEUDO_GAUSS) ? 1 : 0;
+  a.hard_reset = (c.flags & V1G_FLAG_HARD_RESET) ? 1 : 0;
+  a.tape_v = h->tape_v; a.tape_zr = h->tape_zr;
+  a.lgn_off = h->lgn_offsets; a.lgn_entries = h->lgn_entries; a.lgn_nseg = h->lgn_nseg;
+  a.bkg_counts = h->tape_counts;
+  a.rate_coef = want_rate ? rate_coef : nullptr;
+  a.sgrad = want_sync ? sgrad : nullptr;
+  a.sync_bin = ls.sync_bin; a.nbins = nbins;
+  a.volt_coef = ls.voltage_cost * ls.loss_scale / ((float)B * (float)T * (float)N);
+  a.v_lo = ls.v_lo;
+  a.g_z = g_z; a.g_v = g_v;
+  a.dw_rec = h->dw_csr[V1G_SRC_REC]; a.dw_lgn = h->dw_csr[V1G_SRC_LGN]; a.dw_bkg = h->dw_csr[V1G_SRC_BKG];
+  a.loss_acc = acc;
+  a.Q = h->dy_ring; a.state_ws = h->state_ws;
+  a.barrier = h->barrier; a.status = h->dev_status; a.counters = h->counters;
+  a.spin_limit = h->opt_spin_limit;
+  a.phase_ns = nullptr;
+  if (h->opt_phase_timers) {
+    if ((rc = v1g_reserve(h, &h->phase_ns, &h->phase_ns_cap, (int64_t)4 * plan.grid))) return rc;
+    V1G_CUDA(h, cudaMemsetAsync(h->phase_ns, 0, sizeof(unsigned long long) * 4 * plan.grid, st));
+    a.phase_ns = h->phase_ns;
+    h->phase_grid = plan.grid;
+  }
+  rc = (R == 4) ? launch_bwd_r<4>(h, a, BP, proj, plan.grid, smem, st)
+                : launch_bwd_r<5>(h, a, BP, proj, plan.grid, smem, st);
+  if (rc) return rc;
+
+  // weight gradients back to the caller's synapse order, accumulated
+  const int blocks = h->n_sms * 8;
+  if (d_w_rec && rs.nnz) permute_add_kernel<<<blocks, 256, 0, st>>>(h->dw_csr[V1G_SRC_REC], rs.perm, d_w_rec, rs.nnz);
+  if (d_w_lgn && lsrc.nnz) permute_add_kernel<<<blocks, 256, 0, st>>>(h->dw_csr[V1G_SRC_LGN], lsrc.perm, d_w_lgn, lsrc.nnz);
+  if (d_w_bkg && bk.nnz) permute_add_kernel<<<blocks, 256, 0, st>>>(h->dw_csr[V1G_SRC_BKG], bk.in_perm, d_w_bkg, bk.nnz);
+  finish_loss_kernel<<<1, 32, 0, st>>>(acc, loss_out);
+  V1G_CUDA(h, cudaGetLastError());
+  return V1G_OK;
 }
