@@ -231,6 +231,15 @@ int v1g_synchronize(V1GHandle* h, void* stream);
  * may spin before giving up).  No counterpart in the reference. */
 int v1g_set_option(V1GHandle* h, const char* name, long long value);
 
+/* Device time in ms of the last forward (which = 0) or backward (which = 1) rollout kernel,
+ * from CUDA events recorded on the launch stream around that kernel alone; blocks until the
+ * kernel has finished.  No counterpart in the reference. */
+int v1g_last_kernel_ms(V1GHandle* h, int which, float* ms);
+
+/* Number of CUDA kernels this library has launched in the process so far (all handles).  No
+ * counterpart in the reference. */
+long long v1g_launch_count(void);
+
 /* With option "phase_timers" = 1 the rollout kernels record, per thread block, the nanoseconds
  * spent in their dense, scatter and barrier phases and in total; this copies up to max_blocks
  * records of 4 values to the host.  A profiling aid with no counterpart in the reference. */

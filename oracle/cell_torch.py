@@ -40,6 +40,9 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+# the backward pass builds COO tensors from indices that are valid by construction
+torch.sparse.check_sparse_tensor_invariants.disable()
+
 
 # --------------------------------------------------------------------------------------
 # spike function and its surrogate gradient

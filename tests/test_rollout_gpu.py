@@ -1,0 +1,238 @@
+"""GPU parity of the fused rollouts (forward and BPTT) against the CPU oracle and the fixtures."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from util import TOL_GRAD, TOL_STATE, make_case, make_inputs, rel_err
+from v1_glif_model_b200 import synth
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+KW = dict(dampening_factor=0.5, pseudo_width=0.5, recurrent_dampening_factor=0.5,
+          voltage_gradient_dampening=0.5)
+LOSS = dict(rate_cost=10.0, voltage_cost=1e-1, sync_cost=0.5, fano_target=1.0, sync_bin=10)
+
+
+def _cells(name, options=(), **kw):
+    from v1_glif_model_b200.models import V1Column
+    dense = kw.pop("dense_basis", False)
+    nrec = kw.pop("n_receptors", None)
+    dtype = kw.pop("dtype", torch.float32)
+    cfg, dicts, orc = make_case(name, dense_basis=dense, n_receptors=nrec, dtype=dtype, **kw)
+    cell = V1Column(*dicts, **kw)
+    for k, v in options:
+        cell.set_option(k, v)
+    return cfg, dicts, orc, cell
+
+
+def _compare_rollout(cfg, orc, cell, x, c):
+    with torch.no_grad():
+        zo, vo, so = orc.rollout(torch.from_numpy(x), torch.from_numpy(c).long())
+    state = cell.zero_state(x.shape[0])
+    z, v = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), state=state)
+    cell.synchronize()
+    # spikes are compared exactly; a borderline threshold crossing that flips under a different
+    # summation order of the currents would show here as a first divergence step
+    diff = (z.cpu().float() != zo).nonzero()
+    assert diff.numel() == 0, f"first spike divergence at (b,t,n)={diff[0].tolist()}"
+    assert rel_err(v, vo) <= TOL_STATE
+    for got, want in zip(state[:6], so[:6]):
+        assert rel_err(got.float(), want.float()) <= TOL_STATE
+    assert torch.equal(state[0].cpu(), so[0])          # z_buf
+    assert torch.equal(state[2].cpu().long(), so[2])   # refractory counters
+    return z, v
+
+
+@pytest.mark.parametrize("name,options,kw", [
+    ("tiny", (), {}),
+    ("small", (), {}),
+    ("small", (("rollout_chunk", 32),), {}),
+    ("small", (("rollout_chunk", 64), ("force_smem_kernel", 1)), {}),
+    ("small", (("rollout_chunk", 96), ("state_in_global", 1)), {}),
+    ("small", (), dict(hard_reset=True)),
+    ("small", (), dict(dense_basis=True)),
+    ("small", (("force_smem_kernel", 1),), dict(dense_basis=True, n_receptors=4)),
+    ("small", (), dict(n_receptors=4)),
+    ("small", (("force_smem_kernel", 1),), dict(n_receptors=3)),
+])
+def test_forward_rollout_matches_oracle(name, options, kw):
+    cfg, dicts, orc, cell = _cells(name, options, **kw)
+    x, c = make_inputs(cfg)
+    _compare_rollout(cfg, orc, cell, x, c)
+    cnt = cell.counters()
+    assert cnt["spikes"] > 0 and cnt["rec_rows"] == cnt["spikes"] * orc.max_delay
+
+
+def test_forward_rollout_c1_free_running():
+    """Configuration 1 (5,000 neurons, batch 1): free-running spike trains agree with the oracle."""
+    cfg, dicts, orc, cell = _cells("C1")
+    x, c = make_inputs(cfg, seq_len=60)
+    _compare_rollout(cfg, orc, cell, x, c)
+
+
+def test_edge_cases_empty_input_and_single_step():
+    cfg, dicts, orc, cell = _cells("tiny")
+    x, c = make_inputs(cfg, seq_len=7)
+    _compare_rollout(cfg, orc, cell, np.zeros_like(x), np.zeros_like(c))   # no events at all
+    for t_len in (1, 2, 3):
+        _compare_rollout(cfg, orc, cell, x[:, :t_len], c[:, :t_len])
+    _compare_rollout(cfg, orc, cell, np.ones_like(x), c)                   # every LGN unit fires
+
+
+@pytest.mark.parametrize("options", [(), (("force_smem_kernel", 1),)])
+def test_chunked_rollout_carries_state(options):
+    """Two chunks with the state carried over equal one rollout (osi_dsi_estimator.py:252-294)."""
+    cfg, dicts, orc, cell = _cells("small", options)
+    x, c = make_inputs(cfg, seq_len=50)
+    xg, cg = torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda()
+    s_one = cell.zero_state(cfg.batch)
+    z1, v1 = cell.rollout(xg, cg, state=s_one)
+    s_two = cell.zero_state(cfg.batch)
+    za, va = cell.rollout(xg[:, :23].contiguous(), cg[:, :23].contiguous(), state=s_two)
+    zb, vb = cell.rollout(xg[:, 23:].contiguous(), cg[:, 23:].contiguous(), state=s_two)
+    cell.synchronize()
+    assert torch.equal(torch.cat([za, zb], 1), z1)
+    assert rel_err(torch.cat([va, vb], 1), v1) <= TOL_STATE
+    for a, b in zip(s_two[:6], s_one[:6]):
+        assert rel_err(a.float(), b.float()) <= TOL_STATE
+
+
+def test_rollout_through_host_buffers():
+    cfg, dicts, orc, cell = _cells("small")
+    x, c = make_inputs(cfg)
+    z_dev, v_dev = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda())
+    z_host, v_host = cell.rollout_host(x, c, want_z=True, want_v=True)
+    assert np.array_equal(z_host, z_dev.cpu().numpy())
+    assert rel_err(v_host, v_dev) <= TOL_STATE
+
+
+def test_golden_fixture_forward_and_gradients():
+    g = np.load(os.path.join(ROOT, "tests", "golden", "tiny_rollout.npz"))
+    cfg, dicts, orc, cell = _cells("tiny", **KW)
+    z, v = cell.rollout(torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["bkg_counts"]).cuda(),
+                        save_for_bwd=True)
+    assert np.array_equal(z.cpu().numpy(), g["z"])
+    assert rel_err(v, g["v"]) <= TOL_STATE
+    tgt = torch.from_numpy(synth.make_rate_targets(cfg)).cuda() / 1000.0
+    vlo = torch.from_numpy((-20.0 / cell.voltage_scale).astype(np.float32)).cuda()
+    dwr, dwl, dwb, losses = cell.backward(dict(LOSS, rate_target=tgt, v_lo=vlo))
+    cell.synchronize()
+    assert abs(float(losses[0]) - float(g["loss"])) <= 1e-5 * abs(float(g["loss"]))
+    assert rel_err(dwr, g["dw_rec"]) <= TOL_GRAD
+    assert rel_err(dwl, g["dw_lgn"]) <= TOL_GRAD
+    assert rel_err(dwb, g["dw_bkg"]) <= TOL_GRAD
+
+
+def _oracle_grads(orc, cfg, x, c, vscale, dtype, g_z=None, g_v=None, loss=LOSS):
+    z, v, _ = orc.rollout(torch.from_numpy(x), torch.from_numpy(c).long())
+    from oracle import losses as OL
+    tgt = (torch.from_numpy(synth.make_rate_targets(cfg)).double() / 1000.0).to(dtype)
+    vlo = torch.from_numpy(-20.0 / vscale).to(dtype)
+    total = OL.rate_loss(z, tgt, loss["rate_cost"]) + OL.voltage_loss(v, vlo, loss["voltage_cost"]) + \
+        OL.sync_loss(z, loss["sync_bin"], loss["sync_cost"], loss["fano_target"])
+    if g_z is not None:
+        total = total + (z * g_z).sum() + (v * g_v).sum()
+    total.backward()
+    return z.detach(), total.item(), [orc.recurrent_weight_values.grad, orc.input_weight_values.grad,
+                                     orc.bkg_input_weights.grad]
+
+
+@pytest.mark.parametrize("name,options,kw", [
+    ("tiny", (), {}),
+    ("small", (), {}),
+    ("small", (("rollout_chunk", 32),), {}),
+    ("small", (("rollout_chunk", 64), ("state_in_global", 1)), {}),
+    ("small", (), dict(dense_basis=True)),
+    ("small", (), dict(n_receptors=4)),
+    ("small", (), dict(pseudo_gauss=True, gauss_std=0.3)),
+    ("small", (), dict(hard_reset=True)),
+])
+def test_bptt_gradients_match_oracle_autograd(name, options, kw):
+    kw = dict(KW, **kw)
+    cfg, dicts, orc, cell = _cells(name, options, **kw)
+    x, c = make_inputs(cfg)
+    zo, lo, go = _oracle_grads(orc, cfg, x, c, cell.voltage_scale, torch.float32)
+    z, _ = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), save_for_bwd=True)
+    assert torch.equal(z.cpu().float(), zo)
+    tgt = torch.from_numpy(synth.make_rate_targets(cfg)).cuda() / 1000.0
+    vlo = torch.from_numpy((-20.0 / cell.voltage_scale).astype(np.float32)).cuda()
+    grads = cell.backward(dict(LOSS, rate_target=tgt, v_lo=vlo))
+    cell.synchronize()
+    assert abs(float(grads[3][0]) - lo) <= 1e-4 * abs(lo)
+    for got, want in zip(grads[:3], go):
+        assert rel_err(got, want) <= TOL_GRAD
+
+
+def test_bptt_with_explicit_output_gradients():
+    """dL/dz and dL/dv supplied as tensors (the general tape.gradient form), no in-kernel loss."""
+    cfg, dicts, orc, cell = _cells("small", **KW)
+    x, c = make_inputs(cfg)
+    g = torch.Generator().manual_seed(11)
+    shape = (cfg.batch, cfg.seq_len, cfg.n_neurons)
+    g_z, g_v = torch.randn(shape, generator=g) * 1e-2, torch.randn(shape, generator=g) * 1e-3
+    zero = dict(rate_cost=0.0, voltage_cost=0.0, sync_cost=0.0, fano_target=1.0, sync_bin=10)
+    zo, lo, go = _oracle_grads(orc, cfg, x, c, cell.voltage_scale, torch.float32, g_z, g_v, loss=zero)
+    cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), return_z=False, return_v=False,
+                 save_for_bwd=True)
+    grads = cell.backward(None, g_z=g_z.cuda(), g_v=g_v.cuda())
+    cell.synchronize()
+    for got, want in zip(grads[:3], go):
+        assert rel_err(got, want) <= TOL_GRAD
+
+
+def test_backward_without_saved_forward_is_an_error():
+    from v1_glif_model_b200._lib import V1GError
+    cfg, dicts, orc, cell = _cells("tiny")
+    with pytest.raises(V1GError, match="save_for_bwd"):
+        cell.backward(None)
+
+
+def test_training_step_updates_weights_with_sign_constraint():
+    from v1_glif_model_b200.training import Trainer
+    cfg, dicts, orc, cell = _cells("small", **KW)
+    x, c = make_inputs(cfg)
+    tgt = torch.from_numpy(synth.make_rate_targets(cfg)).cuda() / 1000.0
+    vlo = torch.from_numpy((-20.0 / cell.voltage_scale).astype(np.float32)).cuda()
+    tr = Trainer(cell, dict(LOSS, rate_target=tgt, v_lo=vlo), learning_rate=1e-2)
+    w0 = cell.recurrent_weight_values.clone()
+    l0 = tr.step(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda())
+    cell.synchronize()
+    w1 = cell.recurrent_weight_values
+    assert not torch.equal(w0, w1)
+    assert torch.all((w1 >= 0) == cell.recurrent_weight_positive | (w1 == 0))
+    assert torch.isfinite(l0).all()
+
+
+def test_full_size_column_properties():
+    """66,634-neuron column, batch 5: size-independent checks (no oracle at this size)."""
+    from v1_glif_model_b200.models import V1Column
+    cfg = synth.CONFIGS["C3"]
+    dicts = synth.make_network(cfg, 0)
+    cell = V1Column(*dicts)
+    t_len = 60
+    x = torch.from_numpy(synth.make_lgn_spikes(cfg, cfg.batch, t_len)).cuda()
+    c = torch.from_numpy(synth.make_bkg_counts(cfg, cfg.batch, t_len)).cuda()
+    z, v = cell.rollout(x, c)
+    cell.synchronize()
+    cnt = cell.counters()
+    # event counters are exact integer identities of the spike trains and the connectivity
+    order, splits = cell.pre_ind_table(0)
+    n, d = cfg.n_neurons, cell.max_delay
+    outdeg = torch.from_numpy(np.diff(splits).reshape(d, n).sum(0)).cuda()
+    assert cnt["spikes"] == int(z.sum())
+    assert cnt["rec_events"] == int((z.sum((0, 1)).long() * outdeg).sum())
+    _, lsplits = cell.pre_ind_table(1)
+    ldeg = torch.from_numpy(np.diff(lsplits)).cuda()
+    assert cnt["lgn_rows"] == int(x.sum())
+    assert cnt["lgn_events"] == int((x.sum((0, 1)).long() * ldeg).sum())
+    assert torch.isfinite(v).all()
+    # the two forward kernels agree (summation order of the ring atomics is the only difference)
+    cell.set_option("force_smem_kernel", 1)
+    z2, v2 = cell.rollout(x, c)
+    cell.synchronize()
+    mismatch = float((z2 != z).float().mean())
+    assert mismatch <= 1e-6
+    if mismatch == 0.0:
+        assert rel_err(v2, v) <= TOL_STATE

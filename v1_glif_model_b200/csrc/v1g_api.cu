@@ -18,6 +18,11 @@ int v1g_fail(const V1GHandle* h, int code, const char* fmt, ...) {
 
 static std::string g_create_err;
 
+#include <atomic>
+static std::atomic<long long> g_launches{0};
+void v1g_count_launches(int n) { g_launches += n; }
+extern "C" long long v1g_launch_count(void) { return g_launches.load(); }
+
 extern "C" const char* v1g_version(void) { return "v1g-sm100a-1"; }
 
 extern "C" const char* v1g_last_error(const V1GHandle* h) {
@@ -79,6 +84,7 @@ extern "C" int v1g_create(const V1GConfig* cfg, V1GHandle** out) {
   chk(cudaMalloc((void**)&h->barrier, 8 * 16 * sizeof(unsigned long long)));
   chk(cudaMalloc((void**)&h->dev_status, 4 * sizeof(int32_t)));
   chk(cudaMalloc((void**)&h->counters, sizeof(V1GCounters)));
+  for (int i = 0; i < 4; ++i) chk(cudaEventCreate(&h->ev[i]));
   if (rc == V1G_OK) {
     chk(cudaMemset(h->dev_status, 0, 4 * sizeof(int32_t)));
     chk(cudaMemset(h->counters, 0, sizeof(V1GCounters)));
@@ -138,6 +144,8 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   cudaFree(h->stage_z);
   cudaFree(h->stage_v);
   cudaFree(h->phase_ns);
+  for (int i = 0; i < 4; ++i)
+    if (h->ev[i]) cudaEventDestroy(h->ev[i]);
   delete h;
   return V1G_OK;
 }
@@ -346,7 +354,11 @@ extern "C" int v1g_set_weights(V1GHandle* h, int source, const float* w, void* s
   const int threads = 256;
   const int blocks = (int)std::min<int64_t>((s.nnz + threads - 1) / threads, 148 * 16);
   permute_weights_kernel<<<blocks, threads, 0, st>>>(s.w_ref, s.perm, s.w, s.nnz);
-  if (s.in_perm) permute_weights_kernel<<<blocks, threads, 0, st>>>(s.w_ref, s.in_perm, s.w_in, s.nnz);
+  v1g_count_launches(1);
+  if (s.in_perm) {
+    permute_weights_kernel<<<blocks, threads, 0, st>>>(s.w_ref, s.in_perm, s.w_in, s.nnz);
+    v1g_count_launches(1);
+  }
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;
 }
@@ -370,6 +382,14 @@ extern "C" int v1g_synchronize(V1GHandle* h, void* stream) {
 extern "C" int v1g_get_counters(V1GHandle* h, V1GCounters* out_host) {
   if (!h || !out_host) return V1G_EINVAL;
   V1G_CUDA(h, cudaMemcpy(out_host, h->counters, sizeof(V1GCounters), cudaMemcpyDeviceToHost));
+  return V1G_OK;
+}
+
+extern "C" int v1g_last_kernel_ms(V1GHandle* h, int which, float* ms) {
+  if (!h || !ms || which < 0 || which > 1) return V1G_EINVAL;
+  if (!h->ev_valid[which]) return v1g_fail(h, V1G_ESTATE, "no rollout kernel of that kind has run");
+  V1G_CUDA(h, cudaEventSynchronize(h->ev[2 * which + 1]));
+  V1G_CUDA(h, cudaEventElapsedTime(ms, h->ev[2 * which], h->ev[2 * which + 1]));
   return V1G_OK;
 }
 

@@ -143,6 +143,7 @@ int v1g_compact_count_scan(V1GHandle* h, int kind, const void* x, int n_rows, in
                                                          time_major_T, offsets);
   }
   scan_kernel<<<1, 1024, 0, st>>>(offsets, m, h->d_count);
+  v1g_count_launches(m > 0 ? 2 : 1);
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;
 }
@@ -159,6 +160,7 @@ int v1g_compact_fill(V1GHandle* h, int kind, const void* x, int n_rows, int64_t 
   else
     fill_kernel<uint8_t, V1G_COMPACT_U8_PACKED><<<(unsigned)m, 256, 0, st>>>(
         (const uint8_t*)x, n_rows, n_cols, nseg, time_major_T, offsets, out, cap);
+  v1g_count_launches(1);
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;
 }

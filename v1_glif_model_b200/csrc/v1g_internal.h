@@ -111,9 +111,15 @@ struct V1GHandle {
   unsigned long long* phase_ns = nullptr;
   int64_t phase_ns_cap = 0;
   int phase_grid = 0;
+  // CUDA events bracketing the last forward [0,1] and backward [2,3] rollout kernel
+  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  bool ev_valid[2] = {false, false};
 };
 
 int v1g_fail(const V1GHandle* h, int code, const char* fmt, ...);
+
+// process-wide count of kernel launches made by this library (for the bench's gpu_launches)
+void v1g_count_launches(int n);
 
 #define V1G_CUDA(h, call)                                                              \
   do {                                                                                 \

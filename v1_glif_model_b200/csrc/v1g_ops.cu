@@ -255,6 +255,7 @@ extern "C" int v1g_syn_currents_fwd(V1GHandle* h, int source, const float* x, in
   scatter_fwd_kernel<<<h->n_sms * 4, 256, S * R * sizeof(float), st>>>(
       h->coords, h->d_count, s.rowptr, s.post, s.w, s.sid, h->basis, x, s.n_cols, N, R, S, s.delays,
       s.n_src, source == V1G_SRC_BKG, i_flat);
+  v1g_count_launches(1);
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;
 }
@@ -298,6 +299,7 @@ extern "C" int v1g_step_fwd(V1GHandle* h, int32_t batch, const V1GState* in,
   step_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       make_consts(h), batch, h->decay, h->cf, h->asc_decay, h->asc_amps, h->tref, *in, rec_inputs,
       *out, z_out);
+  v1g_count_launches(1);
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;
 }
@@ -314,6 +316,7 @@ extern "C" int v1g_step_bwd(V1GHandle* h, int32_t batch, const V1GState* g_out, 
   step_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       make_consts(h), batch, h->decay, h->cf, h->asc_decay, *g_out, g_z, g_v_out, new_v, new_r,
       *g_in, g_rec_inputs);
+  v1g_count_launches(1);
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;
 }

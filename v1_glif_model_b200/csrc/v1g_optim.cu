@@ -45,5 +45,6 @@ extern "C" int v1g_expadam_update(float* w, const float* grad, float* m, float* 
   const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
   expadam_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(w, grad, m, v, positive, n, alpha,
                                                            1.f - beta1, 1.f - beta2, eps, grad_scale);
+  v1g_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? V1G_OK : V1G_ECUDA;
 }

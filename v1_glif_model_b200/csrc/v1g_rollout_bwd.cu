@@ -523,7 +523,11 @@ int launch_bwd(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream
   if (per_sm < 1 || grid > per_sm * h->n_sms)
     return v1g_fail(h, V1G_ERANGE, "rollout grid of %d blocks cannot be co-resident (%d per SM)", grid, per_sm);
   void* args[] = {(void*)&a};
+  V1G_CUDA(h, cudaEventRecord(h->ev[2], st));
   V1G_CUDA(h, cudaLaunchCooperativeKernel((void*)kern, dim3(grid), dim3(NT), args, smem, st));
+  V1G_CUDA(h, cudaEventRecord(h->ev[3], st));
+  h->ev_valid[1] = true;
+  v1g_count_launches(1);
   return V1G_OK;
 }
 
@@ -598,6 +602,7 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   const bool want_rate = ls.rate_cost != 0.f, want_sync = nbins >= 1;
   if (want_rate || want_sync) {
     spike_stats_kernel<<<(unsigned)(T * B), 256, 0, st>>>(h->tape_zr, T, B, N, spike_count, popcount);
+    v1g_count_launches(1 + (want_rate ? 1 : 0) + (want_sync ? 1 : 0));
     if (want_rate)
       rate_loss_kernel<<<(N + 255) / 256, 256, 0, st>>>(spike_count, ls.rate_target, N,
                                                        1.f / ((float)B * (float)T),
@@ -659,6 +664,7 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   if (d_w_lgn && lsrc.nnz) permute_add_kernel<<<blocks, 256, 0, st>>>(h->dw_csr[V1G_SRC_LGN], lsrc.perm, d_w_lgn, lsrc.nnz);
   if (d_w_bkg && bk.nnz) permute_add_kernel<<<blocks, 256, 0, st>>>(h->dw_csr[V1G_SRC_BKG], bk.in_perm, d_w_bkg, bk.nnz);
   finish_loss_kernel<<<1, 32, 0, st>>>(acc, loss_out);
+  v1g_count_launches(1 + ((d_w_rec && rs.nnz) ? 1 : 0) + ((d_w_lgn && lsrc.nnz) ? 1 : 0) + ((d_w_bkg && bk.nnz) ? 1 : 0));
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;
 }

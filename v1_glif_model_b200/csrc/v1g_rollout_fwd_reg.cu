@@ -348,7 +348,11 @@ int launch(V1GHandle* h, const FwdArgs& a, int grid, size_t smem, cudaStream_t s
   if (per_sm < 1 || grid > per_sm * h->n_sms)
     return v1g_fail(h, V1G_ERANGE, "rollout grid of %d blocks cannot be co-resident (%d per SM)", grid, per_sm);
   void* args[] = {(void*)&a};
+  V1G_CUDA(h, cudaEventRecord(h->ev[0], st));
   V1G_CUDA(h, cudaLaunchCooperativeKernel((void*)kern, dim3(grid), dim3(NT), args, smem, st));
+  V1G_CUDA(h, cudaEventRecord(h->ev[1], st));
+  h->ev_valid[0] = true;
+  v1g_count_launches(1);
   return V1G_OK;
 }
 

@@ -204,6 +204,12 @@ class V1Column:
         self._check(self._lib.v1g_get_counters(self._libh, C.byref(c)))
         return {n: int(getattr(c, n)) for n, _ in c._fields_}
 
+    def last_kernel_ms(self, which):
+        """Device milliseconds of the last forward (0) or backward (1) rollout kernel alone."""
+        ms = C.c_float(0.0)
+        self._check(self._lib.v1g_last_kernel_ms(self._libh, which, C.byref(ms)))
+        return ms.value
+
     def phase_times(self):
         """Per-block (dense, scatter, barrier, total) nanoseconds of the last rollout kernel
         (needs ``set_option('phase_timers', 1)``)."""

@@ -51,22 +51,22 @@ class SynthConfig:
     bkg_rate_hz: float = 250.0
     # multipliers found by calibration so that the mean V1 rate lands in the regime the
     # configuration asks for; the bench prints the rate it actually measured
-    bkg_weight_pa: float = 30.0
-    lgn_weight_pa: float = 6.0
+    bkg_weight_pa: float = 11.6
+    lgn_weight_pa: float = 2.0
 
 
 CONFIGS = {
     # CPU-runnable small net, forward only
-    "C1": SynthConfig("C1", 5000, 0, 0.80, 200, 2000, 50, batch=1, seq_len=200),
+    "C1": SynthConfig("C1", 5000, 0, 0.80, 200, 2000, 50, batch=1, seq_len=200, bkg_weight_pa=8.5),
     # same net, fwd+bwd
-    "C2": SynthConfig("C2", 5000, 0, 0.80, 200, 2000, 50, batch=2, seq_len=500),
+    "C2": SynthConfig("C2", 5000, 0, 0.80, 200, 2000, 50, batch=2, seq_len=500, bkg_weight_pa=8.5),
     # full-size column forward
     "C3": SynthConfig("C3", 66634, 17, 0.85, 120, 17400, 30, batch=5, seq_len=2500),
     # full-size column training step (per-GPU batch)
     "C4": SynthConfig("C4", 66634, 17, 0.85, 120, 17400, 30, batch=5, seq_len=500),
     # scaling stress, high activity
     "C5": SynthConfig("C5", 230924, 17, 0.85, 150, 17400, 30, batch=4, seq_len=300,
-                      bkg_weight_pa=40.0),
+                      bkg_weight_pa=14.0, lgn_weight_pa=2.5),
     # tiny nets for unit tests / golden fixtures
     "tiny": SynthConfig("tiny", 48, 3, 0.75, 6, 12, 3, n_bkg=5, bkg_in_degree=2, batch=2,
                         seq_len=40, bkg_weight_pa=60.0, lgn_weight_pa=40.0),

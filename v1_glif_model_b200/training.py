@@ -1,0 +1,109 @@
+"""Data-parallel training step around the fused rollouts.
+
+Mirrors the reference's ``train_step_combined`` (``multi_training.py:483-560``): one forward
+rollout, BPTT, a sum of the dense fp32 weight gradients over replicas, then an
+``ExponentiatedAdam`` step (``v1_model_utils/optimizers.py:353-376``) followed by the sign
+constraint (``models.py:419-427``) and a refresh of the kernels' weight copies
+(``models.py:966-976``).  The reference reduces gradients inside
+``optimizer.apply_gradients`` under ``MirroredStrategy`` with ``HierarchicalCopyAllReduce``
+(``tf_utils.py:131-139``); here every rank is one process with one GPU and the three gradients
+live in ONE flat buffer that is all-reduced in place with a single NCCL call.  Losses are
+pre-scaled by ``1/world_size`` as in ``multi_training.py:427-429``, so the reduction is a sum.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+class FlatGradients:
+    """One flat fp32 buffer holding the gradients of several weight vectors back to back.
+
+    ``views[i]`` aliases the slice of weight vector ``i``; ``all_reduce`` sums the whole buffer
+    over the process group in one collective (a no-op for a single process).
+    """
+
+    def __init__(self, sizes, device):
+        self.sizes = [int(s) for s in sizes]
+        self.flat = torch.zeros(sum(self.sizes), dtype=torch.float32, device=device)
+        self.views = []
+        off = 0
+        for s in self.sizes:
+            self.views.append(self.flat[off:off + s])
+            off += s
+
+    def zero_(self):
+        self.flat.zero_()
+
+    def all_reduce(self, group=None):
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group)
+        return self.flat
+
+
+class ExponentiatedAdam:
+    """Exponentiated-gradient Adam on flat fp32 weights (``optimizers.py:353-376``).
+
+    ``m += (g - m)(1 - b1)``, ``v += (g^2 - v)(1 - b2)``,
+    ``alpha = lr * sqrt(1 - b2^t) / (1 - b1^t)``,
+    ``w <- w * exp(-alpha * m / (sqrt(v) + eps) * sign(w))`` with ``sign(0) = +1``, then the sign
+    constraint ``where(positive, relu(w), -relu(-w))``.  The arithmetic runs in one CUDA kernel of
+    ``libv1g.so``.
+    """
+
+    def __init__(self, params, positives, learning_rate=1e-3, beta_1=0.9, beta_2=0.999,
+                 epsilon=1e-11):
+        self.params = list(params)
+        self.positives = [p.to(torch.uint8).contiguous() for p in positives]
+        self.lr, self.b1, self.b2, self.eps = learning_rate, beta_1, beta_2, epsilon
+        self.m = [torch.zeros_like(p) for p in self.params]
+        self.v = [torch.zeros_like(p) for p in self.params]
+        self.iterations = 0
+
+    def apply_gradients(self, grads, grad_scale=1.0):
+        lib = _lib.load()
+        self.iterations += 1
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for p, g, m, v, pos in zip(self.params, grads, self.m, self.v, self.positives):
+            if not p.is_cuda:
+                raise RuntimeError("ExponentiatedAdam runs on the GPU only")
+            rc = lib.v1g_expadam_update(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(),
+                                        pos.data_ptr(), p.numel(), self.lr, self.b1, self.b2,
+                                        self.eps, self.iterations, grad_scale, stream)
+            if rc != _lib.OK:
+                raise _lib.V1GError(rc, "v1g_expadam_update failed")
+
+
+class Trainer:
+    """One replica of the data-parallel training loop (batch sharded over ranks)."""
+
+    def __init__(self, cell, loss, learning_rate=1e-3, train_input=True, train_noise=False,
+                 group=None):
+        self.cell = cell
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.loss = dict(loss)
+        self.loss["loss_scale"] = self.loss.get("loss_scale", 1.0) / self.world
+        weights = [cell.recurrent_weight_values, cell.input_weight_values, cell.bkg_input_weights]
+        positives = [cell.recurrent_weight_positive, cell.input_weight_positive,
+                     cell.bkg_input_weight_positive]
+        self.trainable = [True, bool(train_input), bool(train_noise)]
+        self.grads = FlatGradients([w.numel() for w in weights], cell.device)
+        sel = [i for i, t in enumerate(self.trainable) if t]
+        self.opt = ExponentiatedAdam([weights[i] for i in sel], [positives[i] for i in sel],
+                                     learning_rate=learning_rate)
+        self._sel = sel
+
+    def step(self, x, bkg_counts):
+        """Forward rollout, BPTT, gradient all-reduce, Exp-Adam update.  Returns losses[4]."""
+        self.grads.zero_()
+        self.cell.rollout(x, bkg_counts, return_z=False, return_v=False, save_for_bwd=True)
+        _, _, _, losses = self.cell.backward(self.loss, accumulate_into=self.grads.views)
+        self.grads.all_reduce(self.group)
+        self.opt.apply_gradients([self.grads.views[i] for i in self._sel])
+        self.cell.refresh_weights()
+        return losses
