@@ -279,7 +279,7 @@ def run_ours(args):
     bb = bwd_bytes_per_launch(cnt, n, r, b, t_len, nnz_rec)
     fb = fwd_bytes_per_launch(cnt, n, r, b, t_len)
     bwd_s, fwd_s = float(np.mean(bwd_ms)) * 1e-3, float(np.mean(fwd_ms)) * 1e-3
-    traffic = load_traffic()
+    traffic = load_traffic(t_len)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -363,7 +363,7 @@ def forward_only(cell, lib, dev, args):
                          "achieved": fb / (kms[0] * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": fb / (kms[0] * 1e-3) / 1e9 / peak, "kernel_ms": kms[0],
                          "algorithmic_bytes_per_launch": fb,
-                         "traffic": load_traffic().get("rollout_fwd_reg_kernel_c3")},
+                         "traffic": load_traffic(t_len).get("rollout_fwd_reg_kernel")},
             "mean_rate_hz": cnt["spikes"] / ns * 1000.0}
 
 
@@ -378,11 +378,14 @@ def cpu_baseline(cfg, dicts, args):
                       f"N={cfg.n_neurons}, torch CPU restatement of the reference cell (oracle/)"}
 
 
-def load_traffic():
+def load_traffic(t_len=1):
+    """DRAM bytes per launch from the committed ncu captures (measured per simulated step on a
+    T=100 case; the kernels' traffic is proportional to T)."""
     path = os.path.join(ROOT, "profiles", "dram_traffic.json")
     if os.path.exists(path):
         with open(path) as f:
-            return json.load(f)
+            per_step = json.load(f).get("per_step_bytes", {})
+        return {k: v * t_len for k, v in per_step.items()}
     return {}
 
 
