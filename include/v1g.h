@@ -158,6 +158,23 @@ int v1g_set_weights(V1GHandle* h, int source, const float* w, void* stream);
 int v1g_compact_spikes(V1GHandle* h, const float* x, int32_t n_rows, int64_t n_cols,
                        int64_t* coords, int64_t cap, int32_t* count, void* stream);
 
+/* Same result as v1g_compact_spikes, for callers that may not allocate device memory.  It has no
+ * counterpart in the reference.  Who needs it: code that runs as an op inside TensorFlow or
+ * PyTorch (device memory there has to come from the framework's allocator; a cudaMalloc made
+ * behind its back is not accounted for and blocks all streams of the GPU while it runs) and
+ * programs that work inside a memory budget fixed at start-up.  This entry point takes no handle
+ * and calls no cudaMalloc, cudaFree or other allocating routine; its working counters live in a
+ * fixed array inside the library (256 KiB on every GPU that loads the library, held until exit).
+ * Limit: n_rows * ceil(n_cols / 4096) <= 65536, i.e. up to 268 M input elements; larger inputs are
+ * refused with V1G_ERANGE and a message from v1g_last_error(NULL).
+ * The first call on each device looks up the array's device address; make that call with the
+ * device current and before any stream capture is begun on it.  All calls share the one array:
+ * calls that can overlap on the GPU (different streams or threads) race and must be serialised by
+ * the caller.  Nothing has to be cleared between calls.  x, coords and count are device pointers
+ * as for v1g_compact_spikes; count may be NULL. */
+int v1g_compact_spikes_noalloc(const float* x, int32_t n_rows, int64_t n_cols, int64_t* coords,
+                               int64_t cap, int32_t* count, void* stream);
+
 /* calculate_synaptic_currents forward (models.py:103-169), calculate_input_current_from_spikes
  * (models.py:814-863) and calculate_noise_current with given counts (models.py:890-940).
  * x[B, n_source_cols] float32: spikes (REC, LGN) or Poisson counts as floats (BKG).

@@ -54,6 +54,7 @@ SIGNATURES = {
     "v1g_set_neuron_params": (C.c_int, [_P] * 9),
     "v1g_set_weights": (C.c_int, [_P, C.c_int, _P, _P]),
     "v1g_compact_spikes": (C.c_int, [_P, _P, C.c_int32, C.c_int64, _P, C.c_int64, _P, _P]),
+    "v1g_compact_spikes_noalloc": (C.c_int, [_P, C.c_int32, C.c_int64, _P, C.c_int64, _P, _P]),
     "v1g_syn_currents_fwd": (C.c_int, [_P, C.c_int, _P, C.c_int32, _P, _P]),
     "v1g_syn_currents_bwd": (C.c_int, [_P, C.c_int, _P, _P, C.c_int32, _P, _P, _P]),
     "v1g_step_fwd": (C.c_int, [_P, C.c_int32, C.POINTER(V1GState), _P, C.POINTER(V1GState), _P, _P]),

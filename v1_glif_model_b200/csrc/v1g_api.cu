@@ -21,6 +21,7 @@ static std::string g_create_err;
 #include <atomic>
 static std::atomic<long long> g_launches{0};
 void v1g_count_launches(int n) { g_launches += n; }
+void v1g_set_global_error(const char* msg) { g_create_err = msg ? msg : ""; }
 extern "C" long long v1g_launch_count(void) { return g_launches.load(); }
 
 extern "C" const char* v1g_version(void) { return "v1g-sm100a-1"; }

@@ -184,3 +184,74 @@ extern "C" int v1g_compact_spikes(V1GHandle* h, const float* x, int32_t n_rows, 
     V1G_CUDA(h, cudaMemcpyAsync(count, h->d_count, sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
   return V1G_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Compaction without any allocation
+// ------------------------------------------------------------------------------------------
+// v1g_compact_spikes keeps its per-segment counters in a buffer that the handle obtains from
+// cudaMalloc.  Some hosts of this code must not do that: an op kernel inside TensorFlow or
+// PyTorch is expected to take all device memory from the framework's own allocator (a raw
+// cudaMalloc escapes its accounting and stalls every stream of the device while it runs), and a
+// caller that only holds a fixed memory budget handed to it at start-up has nothing to allocate
+// from.  For them the counters live in the fixed array below, which is part of the library image:
+// every GPU on which the library is loaded sets aside 256 KiB for it until the process exits.
+#define V1G_NOALLOC_MAX_SEGMENTS 65536
+static __device__ __align__(256) int32_t g_noalloc_counters[V1G_NOALLOC_MAX_SEGMENTS + 2];
+
+// In host code the name above is only a handle for the runtime, not something a kernel can be
+// given; the device address is looked up once per device and remembered here.
+#define V1G_NOALLOC_MAX_DEVICES 64
+static int32_t* g_noalloc_counters_dev[V1G_NOALLOC_MAX_DEVICES];
+
+extern "C" int v1g_compact_spikes_noalloc(const float* x, int32_t n_rows, int64_t n_cols,
+                                          int64_t* coords, int64_t cap, int32_t* count,
+                                          void* stream) {
+  if (n_rows < 0 || n_cols < 0 || cap < 0 || (!x && (int64_t)n_rows * n_cols > 0) ||
+      (!coords && cap > 0)) {
+    v1g_set_global_error("v1g_compact_spikes_noalloc: bad argument");
+    return V1G_EINVAL;
+  }
+  const int64_t nseg = (n_cols + V1G_SEG - 1) / V1G_SEG;
+  const int64_t m = (int64_t)n_rows * nseg;
+  if (m > V1G_NOALLOC_MAX_SEGMENTS) {
+    char msg[200];
+    snprintf(msg, sizeof(msg),
+             "v1g_compact_spikes_noalloc: %lld segments of %d columns exceed the fixed scratch of "
+             "%d segments (n_rows * ceil(n_cols / %d) must stay within it)",
+             (long long)m, V1G_SEG, V1G_NOALLOC_MAX_SEGMENTS, V1G_SEG);
+    v1g_set_global_error(msg);
+    return V1G_ERANGE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= V1G_NOALLOC_MAX_DEVICES) {
+    v1g_set_global_error("v1g_compact_spikes_noalloc: no usable current CUDA device");
+    return V1G_ECUDA;
+  }
+  if (!g_noalloc_counters_dev[dev]) {
+    // first call on this device (it is the current one): resolve the array's device address
+    int32_t* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_counters);
+    if (e != cudaSuccess || !p) {
+      v1g_set_global_error(cudaGetErrorString(e));
+      return V1G_ECUDA;
+    }
+    g_noalloc_counters_dev[dev] = p;
+  }
+  int32_t* counters = g_noalloc_counters_dev[dev];
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nseg_i = (int)nseg;
+  // every counter the later passes read is written by the count pass of this same call, so the
+  // values left by the previous call never need clearing
+  if (m > 0)
+    count_kernel<float><<<(unsigned)m, 256, 0, st>>>(x, n_rows, n_cols, nseg_i, 0, counters);
+  scan_kernel<<<1, 1024, 0, st>>>(counters, m, count);
+  if (m > 0)
+    fill_kernel<float, V1G_COMPACT_F32_COORDS><<<(unsigned)m, 256, 0, st>>>(
+        x, n_rows, n_cols, nseg_i, 0, counters, coords, cap);
+  v1g_count_launches(m > 0 ? 3 : 1);
+  if (cudaGetLastError() != cudaSuccess) {
+    v1g_set_global_error("v1g_compact_spikes_noalloc: kernel launch failed");
+    return V1G_ECUDA;
+  }
+  return V1G_OK;
+}

@@ -121,6 +121,9 @@ int v1g_fail(const V1GHandle* h, int code, const char* fmt, ...);
 // process-wide count of kernel launches made by this library (for the bench's gpu_launches)
 void v1g_count_launches(int n);
 
+// message returned by v1g_last_error(NULL), for entry points that take no handle
+void v1g_set_global_error(const char* msg);
+
 #define V1G_CUDA(h, call)                                                              \
   do {                                                                                 \
     cudaError_t e_ = (call);                                                           \
