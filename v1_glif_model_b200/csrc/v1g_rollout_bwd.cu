@@ -32,7 +32,7 @@
 namespace {
 
 struct BwdArgs {
-  int N, D, K, B, T, Np, chunk, chunkP, S, C, n_bkg, state_in_smem;
+  int N, D, K, B, T, Np, chunk, chunkP, S, C, n_bkg, state_in_smem, bkg_in_smem, bkg_cap;
   const int32_t *rec_rowptr, *rec_post;
   const float* rec_w;
   const uint8_t* rec_sid;
@@ -43,7 +43,7 @@ struct BwdArgs {
   const float *decay, *cf, *asc_decay, *basis;
   float sd[V1G_MAX_RECEPTORS], pinit[V1G_MAX_RECEPTORS], dtsd[V1G_MAX_RECEPTORS];
   float lr_scale, vd_keep, rec_factor, damp, width, gauss_std;
-  int gauss, hard_reset;
+  int gauss, hard_reset, csr_evict_first;
   // saved forward
   const float* tape_v;
   const uint8_t* tape_zr;
@@ -97,11 +97,13 @@ __device__ __forceinline__ void load_row(const float* p, float (&q)[BP_]) {
   }
 }
 
-template <int R_, int BP_, bool PROJ>
+template <int R_, int BP_, bool PROJ, int DT>
 __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int B = a.B, D = a.D, K = a.K, N = a.N, Np = a.Np, chunkP = a.chunkP, T = a.T, C = a.C;
+  const int B = a.B, K = a.K, N = a.N, Np = a.Np, chunkP = a.chunkP, T = a.T, C = a.C;
+  const int D = DT > 0 ? DT : a.D;  // delay buckets; a compile-time constant in the common case
+  constexpr int DMAX = DT > 0 ? DT : V1G_MAX_DELAY;
   const int n0 = blockIdx.x * a.chunk;
   const int cn = min(a.chunk, N - n0);
   const int nb = B * a.n_bkg;
@@ -120,7 +122,26 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   uint8_t* need_s = (uint8_t*)take(chunkP);            // row must be walked
   uint8_t* zmask_s = (uint8_t*)take(chunkP);           // batch rows that spiked at this step
   int* s_cnt = (int*)take(sizeof(int) * nb);
-  int* s_misc = (int*)take(sizeof(int) * 4);
+  int* s_misc = (int*)take(sizeof(int) * 4);  // [1] abort flag, [2] rows queued, [3] next queue slot
+  uint16_t* rowq_s = (uint16_t*)take(sizeof(uint16_t) * chunkP);  // rows to walk this step
+  int32_t* rp_s = (int32_t*)take(sizeof(int32_t) * ((size_t)chunkP * D + 1));  // row pointers of the slice
+  float* c_decay = (float*)take(sizeof(float) * chunkP);  // per-neuron constants of the slice
+  float* c_cf = (float*)take(sizeof(float) * chunkP);
+  float* c_ad0 = (float*)take(sizeof(float) * chunkP);
+  float* c_ad1 = (float*)take(sizeof(float) * chunkP);
+  float* c_rc = (float*)take(sizeof(float) * chunkP);
+  float* c_vlo = (float*)take(sizeof(float) * chunkP);
+  int* bkptr_s = (int*)take(sizeof(int) * (chunkP + 1));  // background in-synapse ranges, slice-relative
+  // background in-synapses of the slice and their weight-gradient accumulators; on chip when they
+  // fit, otherwise the global tables are used directly
+  int* bk_pre_s = nullptr;
+  uint8_t* bk_sid_s = nullptr;
+  float* bk_dw_s = nullptr;
+  if (a.bkg_in_smem) {
+    bk_pre_s = (int*)take(sizeof(int) * a.bkg_cap);
+    bk_dw_s = (float*)take(sizeof(float) * a.bkg_cap);
+    bk_sid_s = (uint8_t*)take(a.bkg_cap);
+  }
   float* base;
   if (a.state_in_smem)
     base = (float*)take(sizeof(float) * plane * (3 + 2 * R_));
@@ -133,6 +154,32 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   float* G_pr = G_p + plane * R_;  // [r][b][k]
 
   for (int i = tid; i < a.S * R_; i += NT) basis_s[i] = a.basis[i];
+  for (int i = tid; i <= cn * D; i += NT) rp_s[i] = a.rec_rowptr[(int64_t)n0 * D + i];
+  for (int k = tid; k < cn; k += NT) {
+    const int n = n0 + k;
+    c_decay[k] = a.decay[n];
+    c_cf[k] = a.cf[n];
+    c_ad0[k] = a.asc_decay[2 * n];
+    c_ad1[k] = a.asc_decay[2 * n + 1];
+    c_rc[k] = a.rate_coef ? a.rate_coef[n] : 0.f;
+    c_vlo[k] = a.v_lo ? a.v_lo[n] : 0.f;
+  }
+  const int bk_base = a.bkg_inptr[n0];
+  const int bk_m = a.bkg_inptr[n0 + cn] - bk_base;
+  for (int k = tid; k <= cn; k += NT) bkptr_s[k] = a.bkg_inptr[n0 + k] - bk_base;
+  const int* bk_pre = a.bkg_inpre + bk_base;
+  const uint8_t* bk_sid = a.bkg_insid + bk_base;
+  float* bk_dw = a.dw_bkg + bk_base;
+  if (a.bkg_in_smem) {
+    for (int j = tid; j < bk_m; j += NT) {
+      bk_pre_s[j] = bk_pre[j];
+      bk_sid_s[j] = bk_sid[j];
+      bk_dw_s[j] = 0.f;
+    }
+    bk_pre = bk_pre_s;
+    bk_sid = bk_sid_s;
+    bk_dw = bk_dw_s;
+  }
   for (int i = tid; i < (int)plane * (3 + 2 * R_); i += NT) base[i] = 0.f;
   if (tid < 4) s_misc[tid] = 0;
   __syncthreads();
@@ -184,6 +231,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         seen = v1g_wait(v1g_phase_counter(a.barrier, it - 2), target, a.spin_limit, a.status);
       if (seen < target) s_misc[1] = 1;
     }
+    if (tid == 0) {
+      s_misc[2] = 0;  // row queue of this step
+      s_misc[3] = 0;
+    }
     __syncthreads();
     if (s_misc[1]) {
       ok = false;
@@ -194,18 +245,35 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     // ---------------- phase A: this step's tape, row flags, counts of step t-2 ----------------
     for (int k = tid; k < cn; k += NT) {
       const int n = n0 + k;
+      // all tape loads of the neuron are issued before any of them is used
+      float vv[BP_];
+      unsigned zz[BP_];
+#pragma unroll
+      for (int b = 0; b < BP_; ++b) {
+        vv[b] = 0.f;
+        zz[b] = 2u;
+        if (b < B) {
+          const int64_t ti = ((int64_t)t * B + b) * N + n;
+          vv[b] = __ldcs(a.tape_v + ti);
+          zz[b] = __ldcs(a.tape_zr + ti);
+        }
+      }
       unsigned zm = 0, need = 0;
-      for (int b = 0; b < B; ++b) {
-        const int64_t ti = ((int64_t)t * B + b) * N + n;
-        const float v = __ldcs(a.tape_v + ti);
-        const unsigned zr = __ldcs(a.tape_zr + ti);
-        tv_s[b * chunkP + k] = v;
-        tz_s[b * chunkP + k] = (uint8_t)zr;
-        zm |= (zr & 1u) << b;
-        if (!(zr & 2u) && pseudo_h(v - 1.f, a) != 0.f) need = 1;
+#pragma unroll
+      for (int b = 0; b < BP_; ++b) {
+        if (b < B) {
+          tv_s[b * chunkP + k] = vv[b];
+          tz_s[b * chunkP + k] = (uint8_t)zz[b];
+          zm |= (zz[b] & 1u) << b;
+          if (!(zz[b] & 2u) && pseudo_h(vv[b] - 1.f, a) != 0.f) need = 1;
+        }
       }
       zmask_s[k] = (uint8_t)zm;
       need_s[k] = (uint8_t)(need | (zm ? 1u : 0u));
+      if (need | zm)
+        rowq_s[atomicAdd(&s_misc[2], 1)] = (uint16_t)k;  // queue the row (order is irrelevant)
+      else
+        for (int b = 0; b < B; ++b) gz_s[b * chunkP + k] = 0.f;  // row is not walked
     }
     if (t >= 2)
       for (int i = tid; i < nb; i += NT) {
@@ -218,65 +286,132 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     // ---------------- phase B: gather over the out-synapses of every needed neuron ----------------
     if (tid == 0) seen = (it >= 1) ? v1g_ld_acquire(v1g_phase_counter(a.barrier, it - 1)) : 0;
     const int tk = t % K;
-    for (int k = warp; k < cn; k += NW) {
-      if (!need_s[k]) {
-        if (lane < B) gz_s[lane * chunkP + k] = 0.f;
-        continue;
-      }
-      const unsigned zm = zmask_s[k];
-      int rp = 0;
-      if (lane <= D) rp = a.rec_rowptr[(int64_t)(n0 + k) * D + lane];
-      int bound[V1G_MAX_DELAY + 1];
+    constexpr int U = PROJ ? 4 : 1;  // row iterations (32 synapses each) kept in flight per warp
+    // one pass = U*32 consecutive synapses of a row, lane l holding synapses jb + u*32 + l
+    auto load_pass = [&](int jb, int j1, int (&post)[U], int (&sid)[U], float (&w)[U]) {
 #pragma unroll
-      for (int d = 0; d <= V1G_MAX_DELAY; ++d) bound[d] = __shfl_sync(0xffffffffu, rp, d <= D ? d : 0);
-      const int j0 = bound[0], j1 = __shfl_sync(0xffffffffu, rp, D);
+      for (int u = 0; u < U; ++u) {
+        const int j = jb + u * 32 + lane;
+        const bool v = j < j1;
+        if (a.csr_evict_first) {
+          post[u] = v ? __ldcs(a.rec_post + j) : 0;
+          sid[u] = v ? (int)__ldcs(a.rec_sid + j) : 0;
+          w[u] = v ? __ldcs(a.rec_w + j) : 0.f;
+        } else {
+          post[u] = v ? a.rec_post[j] : 0;
+          sid[u] = v ? (int)a.rec_sid[j] : 0;
+          w[u] = v ? a.rec_w[j] : 0.f;
+        }
+      }
+    };
+    // warps take rows from the queue one at a time, so a warp that drew long rows takes fewer
+    const int nq = s_misc[2];
+    for (;;) {
+      int qi = 0;
+      if (lane == 0) qi = atomicAdd(&s_misc[3], 1);
+      qi = __shfl_sync(0xffffffffu, qi, 0);
+      if (qi >= nq) break;
+      const int k = rowq_s[qi];
+      int cpost[U], csid[U];
+      float cw[U];
+      load_pass(rp_s[k * D], rp_s[k * D + D], cpost, csid, cw);
+      const unsigned zm = zmask_s[k];
+      const int32_t* rp = rp_s + k * D;
+      int bound[DMAX + 1];
+#pragma unroll
+      for (int d = 0; d <= DMAX; ++d) bound[d] = rp[d <= D ? d : D];
+      const int j0 = bound[0], j1 = rp[D];
       float acc[BP_];
 #pragma unroll
       for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
-      for (int j = j0 + lane; j < j1; j += 32) {
-        int d = 1;
+      for (int jb = j0; jb < j1; jb += 32 * U) {
+        if (jb != j0) load_pass(jb, j1, cpost, csid, cw);  // rows longer than one pass
+        int slot[U];
+        bool valid[U];
 #pragma unroll
-        for (int q = 1; q < V1G_MAX_DELAY; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
-        if (t + d >= T) continue;  // no step after the rollout's end
-        int slot = tk + d;
-        if (slot >= K) slot -= K;
-        const int post = a.rec_post[j], sid = a.rec_sid[j];
-        const float w = a.rec_w[j];
-        const float* Qp = a.Q + ((int64_t)slot * Np + post) * C * BP_;
-        float pj[BP_];
-        if (PROJ) {
-          load_row<BP_>(Qp + sid * BP_, pj);
-        } else {
+        for (int u = 0; u < U; ++u) {
+          const int j = jb + u * 32 + lane;
+          valid[u] = j < j1;
+          int d = 1;
 #pragma unroll
-          for (int b = 0; b < BP_; ++b) pj[b] = 0.f;
+          for (int q = 1; q < DMAX; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
+          if (t + d >= T) valid[u] = false;  // no step after the rollout's end
+          slot[u] = tk + d;
+          if (slot[u] >= K) slot[u] -= K;
+          if (!valid[u]) {
+            slot[u] = tk;
+            cw[u] = 0.f;
+            cpost[u] = 0;
+            csid[u] = 0;
+          }
+        }
+        float pj[U][BP_];
 #pragma unroll
-          for (int r = 0; r < R_; ++r) {
-            float q[BP_];
-            load_row<BP_>(Qp + r * BP_, q);
-            const float bs = basis_s[sid * R_ + r];
+        for (int u = 0; u < U; ++u) {
+          const float* Qp = a.Q + (unsigned)((slot[u] * Np + cpost[u]) * C) * BP_;  // < 2^31, checked by the host
+          if (PROJ) {
+            load_row<BP_>(Qp + csid[u] * BP_, pj[u]);
+          } else {
 #pragma unroll
-            for (int b = 0; b < BP_; ++b) pj[b] += q[b] * bs;
+            for (int b = 0; b < BP_; ++b) pj[u][b] = 0.f;
+#pragma unroll
+            for (int r = 0; r < R_; ++r) {
+              float q[BP_];
+              load_row<BP_>(Qp + r * BP_, q);
+              const float bs = basis_s[csid[u] * R_ + r];
+#pragma unroll
+              for (int b = 0; b < BP_; ++b) pj[u][b] += q[b] * bs;
+            }
           }
         }
 #pragma unroll
-        for (int b = 0; b < BP_; ++b) acc[b] += w * pj[b];
-        if (zm) {
-          float dwv = 0.f;
+        for (int u = 0; u < U; ++u) {
 #pragma unroll
-          for (int b = 0; b < BP_; ++b)
-            if (zm & (1u << b)) dwv += pj[b];
-          a.dw_rec[j] += dwv;  // this lane is the only writer of synapse j at this step
+          for (int b = 0; b < BP_; ++b) acc[b] += cw[u] * pj[u][b];
+          if (zm && valid[u]) {
+            float dwv = 0.f;
+#pragma unroll
+            for (int b = 0; b < BP_; ++b)
+              if (zm & (1u << b)) dwv += pj[u][b];
+            a.dw_rec[jb + u * 32 + lane] += dwv;  // this lane is the only writer of the synapse
+          }
         }
       }
+      // sum the BP_ accumulators over the warp: each exchange halves the values a lane carries
+      // (9 shuffles for 8 accumulators instead of 40); lane l ends with the total of batch row
+      // ((l >> 2) & 1) | ((l >> 3) & 1) << 1 | ((l >> 4) & 1) << 2
+      float a4[4];
+      if (BP_ == 8) {
 #pragma unroll
-      for (int b = 0; b < BP_; ++b)
+        for (int i = 0; i < 4; ++i) {
+          const bool hi = lane & 16;
+          const float recv = __shfl_xor_sync(0xffffffffu, hi ? acc[i] : acc[(i + 4) % BP_], 16);
+          a4[i] = (hi ? acc[(i + 4) % BP_] : acc[i]) + recv;
+        }
+      } else {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc[b] += __shfl_xor_sync(0xffffffffu, acc[b], o);
-      float mine = 0.f;
+        for (int i = 0; i < 4; ++i) a4[i] = acc[i] + __shfl_xor_sync(0xffffffffu, acc[i], 16);
+      }
+      float a2[2];
 #pragma unroll
-      for (int b = 0; b < BP_; ++b)
-        if (lane == b) mine = acc[b];
-      if (lane < B) gz_s[lane * chunkP + k] = mine;
+      for (int i = 0; i < 2; ++i) {
+        const bool hi = lane & 8;
+        const float recv = __shfl_xor_sync(0xffffffffu, hi ? a4[i] : a4[i + 2], 8);
+        a2[i] = (hi ? a4[i + 2] : a4[i]) + recv;
+      }
+      float a1;
+      {
+        const bool hi = lane & 4;
+        const float recv = __shfl_xor_sync(0xffffffffu, hi ? a2[0] : a2[1], 4);
+        a1 = (hi ? a2[1] : a2[0]) + recv;
+      }
+      a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+      a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+      {
+        int bsel = ((lane >> 2) & 1) | (((lane >> 3) & 1) << 1);
+        if (BP_ == 8) bsel |= ((lane >> 4) & 1) << 2;
+        if ((lane & 3) == 0 && (BP_ == 8 || lane < 16) && bsel < B) gz_s[bsel * chunkP + k] = a1;
+      }
       if (lane == 0) {
         c_rows += (unsigned long long)D;
         c_events += (unsigned long long)(j1 - j0);
@@ -292,67 +427,86 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     float* Qw = a.Q + (int64_t)((t + K - 2) % K) * Np * C * BP_;
     for (int k = tid; k < cn; k += NT) {
       const int n = n0 + k;
-      const float k_decay = a.decay[n], k_cf = a.cf[n];
-      const float k_ad0 = a.asc_decay[2 * n], k_ad1 = a.asc_decay[2 * n + 1];
-      const float rc = a.rate_coef ? a.rate_coef[n] : 0.f;
-      const float vlo = a.v_lo ? a.v_lo[n] : 0.f;
-      const int bj0 = a.bkg_inptr[n], bj1 = a.bkg_inptr[n + 1];
-      for (int b = 0; b < B; ++b) {
-        const int si = b * chunkP + k;
-        const float v = tv_s[si];
-        const unsigned zr = tz_s[si];
-        const bool free_ = !(zr & 2u);
-        const int64_t oi = ((int64_t)b * T + t) * N + n;
-        float gz = rc + (bin >= 0 ? a.sgrad[b * a.nbins + bin] : 0.f) + (a.g_z ? a.g_z[oi] : 0.f);
-        gz += a.rec_factor * gz_s[si];
-        float gv = G_v[si] + (a.g_v ? a.g_v[oi] : 0.f);
-        if (a.volt_coef != 0.f) {
-          const float hi = fmaxf(v - 1.f, 0.f), lo = fmaxf(vlo - v, 0.f);
-          gv += 2.f * a.volt_coef * (hi - lo);
-          volt_loss += hi * hi + lo * lo;
-        }
-        if (free_) gv += gz * pseudo_h(v - 1.f, a);
-        if (a.hard_reset && !free_) gv = 0.f;
-        G_v[si] = k_decay * a.vd_keep * gv;
-        const float gc1 = k_cf * gv;
-        G_a0[si] = k_ad0 * G_a0[si] + gc1;
-        G_a1[si] = k_ad1 * G_a1[si] + gc1;
-        float dyv[R_];
+      const float k_decay = c_decay[k], k_cf = c_cf[k], k_ad0 = c_ad0[k], k_ad1 = c_ad1[k];
+      const float rc = c_rc[k], vlo = c_vlo[k];
+      float dyv[BP_][R_];  // dy(t-2) of every batch row of this neuron
 #pragma unroll
-        for (int r = 0; r < R_; ++r) {
-          const int pi = (r * B + b) * chunkP + k;
-          const float gp = G_p[pi], gpr = G_pr[pi];
-          const float gp1 = a.sd[r] * gp + gc1;                // g_p(t-1)
-          const float gpr1 = a.sd[r] * gpr + a.dtsd[r] * gp;   // g_pr(t-1)
-          G_p[pi] = gp1;
-          G_pr[pi] = gpr1;
-          const float gpr2 = a.sd[r] * gpr1 + a.dtsd[r] * gp1;  // g_pr(t-2)
-          dyv[r] = (gpr2 * a.pinit[r]) * a.lr_scale;
-        }
-        if (t >= 2) {
-          float* qd = Qw + (int64_t)n * C * BP_ + b;
-          if (PROJ) {
-            for (int c = 0; c < C; ++c) {
-              float s = 0.f;
+      for (int b = 0; b < BP_; ++b) {
 #pragma unroll
-              for (int r = 0; r < R_; ++r) s += basis_s[c * R_ + r] * dyv[r];
-              __stcg(qd + c * BP_, s);
-            }
-          } else {
-#pragma unroll
-            for (int r = 0; r < R_; ++r) __stcg(qd + r * BP_, dyv[r]);
+        for (int r = 0; r < R_; ++r) dyv[b][r] = 0.f;
+        if (b < B) {
+          const int si = b * chunkP + k;
+          const float v = tv_s[si];
+          const unsigned zr = tz_s[si];
+          const bool free_ = !(zr & 2u);
+          const int64_t oi = ((int64_t)b * T + t) * N + n;
+          float gz = rc + (bin >= 0 ? a.sgrad[b * a.nbins + bin] : 0.f) + (a.g_z ? a.g_z[oi] : 0.f);
+          gz += a.rec_factor * gz_s[si];
+          float gv = G_v[si] + (a.g_v ? a.g_v[oi] : 0.f);
+          if (a.volt_coef != 0.f) {
+            const float hi = fmaxf(v - 1.f, 0.f), lo = fmaxf(vlo - v, 0.f);
+            gv += 2.f * a.volt_coef * (hi - lo);
+            volt_loss += hi * hi + lo * lo;
           }
-          // background weight gradient of step t-2 (gather-table order, this thread owns j)
-          for (int j = bj0; j < bj1; ++j) {
-            const int cnt = s_cnt[b * a.n_bkg + a.bkg_inpre[j]];
-            if (cnt > 0) {
-              const float* bs = basis_s + (int)a.bkg_insid[j] * R_;
-              float s = 0.f;
+          if (free_) gv += gz * pseudo_h(v - 1.f, a);
+          if (a.hard_reset && !free_) gv = 0.f;
+          G_v[si] = k_decay * a.vd_keep * gv;
+          const float gc1 = k_cf * gv;
+          G_a0[si] = k_ad0 * G_a0[si] + gc1;
+          G_a1[si] = k_ad1 * G_a1[si] + gc1;
 #pragma unroll
-              for (int r = 0; r < R_; ++r) s += dyv[r] * bs[r];
-              a.dw_bkg[j] += s * (float)cnt;
+          for (int r = 0; r < R_; ++r) {
+            const int pi = (r * B + b) * chunkP + k;
+            const float gp = G_p[pi], gpr = G_pr[pi];
+            const float gp1 = a.sd[r] * gp + gc1;                // g_p(t-1)
+            const float gpr1 = a.sd[r] * gpr + a.dtsd[r] * gp;   // g_pr(t-1)
+            G_p[pi] = gp1;
+            G_pr[pi] = gpr1;
+            const float gpr2 = a.sd[r] * gpr1 + a.dtsd[r] * gp1;  // g_pr(t-2)
+            dyv[b][r] = (gpr2 * a.pinit[r]) * a.lr_scale;
+          }
+        }
+      }
+      if (t >= 2) {
+        // one 16/32-byte row per channel, all batch rows of the neuron at once
+        float4* qd = (float4*)(Qw + (int64_t)n * C * BP_);
+        for (int c = 0; c < C; ++c) {
+          float row[BP_];
+#pragma unroll
+          for (int b = 0; b < BP_; ++b) {
+            if (PROJ) {
+              float s2 = 0.f;
+#pragma unroll
+              for (int r = 0; r < R_; ++r) s2 += basis_s[c * R_ + r] * dyv[b][r];
+              row[b] = s2;
+            } else {
+              float s2 = 0.f;
+#pragma unroll
+              for (int r = 0; r < R_; ++r) s2 = (r == c) ? dyv[b][r] : s2;
+              row[b] = s2;
             }
           }
+          __stcg(qd + c * (BP_ / 4), make_float4(row[0], row[1], row[2], row[3]));
+          if (BP_ == 8) __stcg(qd + c * 2 + 1, make_float4(row[4 % BP_], row[5 % BP_], row[6 % BP_], row[7 % BP_]));
+        }
+        // background weight gradient of step t-2 for the synapses this thread owns
+        for (int j = bkptr_s[k]; j < bkptr_s[k + 1]; ++j) {
+          const int pre = bk_pre[j];
+          const float* bs = basis_s + (int)bk_sid[j] * R_;
+          float accw = 0.f;
+#pragma unroll
+          for (int b = 0; b < BP_; ++b) {
+            if (b < B) {
+              const int cnt = s_cnt[b * a.n_bkg + pre];
+              if (cnt > 0) {
+                float s2 = 0.f;
+#pragma unroll
+                for (int r = 0; r < R_; ++r) s2 += dyv[b][r] * bs[r];
+                accw += s2 * (float)cnt;
+              }
+            }
+          }
+          if (accw != 0.f) bk_dw[j] += accw;
         }
       }
     }
@@ -376,6 +530,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   __syncthreads();
   ok = ok && !s_misc[1];
   if (ok && T >= 1) lgn_dw(0);
+  if (a.bkg_in_smem)
+    for (int j = tid; j < bk_m; j += NT) a.dw_bkg[bk_base + j] += bk_dw_s[j];
 
   if (prof) {
     unsigned long long* o = a.phase_ns + 4 * blockIdx.x;
@@ -514,9 +670,9 @@ __global__ void finish_loss_kernel(float* acc, float* out) {
   }
 }
 
-template <int R_, int BP_, bool PROJ>
-int launch_bwd(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream_t st) {
-  auto kern = rollout_bwd_kernel<R_, BP_, PROJ>;
+template <int R_, int BP_, bool PROJ, int DT>
+int launch_bwd_d(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream_t st) {
+  auto kern = rollout_bwd_kernel<R_, BP_, PROJ, DT>;
   V1G_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0;
   V1G_CUDA(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, smem));
@@ -529,6 +685,12 @@ int launch_bwd(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream
   h->ev_valid[1] = true;
   v1g_count_launches(1);
   return V1G_OK;
+}
+
+template <int R_, int BP_, bool PROJ>
+int launch_bwd(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream_t st) {
+  if (a.D == 5) return launch_bwd_d<R_, BP_, PROJ, 5>(h, a, grid, smem, st);
+  return launch_bwd_d<R_, BP_, PROJ, 0>(h, a, grid, smem, st);
 }
 
 template <int R_>
@@ -563,15 +725,33 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
 
   V1GRolloutPlan plan;
   v1g_plan_rollout(h, B, 3 + 2 * R, 0, 0, &plan);
+  if (plan.chunkP > 65535) return v1g_fail(h, V1G_ERANGE, "slice of %d neurons per block exceeds 65535", plan.chunkP);
   auto al = [](size_t b) { return (b + 15) & ~(size_t)15; };
   const size_t plane = (size_t)B * plan.chunkP;
   size_t smem = al(sizeof(float) * S * R) + 2 * al(sizeof(float) * plane) + al(plane) +
-                2 * al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 4);
+                2 * al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 4) +
+                al(sizeof(uint16_t) * plan.chunkP) +
+                al(sizeof(int32_t) * ((size_t)plan.chunkP * D + 1)) + 6 * al(sizeof(float) * plan.chunkP) +
+                al(sizeof(int) * (plan.chunkP + 1));
   const size_t state_bytes = al(sizeof(float) * plane * (3 + 2 * R));
   int state_in_smem = 0;
   if (!h->opt_force_global && smem + state_bytes <= (size_t)h->smem_optin) {
     state_in_smem = 1;
     smem += state_bytes;
+  }
+  int bkg_cap = 0;
+  {
+    const V1GSource& bk0 = h->src[V1G_SRC_BKG];
+    for (int g = 0; g < plan.grid; ++g) {
+      const int a0 = g * plan.chunk, a1 = std::min(N, a0 + plan.chunk);
+      bkg_cap = std::max(bkg_cap, bk0.in_ptr_host[a1] - bk0.in_ptr_host[a0]);
+    }
+  }
+  const size_t bkg_bytes = al(sizeof(int) * bkg_cap) + al(sizeof(float) * bkg_cap) + al(bkg_cap);
+  int bkg_in_smem = 0;
+  if (smem + bkg_bytes <= (size_t)h->smem_optin) {
+    bkg_in_smem = 1;
+    smem += bkg_bytes;
   }
   if (smem > (size_t)h->smem_optin)
     return v1g_fail(h, V1G_ERANGE, "backward rollout needs %zu B of shared memory per block", smem);
@@ -580,6 +760,7 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
 
   // scratch: Q ring, CSR-order weight gradients, loss tables
   const int64_t q_elems = (int64_t)K * Np * C * BP;
+  if (q_elems >= 0x7fffffffLL) return v1g_fail(h, V1G_ERANGE, "backward Q ring of %lld elements exceeds 32-bit indexing", (long long)q_elems);
   if ((rc = v1g_reserve(h, &h->dy_ring, &h->dy_ring_cap, q_elems))) return rc;
   const int nbins = (ls.sync_cost != 0.f && ls.sync_bin > 0) ? T / ls.sync_bin : 0;
   // loss scratch layout (floats): acc[4] | rate_coef[N] | sgrad[B*nbins] | spike_count[N] (int) | popcount[T*B] (int)
@@ -617,6 +798,8 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   a.N = N; a.D = D; a.K = K; a.B = B; a.T = T; a.Np = Np;
   a.chunk = plan.chunk; a.chunkP = plan.chunkP; a.S = S; a.C = C; a.n_bkg = c.n_bkg;
   a.state_in_smem = state_in_smem;
+  a.bkg_in_smem = bkg_in_smem;
+  a.bkg_cap = bkg_cap;
   const V1GSource& rs = h->src[V1G_SRC_REC];
   const V1GSource& lsrc = h->src[V1G_SRC_LGN];
   const V1GSource& bk = h->src[V1G_SRC_BKG];
@@ -633,6 +816,7 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   a.damp = c.dampening_factor; a.width = c.pseudo_width; a.gauss_std = c.gauss_std;
   a.gauss = (c.flags & V1G_FLAG_PSEUDO_GAUSS) ? 1 : 0;
   a.hard_reset = (c.flags & V1G_FLAG_HARD_RESET) ? 1 : 0;
+  a.csr_evict_first = h->opt_csr_evict_first;
   a.tape_v = h->tape_v; a.tape_zr = h->tape_zr;
   a.lgn_off = h->lgn_offsets; a.lgn_entries = h->lgn_entries; a.lgn_nseg = h->lgn_nseg;
   a.bkg_counts = h->tape_counts;
@@ -654,8 +838,34 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
     a.phase_ns = h->phase_ns;
     h->phase_grid = plan.grid;
   }
+  // keep the Q ring resident in L2 (it is gathered at random, one sector per synapse and step)
+  {
+    cudaDeviceProp prop;
+    V1G_CUDA(h, cudaGetDeviceProperties(&prop, h->device));
+    const size_t q_bytes = (size_t)q_elems * sizeof(float);
+    if (h->opt_l2_window && prop.persistingL2CacheMaxSize > 0 && prop.accessPolicyMaxWindowSize > 0) {
+      const size_t carve = std::min<size_t>((size_t)prop.persistingL2CacheMaxSize, q_bytes);
+      V1G_CUDA(h, cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, carve));
+      cudaStreamAttrValue attr;
+      attr.accessPolicyWindow.base_ptr = h->dy_ring;
+      attr.accessPolicyWindow.num_bytes = std::min<size_t>(q_bytes, (size_t)prop.accessPolicyMaxWindowSize);
+      attr.accessPolicyWindow.hitRatio = (float)std::min(1.0, (double)carve / (double)attr.accessPolicyWindow.num_bytes);
+      attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+      attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+      V1G_CUDA(h, cudaStreamSetAttribute(st, cudaStreamAttributeAccessPolicyWindow, &attr));
+    }
+  }
   rc = (R == 4) ? launch_bwd_r<4>(h, a, BP, proj, plan.grid, smem, st)
                 : launch_bwd_r<5>(h, a, BP, proj, plan.grid, smem, st);
+  {
+    cudaStreamAttrValue attr;
+    attr.accessPolicyWindow.base_ptr = nullptr;
+    attr.accessPolicyWindow.num_bytes = 0;
+    attr.accessPolicyWindow.hitRatio = 0.f;
+    attr.accessPolicyWindow.hitProp = cudaAccessPropertyNormal;
+    attr.accessPolicyWindow.missProp = cudaAccessPropertyNormal;
+    cudaStreamSetAttribute(st, cudaStreamAttributeAccessPolicyWindow, &attr);
+  }
   if (rc) return rc;
 
   // weight gradients back to the caller's synapse order, accumulated
