@@ -6,11 +6,15 @@ reference calls.  Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-basel
 ``bench.py`` may import it; no product code path does.
 
 PARITY PINNING: the reference ships no tests, golden vectors or fixtures for this path, and
-TensorFlow is not installable where this was written.  The oracle is pinned by
-``tests/golden/run_reference_models.py``, which imports the reference's own ``models.py`` over a
-small stand-in for the TensorFlow calls it makes and compares outputs and gradients with this file
-(see ``tests/test_oracle_pinning.py``); where that stand-in is not available the status is
-"parity unpinned".
+TensorFlow, which it needs, is not installable where this was written.  The oracle is pinned
+against the reference's OWN cell instead: ``tests/golden/run_reference_models.py`` imports the
+unmodified ``v1_model_utils/models.py`` from the reference tree over ``tests/golden/tf_standin.py``
+(a torch-backed stand-in for the TensorFlow calls the file makes), steps its ``V1Column.call`` and
+back-propagates through its custom gradients; the outputs are committed as
+``tests/golden/reference_*.npz`` and ``tests/test_oracle_pinning.py`` requires this oracle to
+reproduce them (spikes, refractory counters and the CSR table exactly; voltages and state to
+1e-12; the three weight gradients to 1e-10, all in fp64).  Not pinned: TensorFlow's own kernels
+(summation order of ``unsorted_segment_sum``, the Philox Poisson sampler), which never ran.
 
 Correspondence (reference ``v1_model_utils/models.py`` line numbers):
 

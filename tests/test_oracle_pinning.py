@@ -1,0 +1,85 @@
+"""Pins the oracle (and, on a GPU, the CUDA path) to the reference's own cell.
+
+``tests/golden/reference_*.npz`` were produced by ``tests/golden/run_reference_models.py``, which
+imports the reference's unmodified ``v1_model_utils/models.py`` over a torch-backed stand-in for
+the TensorFlow calls it makes and steps its ``V1Column.call``.  The fixtures travel; the reference
+tree and the stand-in are not needed to run these tests.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from util import TOL_GRAD, TOL_STATE, make_case, rel_err
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CASES = ["reference_tiny", "reference_tiny_hard_reset", "reference_small"]
+
+
+def _load(name):
+    g = np.load(os.path.join(ROOT, "tests", "golden", name + ".npz"))
+    kw = dict(dampening_factor=float(g["kw_dampening_factor"]),
+              recurrent_dampening_factor=float(g["kw_recurrent_dampening_factor"]),
+              voltage_gradient_dampening=float(g["kw_voltage_gradient_dampening"]),
+              hard_reset=bool(g["hard_reset"]))
+    return g, kw
+
+
+def _cotangents(g):
+    """Output cotangents of the fixture: stored, or regenerated from its seed (same generator
+    calls as tests/golden/run_reference_models.py)."""
+    if "g_z" in g.files:
+        return torch.from_numpy(g["g_z"]), torch.from_numpy(g["g_v"])
+    gen = torch.Generator().manual_seed(int(g["g_seed"]))
+    shape = g["v"].shape
+    g_z = torch.randn(shape, generator=gen, dtype=torch.float64) * 1e-2
+    g_v = torch.randn(shape, generator=gen, dtype=torch.float64) * 1e-3
+    return g_z, g_v
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_oracle_equals_reference_cell(name):
+    g, kw = _load(name)
+    cfg, dicts, orc = make_case(str(g["config"]), seed=int(g["seed"]), dtype=torch.float64, **kw)
+    # the CSR table the reference built (make_pre_ind_table) is reproduced exactly
+    assert np.array_equal(orc.pre_ind_table.order.numpy(), g["pre_ind_order"])
+    assert np.array_equal(orc.pre_ind_table.row_splits.numpy(), g["pre_ind_row_splits"])
+    z, v, state = orc.rollout(torch.from_numpy(g["x"]), torch.from_numpy(g["bkg_counts"]).long())
+    assert np.array_equal(z.detach().numpy().astype(np.uint8), g["z"])
+    assert np.abs(v.detach().numpy() - g["v"]).max() <= 1e-12
+    for got, key in zip((state[0], state[3], state[4], state[5]), ("z_buf", "asc", "psc_rise", "psc")):
+        assert np.abs(got.detach().numpy() - g[key]).max() <= 1e-12
+    assert np.array_equal(state[2].numpy(), g["r"].astype(np.int64))
+    g_z, g_v = _cotangents(g)
+    ((z * g_z).sum() + (v * g_v).sum()).backward()
+    for w, key in ((orc.recurrent_weight_values, "dw_rec"), (orc.input_weight_values, "dw_lgn"),
+                   (orc.bkg_input_weights, "dw_bkg")):
+        assert rel_err(w.grad, g[key]) <= 1e-10
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", CASES)
+def test_cuda_path_equals_reference_cell(name):
+    from v1_glif_model_b200.models import V1Column
+    g, kw = _load(name)
+    cfg, dicts, _ = make_case(str(g["config"]), seed=int(g["seed"]), **kw)
+    cell = V1Column(*dicts, **kw)
+    order, splits = cell.pre_ind_table(0)
+    assert np.array_equal(order, g["pre_ind_order"]) and np.array_equal(splits, g["pre_ind_row_splits"])
+    state = cell.zero_state(g["x"].shape[0])
+    z, v = cell.rollout(torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["bkg_counts"]).cuda(),
+                        state=state)
+    cell.synchronize()
+    assert np.array_equal(z.cpu().numpy(), g["z"])
+    assert rel_err(v, g["v"]) <= TOL_STATE
+    for got, key in zip((state[0], state[3], state[4], state[5]), ("z_buf", "asc", "psc_rise", "psc")):
+        assert rel_err(got, g[key]) <= TOL_STATE
+    assert np.array_equal(state[2].cpu().numpy(), g["r"])
+    cell.rollout(torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["bkg_counts"]).cuda(),
+                 return_z=False, return_v=False, save_for_bwd=True)
+    g_z, g_v = _cotangents(g)
+    grads = cell.backward(None, g_z=g_z.float().cuda(), g_v=g_v.float().cuda())
+    cell.synchronize()
+    for got, key in zip(grads[:3], ("dw_rec", "dw_lgn", "dw_bkg")):
+        assert rel_err(got, g[key]) <= TOL_GRAD
