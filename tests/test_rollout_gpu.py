@@ -165,6 +165,23 @@ def test_bptt_gradients_match_oracle_autograd(name, options, kw):
         assert rel_err(got, want) <= TOL_GRAD
 
 
+@pytest.mark.parametrize("options", [(), (("no_q_pack", 1),), (("rollout_chunk", 64),)])
+def test_bptt_batch_of_five(options):
+    """Batch 5 stores the backward Q rows as five 24-bit floats per 16-byte row (7.6e-6 relative
+    rounding); the gradients must stay inside the 1e-4 bar, as they do with fp32 rows."""
+    cfg, dicts, orc, cell = _cells("small", options, **KW)
+    x, c = make_inputs(cfg, batch=5, seq_len=40)
+    zo, lo, go = _oracle_grads(orc, cfg, x, c, cell.voltage_scale, torch.float32)
+    z, _ = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), save_for_bwd=True)
+    assert torch.equal(z.cpu().float(), zo)
+    tgt = torch.from_numpy(synth.make_rate_targets(cfg)).cuda() / 1000.0
+    vlo = torch.from_numpy((-20.0 / cell.voltage_scale).astype(np.float32)).cuda()
+    grads = cell.backward(dict(LOSS, rate_target=tgt, v_lo=vlo))
+    cell.synchronize()
+    for got, want in zip(grads[:3], go):
+        assert rel_err(got, want) <= TOL_GRAD
+
+
 def test_bptt_with_explicit_output_gradients():
     """dL/dz and dL/dv supplied as tensors (the general tape.gradient form), no in-kernel loss."""
     cfg, dicts, orc, cell = _cells("small", **KW)

@@ -414,6 +414,8 @@ extern "C" int v1g_set_option(V1GHandle* h, const char* name, long long value) {
     h->opt_force_global = value != 0;
   } else if (!strcmp(name, "force_smem_kernel")) {
     h->opt_force_smem_kernel = value != 0;
+  } else if (!strcmp(name, "no_q_pack")) {
+    h->opt_no_q_pack = value != 0;
   } else if (!strcmp(name, "l2_window")) {
     h->opt_l2_window = value != 0;
   } else if (!strcmp(name, "csr_evict_first")) {

@@ -107,6 +107,7 @@ struct V1GHandle {
   int opt_force_global = 0;   // keep rollout state in global memory even if it fits on chip
   long long opt_spin_limit = 4000000LL;
   int opt_force_smem_kernel = 0;  // never pick the register-resident forward kernel
+  int opt_no_q_pack = 0;          // keep the backward Q rows in fp32 even for a batch of 5
   int opt_l2_window = 0;          // pin the backward Q ring in L2 with an access-policy window
   int opt_csr_evict_first = 1;    // read the backward synapse stream with evict-first loads
   int opt_phase_timers = 0;   // record per-block phase times of the rollout kernels

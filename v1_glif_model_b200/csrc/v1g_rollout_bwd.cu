@@ -71,7 +71,10 @@ struct BwdArgs {
   unsigned long long* phase_ns;
 };
 
-constexpr int NT = 512;
+#ifndef V1G_BWD_NT
+#define V1G_BWD_NT 512
+#endif
+constexpr int NT = V1G_BWD_NT;
 constexpr int NW = NT / 32;
 
 __device__ __forceinline__ unsigned long long gtime_b() {
@@ -87,18 +90,51 @@ __device__ __forceinline__ float pseudo_h(float vs, const BwdArgs& a) {
   return a.damp * fmaxf(1.f - x, 0.f);
 }
 
-template <int BP_>
+// A Q row holds the values of all batch rows for one (neuron, channel): BP_ fp32 words, or - for a
+// batch of exactly 5 - five 24-bit floats (sign, 8 exponent, 15 mantissa bits, round to nearest
+// even: 7.6e-6 relative) packed into four words, which keeps the row at 16 bytes and the whole
+// ring at half the size, inside L2.
+__device__ __forceinline__ unsigned f24(float x) {
+  unsigned u = __float_as_uint(x);
+  u += 0x7fu + ((u >> 8) & 1u);
+  return u >> 8;
+}
+
+__device__ __forceinline__ float4 pack_row5(const float (&v)[8]) {
+  const unsigned r0 = f24(v[0]), r1 = f24(v[1]), r2 = f24(v[2]), r3 = f24(v[3]), r4 = f24(v[4]);
+  uint4 w;
+  w.x = r0 | (r1 << 24);
+  w.y = (r1 >> 8) | (r2 << 16);
+  w.z = (r2 >> 16) | (r3 << 8);
+  w.w = r4;
+  return make_float4(__uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z), __uint_as_float(w.w));
+}
+
+template <int BP_, bool PACK>
 __device__ __forceinline__ void load_row(const float* p, float (&q)[BP_]) {
   const float4 a = __ldcg((const float4*)p);
+  if (PACK) {
+    const unsigned w0 = __float_as_uint(a.x), w1 = __float_as_uint(a.y), w2 = __float_as_uint(a.z),
+                   w3 = __float_as_uint(a.w);
+    q[0] = __uint_as_float(w0 << 8);
+    q[1] = __uint_as_float(__funnelshift_l(w0, w1, 16) & 0xffffff00u);
+    q[2] = __uint_as_float(__funnelshift_l(w1, w2, 24) & 0xffffff00u);
+    q[3] = __uint_as_float(w2 & 0xffffff00u);
+    q[4 % BP_] = __uint_as_float(w3 << 8);
+#pragma unroll
+    for (int b = 5; b < BP_; ++b) q[b] = 0.f;
+    return;
+  }
   q[0] = a.x; q[1] = a.y; q[2] = a.z; q[3] = a.w;
   if (BP_ == 8) {
     const float4 b = __ldcg((const float4*)p + 1);
-    q[4] = b.x; q[5] = b.y; q[6] = b.z; q[7] = b.w;
+    q[4 % BP_] = b.x; q[5 % BP_] = b.y; q[6 % BP_] = b.z; q[7 % BP_] = b.w;
   }
 }
 
-template <int R_, int BP_, bool PROJ, int DT>
+template <int R_, int BP_, bool PROJ, int DT, bool PACK>
 __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
+  constexpr int QW = PACK ? 4 : BP_;  // 32-bit words per Q row
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int B = a.B, K = a.K, N = a.N, Np = a.Np, chunkP = a.chunkP, T = a.T, C = a.C;
@@ -199,21 +235,29 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   auto lgn_dw = [&](int tt) {
     const int seg_per_t = B * a.lgn_nseg;
     const int e0 = a.lgn_off[(int64_t)tt * seg_per_t], e1 = a.lgn_off[(int64_t)(tt + 1) * seg_per_t];
-    const float* Qs = a.Q + (int64_t)(tt % K) * Np * C * BP_;
+    const float* Qs = a.Q + (int64_t)(tt % K) * Np * C * QW;
     for (int e = e0 + gw; e < e1; e += gnw) {
       const uint32_t ent = a.lgn_entries[e];
       const int b = ent >> 24, u = ent & 0xffffff;
       const int j0 = a.lgn_rowptr[u], j1 = a.lgn_rowptr[u + 1];
       for (int j = j0 + lane; j < j1; j += 32) {
         const int post = a.lgn_post[j], sid = a.lgn_sid[j];
-        float val;
+        float val = 0.f;
         if (PROJ) {
-          val = __ldcg(Qs + ((int64_t)post * C + sid) * BP_ + b);
-        } else {
-          val = 0.f;
+          float q[BP_];
+          load_row<BP_, PACK>(Qs + ((int64_t)post * C + sid) * QW, q);
 #pragma unroll
-          for (int r = 0; r < R_; ++r)
-            val += __ldcg(Qs + ((int64_t)post * C + r) * BP_ + b) * basis_s[sid * R_ + r];
+          for (int bb = 0; bb < BP_; ++bb) val = (bb == b) ? q[bb] : val;
+        } else {
+#pragma unroll
+          for (int r = 0; r < R_; ++r) {
+            float q[BP_];
+            load_row<BP_, PACK>(Qs + ((int64_t)post * C + r) * QW, q);
+            float qb = 0.f;
+#pragma unroll
+            for (int bb = 0; bb < BP_; ++bb) qb = (bb == b) ? q[bb] : qb;
+            val += qb * basis_s[sid * R_ + r];
+          }
         }
         atomicAdd(a.dw_lgn + j, val);
       }
@@ -348,16 +392,16 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         float pj[U][BP_];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const float* Qp = a.Q + (unsigned)((slot[u] * Np + cpost[u]) * C) * BP_;  // < 2^31, checked by the host
+          const float* Qp = a.Q + (unsigned)((slot[u] * Np + cpost[u]) * C) * QW;  // < 2^31, checked by the host
           if (PROJ) {
-            load_row<BP_>(Qp + csid[u] * BP_, pj[u]);
+            load_row<BP_, PACK>(Qp + csid[u] * QW, pj[u]);
           } else {
 #pragma unroll
             for (int b = 0; b < BP_; ++b) pj[u][b] = 0.f;
 #pragma unroll
             for (int r = 0; r < R_; ++r) {
               float q[BP_];
-              load_row<BP_>(Qp + r * BP_, q);
+              load_row<BP_, PACK>(Qp + r * QW, q);
               const float bs = basis_s[csid[u] * R_ + r];
 #pragma unroll
               for (int b = 0; b < BP_; ++b) pj[u][b] += q[b] * bs;
@@ -424,7 +468,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
 
     // ---------------- phase C: dense adjoint, publish Q(t-2), background weight gradient ----------------
     const int bin = (a.sgrad && a.sync_bin > 0 && t / a.sync_bin < a.nbins) ? t / a.sync_bin : -1;
-    float* Qw = a.Q + (int64_t)((t + K - 2) % K) * Np * C * BP_;
+    float* Qw = a.Q + (int64_t)((t + K - 2) % K) * Np * C * QW;
     for (int k = tid; k < cn; k += NT) {
       const int n = n0 + k;
       const float k_decay = c_decay[k], k_cf = c_cf[k], k_ad0 = c_ad0[k], k_ad1 = c_ad1[k];
@@ -469,7 +513,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       }
       if (t >= 2) {
         // one 16/32-byte row per channel, all batch rows of the neuron at once
-        float4* qd = (float4*)(Qw + (int64_t)n * C * BP_);
+        float4* qd = (float4*)(Qw + (int64_t)n * C * QW);
         for (int c = 0; c < C; ++c) {
           float row[BP_];
 #pragma unroll
@@ -486,8 +530,16 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
               row[b] = s2;
             }
           }
-          __stcg(qd + c * (BP_ / 4), make_float4(row[0], row[1], row[2], row[3]));
-          if (BP_ == 8) __stcg(qd + c * 2 + 1, make_float4(row[4 % BP_], row[5 % BP_], row[6 % BP_], row[7 % BP_]));
+          if (PACK) {
+            float r8[8];
+#pragma unroll
+            for (int b = 0; b < 8; ++b) r8[b] = b < BP_ ? row[b % BP_] : 0.f;
+            __stcg(qd + c, pack_row5(r8));
+          } else {
+            __stcg(qd + c * (BP_ / 4), make_float4(row[0], row[1], row[2], row[3]));
+            if (BP_ == 8)
+              __stcg(qd + c * 2 + 1, make_float4(row[4 % BP_], row[5 % BP_], row[6 % BP_], row[7 % BP_]));
+          }
         }
         // background weight gradient of step t-2 for the synapses this thread owns
         for (int j = bkptr_s[k]; j < bkptr_s[k + 1]; ++j) {
@@ -670,9 +722,9 @@ __global__ void finish_loss_kernel(float* acc, float* out) {
   }
 }
 
-template <int R_, int BP_, bool PROJ, int DT>
+template <int R_, int BP_, bool PROJ, int DT, bool PACK>
 int launch_bwd_d(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream_t st) {
-  auto kern = rollout_bwd_kernel<R_, BP_, PROJ, DT>;
+  auto kern = rollout_bwd_kernel<R_, BP_, PROJ, DT, PACK>;
   V1G_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0;
   V1G_CUDA(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, smem));
@@ -687,17 +739,23 @@ int launch_bwd_d(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStre
   return V1G_OK;
 }
 
-template <int R_, int BP_, bool PROJ>
+template <int R_, int BP_, bool PROJ, bool PACK>
 int launch_bwd(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream_t st) {
-  if (a.D == 5) return launch_bwd_d<R_, BP_, PROJ, 5>(h, a, grid, smem, st);
-  return launch_bwd_d<R_, BP_, PROJ, 0>(h, a, grid, smem, st);
+  if (a.D == 5) return launch_bwd_d<R_, BP_, PROJ, 5, PACK>(h, a, grid, smem, st);
+  return launch_bwd_d<R_, BP_, PROJ, 0, PACK>(h, a, grid, smem, st);
 }
 
 template <int R_>
-int launch_bwd_r(V1GHandle* h, const BwdArgs& a, int BP, bool proj, int grid, size_t smem,
+int launch_bwd_r(V1GHandle* h, const BwdArgs& a, int BP, bool proj, bool pack, int grid, size_t smem,
                  cudaStream_t st) {
-  if (BP == 4) return proj ? launch_bwd<R_, 4, true>(h, a, grid, smem, st) : launch_bwd<R_, 4, false>(h, a, grid, smem, st);
-  return proj ? launch_bwd<R_, 8, true>(h, a, grid, smem, st) : launch_bwd<R_, 8, false>(h, a, grid, smem, st);
+  if (BP == 4)
+    return proj ? launch_bwd<R_, 4, true, false>(h, a, grid, smem, st)
+                : launch_bwd<R_, 4, false, false>(h, a, grid, smem, st);
+  if (pack)
+    return proj ? launch_bwd<R_, 8, true, true>(h, a, grid, smem, st)
+                : launch_bwd<R_, 8, false, true>(h, a, grid, smem, st);
+  return proj ? launch_bwd<R_, 8, true, false>(h, a, grid, smem, st)
+              : launch_bwd<R_, 8, false, false>(h, a, grid, smem, st);
 }
 
 }  // namespace
@@ -720,6 +778,8 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   const bool proj = S <= 8;
   const int C = proj ? S : R;
   const int BP = B <= 4 ? 4 : 8;
+  const bool pack = (B == 5) && !h->opt_no_q_pack;  // five 24-bit floats per 16-byte row
+  const int QW = pack ? 4 : BP;
   const int Np = (N + 31) & ~31;
   int rc;
 
@@ -759,7 +819,7 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
     if ((rc = v1g_reserve(h, &h->state_ws, &h->state_ws_cap, (int64_t)(plane * (3 + 2 * R) * plan.grid)))) return rc;
 
   // scratch: Q ring, CSR-order weight gradients, loss tables
-  const int64_t q_elems = (int64_t)K * Np * C * BP;
+  const int64_t q_elems = (int64_t)K * Np * C * QW;
   if (q_elems >= 0x7fffffffLL) return v1g_fail(h, V1G_ERANGE, "backward Q ring of %lld elements exceeds 32-bit indexing", (long long)q_elems);
   if ((rc = v1g_reserve(h, &h->dy_ring, &h->dy_ring_cap, q_elems))) return rc;
   const int nbins = (ls.sync_cost != 0.f && ls.sync_bin > 0) ? T / ls.sync_bin : 0;
@@ -855,8 +915,8 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
       V1G_CUDA(h, cudaStreamSetAttribute(st, cudaStreamAttributeAccessPolicyWindow, &attr));
     }
   }
-  rc = (R == 4) ? launch_bwd_r<4>(h, a, BP, proj, plan.grid, smem, st)
-                : launch_bwd_r<5>(h, a, BP, proj, plan.grid, smem, st);
+  rc = (R == 4) ? launch_bwd_r<4>(h, a, BP, proj, pack, plan.grid, smem, st)
+                : launch_bwd_r<5>(h, a, BP, proj, pack, plan.grid, smem, st);
   {
     cudaStreamAttrValue attr;
     attr.accessPolicyWindow.base_ptr = nullptr;
