@@ -20,7 +20,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -66,44 +65,60 @@ def bwd_bytes_per_launch(cnt, n, r, b, t, nnz_rec):
 
 
 class ClockSampler:
-    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    """Samples SM clocks and throttle reasons through NVML, in-process, while the timed region
+    runs (an `nvidia-smi` subprocess per sample stalls the driver for tens of ms and would itself
+    perturb the measurement)."""
 
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap"}
 
     def __init__(self, index):
-        self.index, self.rows, self.stop_flag, self.thread = index, [], False, None
+        self.index, self.sm, self.bits, self.stop_flag, self.thread = index, [], 0, False, None
+        self.max_mhz, self.handle, self.nv = None, None, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = getattr(torch.cuda.get_device_properties(index), "uuid", None)
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nv = pynvml
+        except Exception:
+            self.nv = None
+
+    def _sample(self):
+        nv = self.nv
+        self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+        try:
+            self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+        except Exception:
+            self.bits |= int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
 
     def _run(self):
         while not self.stop_flag:
             try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                      "--format=csv,noheader,nounits"], capture_output=True,
-                                     text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.split(",")])
+                self._sample()
             except Exception:
                 pass
-            time.sleep(0.2)
+            time.sleep(0.02)
 
     def __enter__(self):
-        self.thread = threading.Thread(target=self._run, daemon=True)
-        self.thread.start()
+        if self.nv is not None:
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
         return self
 
     def __exit__(self, *a):
         self.stop_flag = True
-        self.thread.join(timeout=6)
+        if self.thread is not None:
+            self.thread.join(timeout=2)
 
     def summary(self):
-        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({names[i] for r in self.rows for i in range(4)
-                          if len(r) > 2 + i and r[2 + i].lower().startswith("active")})
-        return {"sm_mhz": float(np.median(sm)) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+        reasons = sorted(name for bit, name in self.REASONS.items() if self.bits & bit)
+        return {"sm_mhz": float(np.median(self.sm)) if self.sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.sm), "source": "nvml" if self.nv else "unavailable"}
 
 
 def loss_spec(cfg, cell_voltage_scale, device):

@@ -130,7 +130,6 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   cudaFree(h->d_count);
   if (h->h_count) cudaFreeHost(h->h_count);
   cudaFree(h->lgn_entries);
-  cudaFree(h->lgn_rows);
   cudaFree(h->lgn_offsets);
   cudaFree(h->ring);
   cudaFree(h->state_ws);

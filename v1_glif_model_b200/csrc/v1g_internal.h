@@ -73,8 +73,6 @@ struct V1GHandle {
   int32_t* h_count = nullptr;  // pinned host mirror
   uint32_t* lgn_entries = nullptr;
   int64_t lgn_entries_cap = 0;
-  int2* lgn_rows = nullptr;  // CSR row bounds of each LGN list entry
-  int64_t lgn_rows_cap = 0;
   int32_t* lgn_offsets = nullptr;  // [T*B*nseg + 1]
   int64_t lgn_offsets_cap = 0;
   int lgn_nseg = 0;

@@ -899,11 +899,11 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
     h->phase_grid = plan.grid;
   }
   // keep the Q ring resident in L2 (it is gathered at random, one sector per synapse and step)
-  {
+  if (h->opt_l2_window) {
     cudaDeviceProp prop;
     V1G_CUDA(h, cudaGetDeviceProperties(&prop, h->device));
     const size_t q_bytes = (size_t)q_elems * sizeof(float);
-    if (h->opt_l2_window && prop.persistingL2CacheMaxSize > 0 && prop.accessPolicyMaxWindowSize > 0) {
+    if (prop.persistingL2CacheMaxSize > 0 && prop.accessPolicyMaxWindowSize > 0) {
       const size_t carve = std::min<size_t>((size_t)prop.persistingL2CacheMaxSize, q_bytes);
       V1G_CUDA(h, cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, carve));
       cudaStreamAttrValue attr;
@@ -917,7 +917,7 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   }
   rc = (R == 4) ? launch_bwd_r<4>(h, a, BP, proj, pack, plan.grid, smem, st)
                 : launch_bwd_r<5>(h, a, BP, proj, pack, plan.grid, smem, st);
-  {
+  if (h->opt_l2_window) {
     cudaStreamAttrValue attr;
     attr.accessPolicyWindow.base_ptr = nullptr;
     attr.accessPolicyWindow.num_bytes = 0;

@@ -24,18 +24,6 @@ namespace {
 
 constexpr int NT = 768;
 
-// row bounds of every LGN list entry, so that the rollout does not chase the row pointers
-__global__ void __launch_bounds__(256) lgn_rows_kernel(const uint32_t* __restrict__ entries,
-                                                       const int32_t* __restrict__ rowptr, int64_t n,
-                                                       int2* __restrict__ rows) {
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (; i < n; i += stride) {
-    const int u = entries[i] & 0xffffff;
-    rows[i] = make_int2(rowptr[u], rowptr[u + 1]);
-  }
-}
-
 template <int R_>
 __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -165,8 +153,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
     v1g_walk_rec<R_>(a, basis_s, lane, b, a.rec_rowptr + (int64_t)n * D, te, c_rec_ev);
   };
   auto scatter_lgn = [&](int tt) {
-    v1g_scatter_lgn<R_>(a, basis_s, lane, blockIdx.x * NW + warp, gridDim.x * NW, tt,
-                        v1g_lgn_begin(a, tt), v1g_lgn_begin(a, tt + 1), c_lgn_rows, c_lgn_ev);
+    v1g_scatter_lgn<R_>(a, basis_s, lane, blockIdx.x * NW + warp, gridDim.x * NW, tt, c_lgn_rows,
+                        c_lgn_ev);
   };
 
   // ---- prologue: pending deliveries of the initial spike buffer, LGN events of step 0 ----
@@ -506,13 +494,6 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
                              h->lgn_entries, n_lgn_events, st)))
     return rc;
   h->lgn_nseg = nseg;
-  if ((rc = v1g_reserve(h, &h->lgn_rows, &h->lgn_rows_cap, n_lgn_events + 1))) return rc;
-  if (n_lgn_events > 0) {
-    lgn_rows_kernel<<<(unsigned)std::min<int64_t>((n_lgn_events + 255) / 256, 65535), 256, 0, st>>>(
-        h->lgn_entries, h->src[V1G_SRC_LGN].rowptr, n_lgn_events, h->lgn_rows);
-    v1g_count_launches(1);
-    V1G_CUDA(h, cudaGetLastError());
-  }
 
   // ---- plan ----
   V1GRolloutPlan plan;
@@ -584,7 +565,7 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
   }
   a.lr_scale = c.lr_scale; a.vd_keep = h->vd_keep; a.vd_drop = h->vd_drop;
   a.hard_reset = (c.flags & V1G_FLAG_HARD_RESET) ? 1 : 0;
-  a.lgn_off = h->lgn_offsets; a.lgn_entries = h->lgn_entries; a.lgn_rows = h->lgn_rows; a.lgn_nseg = nseg;
+  a.lgn_off = h->lgn_offsets; a.lgn_entries = h->lgn_entries; a.lgn_nseg = nseg;
   a.bkg_counts = bkg_counts;
   if (state) a.st = *state; else a.st = V1GState{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   a.state_ws = h->state_ws;

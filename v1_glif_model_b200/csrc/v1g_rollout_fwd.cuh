@@ -25,7 +25,6 @@ struct FwdArgs {
   // inputs
   const int32_t* lgn_off;  // exclusive offsets per (t, b, seg) segment
   const uint32_t* lgn_entries;
-  const int2* lgn_rows;  // CSR row bounds [j0, j1) of every list entry
   int lgn_nseg;
   const int32_t* bkg_counts;  // [B][T][n_bkg]
   // state (reference layouts, all NULL = zero state / no write-back)
@@ -88,20 +87,19 @@ __device__ __forceinline__ void v1g_walk_rec(const FwdArgs& a, const float* basi
   if (lane == 0) events += (unsigned long long)(j1 - j0);
 }
 
-// LGN events [e0, e1) of step tt into ring slot tt mod K; the list is shared by all warps of the
-// grid (gw = global warp index, gnw = warps in the grid).  Each entry carries its CSR row bounds,
-// so the chain of dependent loads is entry -> synapse records -> atomics.
+// LGN events of step tt into ring slot tt mod K; the list is shared by all warps of the grid
+// (gw = global warp index, gnw = warps in the grid).
 template <int R_>
 __device__ __forceinline__ void v1g_scatter_lgn(const FwdArgs& a, const float* basis_s, int lane,
-                                                int gw, int gnw, int tt, int e0, int e1,
-                                                unsigned long long& rows,
+                                                int gw, int gnw, int tt, unsigned long long& rows,
                                                 unsigned long long& events) {
+  const int seg_per_t = a.B * a.lgn_nseg;
+  const int e0 = a.lgn_off[(int64_t)tt * seg_per_t], e1 = a.lgn_off[(int64_t)(tt + 1) * seg_per_t];
   const int slot = tt % a.K;
   for (int e = e0 + gw; e < e1; e += gnw) {
     const uint32_t ent = a.lgn_entries[e];
-    const int2 rb = a.lgn_rows[e];
-    const int b = ent >> 24;
-    const int j0 = rb.x, j1 = rb.y;
+    const int b = ent >> 24, u = ent & 0xffffff;
+    const int j0 = a.lgn_rowptr[u], j1 = a.lgn_rowptr[u + 1];
     for (int j = j0 + lane; j < j1; j += 32) {
       const float wv = a.lgn_w[j];
       const float* bs = basis_s + (int)a.lgn_sid[j] * R_;
@@ -117,11 +115,6 @@ __device__ __forceinline__ void v1g_scatter_lgn(const FwdArgs& a, const float* b
       events += (unsigned long long)(j1 - j0);
     }
   }
-}
-
-// First list index of step tt (tt in 0..T).
-__device__ __forceinline__ int v1g_lgn_begin(const FwdArgs& a, int tt) {
-  return a.lgn_off[(int64_t)tt * a.B * a.lgn_nseg];
 }
 
 // Register-resident variant (one thread per neuron, batch unrolled); V1G_ERANGE when the

@@ -35,12 +35,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
   int* s_cnt = (int*)take(sizeof(int) * 2 * nb);
   int* s_misc = (int*)take(sizeof(int) * 4);
   uint2* bk_s = (uint2*)take(sizeof(uint2) * a.bkg_cap);  // (pre | sid << 24, weight bits)
-  int32_t* rp_s = (int32_t*)take(sizeof(int32_t) * ((size_t)NT * a.D + 1));  // row pointers of the slice
   float* pr_s = (float*)take(sizeof(float) * B_ * R_ * NT) + tid;  // [b][r][tid]
 #define PR(b, r) pr_s[((b)*R_ + (r)) * NT]
 
   for (int i = tid; i < a.S * R_; i += NT) basis_s[i] = a.basis[i];
-  for (int i = tid; i <= cn * D; i += NT) rp_s[i] = a.rec_rowptr[(int64_t)n0 * D + i];
   const int bk_base = a.bkg_inptr[n0];
   {
     const int m = a.bkg_inptr[n0 + cn] - bk_base;
@@ -101,20 +99,13 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
         while (m) {
           const int src = __ffs(m) - 1;
           m &= m - 1;
-          v1g_walk_rec<R_>(a, basis_s, lane, b, rp_s + (warp * 32 + src) * D, -(d + 1), c_rec_ev);
+          v1g_walk_rec<R_>(a, basis_s, lane, b, a.rec_rowptr + (int64_t)(n0 + warp * 32 + src) * D,
+                           -(d + 1), c_rec_ev);
         }
       }
     }
   }
-  // list offsets are fetched one step ahead: lg_e[0..1] bound the events of the next step to
-  // scatter, lg_e[2] is the end of the step after it
-  int lg_e0 = 0, lg_e1 = 0, lg_e2 = 0;
-  if (a.T > 0) {
-    lg_e0 = v1g_lgn_begin(a, 0);
-    lg_e1 = v1g_lgn_begin(a, 1);
-    lg_e2 = a.T > 1 ? v1g_lgn_begin(a, 2) : lg_e1;
-    v1g_scatter_lgn<R_>(a, basis_s, lane, gw, gnw, 0, lg_e0, lg_e1, c_lgn_rows, c_lgn_ev);
-  }
+  if (a.T > 0) v1g_scatter_lgn<R_>(a, basis_s, lane, gw, gnw, 0, c_lgn_rows, c_lgn_ev);
   __syncthreads();
   if (tid == 0) v1g_arrive(v1g_phase_counter(a.barrier, 0));
 
@@ -254,16 +245,11 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
     const int nspk = *nspk_p;
     for (int e = warp; e < nspk; e += NW) {
       const uint32_t ent = spk_list[e];
-      v1g_walk_rec<R_>(a, basis_s, lane, (int)(ent >> 24), rp_s + (int)(ent & 0xffffff) * D, t, c_rec_ev);
+      v1g_walk_rec<R_>(a, basis_s, lane, (int)(ent >> 24),
+                       a.rec_rowptr + (int64_t)(n0 + (int)(ent & 0xffffff)) * D, t, c_rec_ev);
     }
     if (tid == 0) c_spikes += (unsigned long long)nspk;
-    {
-      // offsets of step t+3 are requested now and used next iteration
-      const int lg_e3 = (t + 3 <= a.T) ? v1g_lgn_begin(a, t + 3) : lg_e2;
-      if (t + 1 < a.T) v1g_scatter_lgn<R_>(a, basis_s, lane, gw, gnw, t + 1, lg_e1, lg_e2, c_lgn_rows, c_lgn_ev);
-      lg_e1 = lg_e2;
-      lg_e2 = lg_e3;
-    }
+    if (t + 1 < a.T) v1g_scatter_lgn<R_>(a, basis_s, lane, gw, gnw, t + 1, c_lgn_rows, c_lgn_ev);
     if (prof) {
       const unsigned long long ph3 = gtime();
       ph_barrier += ph1 - ph0;
@@ -390,7 +376,6 @@ size_t v1g_fwd_reg_smem(const V1GHandle* h, int B, int chunkP, int bkg_cap) {
   const V1GConfig& c = h->cfg;
   return al(sizeof(float) * c.n_syn_types * c.n_receptors) + al(sizeof(uint32_t) * B * NT) +
          al(sizeof(int) * 2 * B * c.n_bkg) + al(sizeof(int) * 4) + al(sizeof(uint2) * bkg_cap) +
-         al(sizeof(int32_t) * ((size_t)NT * c.max_delay + 1)) +
          al(sizeof(float) * B * c.n_receptors * NT);
 }
 
