@@ -32,7 +32,7 @@ sys.path.insert(0, ROOT)
 
 from v1_glif_model_b200 import synth  # noqa: E402
 
-METRIC = "simulated neuron-steps/s, fwd+bwd training step at the 66,634-neuron column"
+METRIC = "simulated neuron-steps/s, fwd+bwd training step at the 66k-neuron column"
 UNIT = "neuron-steps/s"
 LOSS = dict(rate_cost=100.0, voltage_cost=1e-3, sync_cost=1.0, fano_target=1.0, sync_bin=50)
 CELL_KW = dict(dampening_factor=0.5, pseudo_width=0.5, recurrent_dampening_factor=0.5,
@@ -159,7 +159,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cfg = synth.CONFIGS["C4"]
+    cfg = synth.CONFIGS[args.config]
     dicts = synth.make_network(cfg, 0)
     t_sample = args.cpu_sample_steps
     one = cpu_training_sample(cfg, dicts, t_sample, 0)
@@ -169,7 +169,7 @@ def run_reference(args):
     sec = float(np.mean(times))
     value = cfg.batch * cfg.n_neurons * t_sample / sec
     cores = torch.get_num_threads()
-    sample = (f"fwd+bwd of {t_sample} of the 500 simulated ms per step, batch {cfg.batch}, "
+    sample = (f"fwd+bwd of {t_sample} of the {cfg.seq_len} simulated ms per step, batch {cfg.batch}, "
               f"N={cfg.n_neurons}; torch CPU restatement of the reference cell")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
@@ -186,11 +186,12 @@ def run_reference(args):
 
 
 def workload_config(cfg, n_gpus, t_len):
-    return {"workload": "C4: 66,634-neuron synthetic column, fwd+bwd training step (rate+voltage+"
-                        "synchrony loss, Exp-Adam on recurrent+LGN weights)",
+    return {"workload": f"{cfg.name}: {cfg.n_neurons:,}-neuron synthetic column, fwd+bwd training step "
+                        "(rate+voltage+synchrony loss, Exp-Adam on recurrent+LGN weights)",
             "n_neurons": cfg.n_neurons, "batch_per_gpu": cfg.batch, "global_batch": cfg.batch * n_gpus,
             "seq_len": t_len, "n_receptors": cfg.n_receptors, "max_delay": cfg.max_delay,
-            "parallelism": f"dp{n_gpus}", "l2": "inputs larger than L2 (saved rollout 0.83 GB per step)"}
+            "parallelism": f"dp{n_gpus}",
+            "l2": "inputs larger than L2 (saved rollout %.2f GB per step)" % (5e-9 * cfg.batch * cfg.n_neurons * t_len)}
 
 
 # --------------------------------------------------------------------------------------
@@ -211,9 +212,10 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # stdout carries the JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
-    cfg = synth.CONFIGS["C4"]
+    cfg = synth.CONFIGS[args.config]
     t_len = args.seq_len or cfg.seq_len
     b = cfg.batch
     dicts = synth.make_network(cfg, 0)
@@ -318,7 +320,7 @@ def run_ours(args):
         "events_per_step": {k: cnt[k] / t_len for k in ("rec_events", "lgn_events", "bkg_events",
                                                         "dw_events", "bwd_events")},
     }
-    if world == 1 and not args.no_fwd:
+    if world == 1 and not args.no_fwd and args.config == "C4":
         line["fwd"] = forward_only(cell, lib, dev, args)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(cfg, dicts, args)
@@ -389,7 +391,7 @@ def cpu_baseline(cfg, dicts, args):
     sec = one()
     return {"value": cfg.batch * cfg.n_neurons * t_sample / sec, "unit": UNIT,
             "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"fwd+bwd of {t_sample} of the 500 simulated ms, batch {cfg.batch}, "
+            "sample": f"fwd+bwd of {t_sample} of the {cfg.seq_len} simulated ms, batch {cfg.batch}, "
                       f"N={cfg.n_neurons}, torch CPU restatement of the reference cell (oracle/)"}
 
 
@@ -410,6 +412,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="C4", choices=["C4", "C5", "C2"],
+                    help="C4 = the metric's configuration (default); C5 = 230,924-neuron stress; C2 = 5,000 neurons")
     ap.add_argument("--seq-len", type=int, default=0, help="override T of the training step")
     ap.add_argument("--fwd-seq-len", type=int, default=0, help="override T of the forward-only leg")
     ap.add_argument("--cpu-sample-steps", type=int, default=6)
