@@ -223,7 +223,8 @@ int v1g_rollout_fwd_host(V1GHandle* h, int32_t batch, int32_t n_steps, const uin
 /* BPTT over the saved rollout (tape.gradient in multi_training.py:493).  The loss is the
  * in-kernel specification plus optional explicit gradients g_z[B,T,N], g_v[B,T,N] (nullable).
  * Weight gradients are ACCUMULATED into d_w_* (caller zeroes them), each in its source's synapse
- * order; any may be NULL.  loss_out[4] (device, nullable) = total, rate, voltage, synchrony. */
+ * order; any may be NULL.  The initial state of the saved rollout is a constant (no gradient is
+ * returned for it), but spikes pending in its z_buf do contribute to d_w_rec.  loss_out[4] (device, nullable) = total, rate, voltage, synchrony. */
 int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const float* g_z, const float* g_v,
                     float* d_w_rec, float* d_w_lgn, float* d_w_bkg, float* loss_out, void* stream);
 

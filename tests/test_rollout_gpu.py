@@ -182,6 +182,33 @@ def test_bptt_batch_of_five(options):
         assert rel_err(got, want) <= TOL_GRAD
 
 
+def test_bptt_from_carried_state_counts_pending_spikes():
+    """Training from a carried state (the reference starts each step from its gray-screen state,
+    multi_training.py:812-831): the state is a constant, but spikes still travelling in its z_buf
+    reach their targets inside the rollout and belong in the recurrent weight gradient."""
+    cfg, dicts, orc, cell = _cells("small", **KW)
+    x, c = make_inputs(cfg, seq_len=50)
+    xo, co = torch.from_numpy(x), torch.from_numpy(c).long()
+    with torch.no_grad():
+        _, _, mid = orc.rollout(xo[:, :20], co[:, :20])
+    assert float(mid[0].sum()) > 0                                  # spikes are pending
+    z2, v2, _ = orc.rollout(xo[:, 20:], co[:, 20:], state=tuple(t.detach() for t in mid))
+    g = torch.Generator().manual_seed(5)
+    g_z = torch.randn(z2.shape, generator=g) * 1e-2
+    g_v = torch.randn(v2.shape, generator=g) * 1e-3
+    ((z2 * g_z).sum() + (v2 * g_v).sum()).backward()
+    want = [orc.recurrent_weight_values.grad, orc.input_weight_values.grad, orc.bkg_input_weights.grad]
+    xg, cg = torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda()
+    state = cell.zero_state(cfg.batch)
+    cell.rollout(xg[:, :20].contiguous(), cg[:, :20].contiguous(), state=state, return_v=False)
+    z, _ = cell.rollout(xg[:, 20:].contiguous(), cg[:, 20:].contiguous(), state=state, save_for_bwd=True)
+    assert torch.equal(z.cpu().float(), z2.detach())
+    grads = cell.backward(None, g_z=g_z.cuda(), g_v=g_v.cuda())
+    cell.synchronize()
+    for got, w in zip(grads[:3], want):
+        assert rel_err(got, w) <= TOL_GRAD
+
+
 def test_bptt_with_explicit_output_gradients():
     """dL/dz and dL/dv supplied as tensors (the general tape.gradient form), no in-kernel loss."""
     cfg, dicts, orc, cell = _cells("small", **KW)

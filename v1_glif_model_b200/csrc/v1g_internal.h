@@ -87,6 +87,9 @@ struct V1GHandle {
   float* tape_v = nullptr;    // [T][B][N]
   uint8_t* tape_zr = nullptr;  // [T][B][N] bit0 spike, bit1 refractory
   int64_t tape_cap = 0;
+  uint8_t* tape_hist0 = nullptr;  // [B][N] spike-history bits of the initial z_buf of the saved rollout
+  int64_t tape_hist0_cap = 0;
+  bool tape_has_hist0 = false;
   int tape_B = 0, tape_T = 0;
   bool tape_valid = false;
   const int32_t* tape_counts = nullptr;  // caller's bkg counts of the saved rollout

@@ -47,6 +47,7 @@ struct BwdArgs {
   // saved forward
   const float* tape_v;
   const uint8_t* tape_zr;
+  const uint8_t* hist0;  // initial spike-history bits [B][N], or NULL for a zero initial state
   const int32_t* lgn_off;
   const uint32_t* lgn_entries;
   int lgn_nseg;
@@ -582,6 +583,46 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   __syncthreads();
   ok = ok && !s_misc[1];
   if (ok && T >= 1) lgn_dw(0);
+  // Spikes that were pending in the initial z_buf (emitted at step -(kb+1), bit kb) are delivered
+  // at steps 0..D-1 and contribute to the recurrent weight gradient; Q(0..D-1) is still in the ring.
+  if (ok && a.hist0) {
+    for (int k = warp; k < cn; k += NW) {
+      const int32_t* rp = rp_s + k * D;
+      const int j0 = rp[0], j1 = rp[D];
+      for (int b = 0; b < B; ++b) {
+        const unsigned hbits = a.hist0[(int64_t)b * N + n0 + k];
+        if (!hbits) continue;
+        for (int j = j0 + lane; j < j1; j += 32) {
+          int d = 1;
+          for (int q = 1; q < D; ++q) d += (j >= rp[q]) ? 1 : 0;
+          const int post = a.rec_post[j], sid = a.rec_sid[j];
+          float dwv = 0.f;
+          for (int kb = 0; kb < D; ++kb) {
+            const int sstep = d - (kb + 1);
+            if (!(hbits & (1u << kb)) || sstep < 0 || sstep >= T) continue;
+            const float* Qp = a.Q + ((int64_t)(sstep % K) * Np + post) * C * QW;
+            float pj[BP_];
+            if (PROJ) {
+              load_row<BP_, PACK>(Qp + sid * QW, pj);
+            } else {
+#pragma unroll
+              for (int bb = 0; bb < BP_; ++bb) pj[bb] = 0.f;
+#pragma unroll
+              for (int r = 0; r < R_; ++r) {
+                float q[BP_];
+                load_row<BP_, PACK>(Qp + r * QW, q);
+#pragma unroll
+                for (int bb = 0; bb < BP_; ++bb) pj[bb] += q[bb] * basis_s[sid * R_ + r];
+              }
+            }
+#pragma unroll
+            for (int bb = 0; bb < BP_; ++bb) dwv += (bb == b) ? pj[bb] : 0.f;
+          }
+          if (dwv != 0.f) a.dw_rec[j] += dwv;
+        }
+      }
+    }
+  }
   if (a.bkg_in_smem)
     for (int j = tid; j < bk_m; j += NT) a.dw_bkg[bk_base + j] += bk_dw_s[j];
 
@@ -878,6 +919,7 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   a.hard_reset = (c.flags & V1G_FLAG_HARD_RESET) ? 1 : 0;
   a.csr_evict_first = h->opt_csr_evict_first;
   a.tape_v = h->tape_v; a.tape_zr = h->tape_zr;
+  a.hist0 = h->tape_has_hist0 ? h->tape_hist0 : nullptr;
   a.lgn_off = h->lgn_offsets; a.lgn_entries = h->lgn_entries; a.lgn_nseg = h->lgn_nseg;
   a.bkg_counts = h->tape_counts;
   a.rate_coef = want_rate ? rate_coef : nullptr;

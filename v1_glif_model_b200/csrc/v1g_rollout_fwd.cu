@@ -24,6 +24,18 @@ namespace {
 
 constexpr int NT = 768;
 
+// bit d-1 of hist0[b*N+n] = neuron n of batch row b spiked d steps before the rollout starts
+__global__ void __launch_bounds__(256) hist0_kernel(const float* __restrict__ z_buf, int B, int D, int N,
+                                                    uint8_t* __restrict__ hist0) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)B * N) return;
+  const int b = (int)(i / N), n = (int)(i - (int64_t)b * N);
+  unsigned hbits = 0;
+  for (int d = 0; d < D; ++d)
+    if (z_buf[((int64_t)b * D + d) * N + n] > 0.f) hbits |= 1u << d;
+  hist0[i] = (uint8_t)hbits;
+}
+
 template <int R_>
 __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -542,6 +554,13 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
       V1G_CUDA(h, cudaMalloc((void**)&h->tape_zr, (size_t)need));
       h->tape_cap = need;
     }
+  }
+  h->tape_has_hist0 = false;
+  if (save_for_bwd && state) {
+    if ((rc = v1g_reserve(h, &h->tape_hist0, &h->tape_hist0_cap, (int64_t)B * N))) return rc;
+    hist0_kernel<<<(unsigned)(((int64_t)B * N + 255) / 256), 256, 0, st>>>(state->z_buf, B, D, N, h->tape_hist0);
+    v1g_count_launches(1);
+    h->tape_has_hist0 = true;
   }
   V1G_CUDA(h, cudaMemsetAsync(h->ring, 0, (size_t)ring_elems * sizeof(float), st));
   V1G_CUDA(h, cudaMemsetAsync(h->barrier, 0, V1G_BARRIER_BYTES, st));
