@@ -243,6 +243,13 @@ int v1g_get_counters(V1GHandle* h, V1GCounters* out_host);
  * op reports errors by raising from session.run. */
 int v1g_synchronize(V1GHandle* h, void* stream);
 
+/* Failure-path check without a fault: launches one thread that waits, with the bounded-wait
+ * helper of the rollout kernels, for a counter nothing increments.  After `polls` polls it gives
+ * up, records the device status and returns normally; the next v1g_synchronize then reports
+ * V1G_ETIMEOUT and clears the status, and the handle stays usable.  No counterpart in the
+ * reference. */
+int v1g_selftest_bounded_wait(V1GHandle* h, long long polls, void* stream);
+
 /* Tuning knobs, mainly for tests: "rollout_chunk" (neurons per thread block in the rollout
  * kernels, multiple of 32, 0 = automatic), "state_in_global" (1 = keep the rollout state in
  * global memory even when it fits in shared memory), "spin_limit" (iterations a grid-barrier wait

@@ -233,6 +233,22 @@ def test_backward_without_saved_forward_is_an_error():
         cell.backward(None)
 
 
+def test_bounded_wait_reports_timeout_and_handle_survives():
+    """A device-side wait that can never be satisfied gives up after its poll limit, the host sees
+    V1G_ETIMEOUT, and the same handle then runs a rollout normally (no trap, no hang)."""
+    import ctypes as C
+    from v1_glif_model_b200._lib import ETIMEOUT, V1GError
+    cfg, dicts, orc, cell = _cells("tiny")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert cell._lib.v1g_selftest_bounded_wait(cell._libh, 2000, stream) == 0
+    with pytest.raises(V1GError) as err:
+        cell.synchronize()
+    assert err.value.code == ETIMEOUT
+    cell.synchronize()                      # status was cleared
+    x, c = make_inputs(cfg)
+    _compare_rollout(cfg, orc, cell, x, c)  # the handle still works
+
+
 def test_training_step_updates_weights_with_sign_constraint():
     from v1_glif_model_b200.training import Trainer
     cfg, dicts, orc, cell = _cells("small", **KW)

@@ -68,6 +68,7 @@ SIGNATURES = {
                                      C.c_float, C.c_float, C.c_int64, C.c_float, _P]),
     "v1g_get_counters": (C.c_int, [_P, C.POINTER(V1GCounters)]),
     "v1g_synchronize": (C.c_int, [_P, _P]),
+    "v1g_selftest_bounded_wait": (C.c_int, [_P, C.c_longlong, _P]),
     "v1g_set_option": (C.c_int, [_P, C.c_char_p, C.c_longlong]),
     "v1g_last_kernel_ms": (C.c_int, [_P, C.c_int, C.POINTER(C.c_float)]),
     "v1g_launch_count": (C.c_longlong, []),

@@ -104,6 +104,7 @@ static void free_source(V1GSource& s) {
   cudaFree(s.w);
   cudaFree(s.sid);
   cudaFree(s.perm);
+  cudaFree(s.meta);
   cudaFree(s.in_ptr);
   cudaFree(s.in_pre);
   cudaFree(s.in_sid);
@@ -215,7 +216,9 @@ extern "C" int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz,
   }
   // Device CSR with the delay buckets of a source neuron made contiguous.
   std::vector<int32_t> rowptr((size_t)n_source_cols + 1), post((size_t)nnz), perm((size_t)nnz);
-  std::vector<uint8_t> sid((size_t)nnz);
+  std::vector<uint8_t> sid((size_t)nnz), meta;
+  const bool want_meta = S <= 32 && D <= 8;
+  if (want_meta) meta.resize((size_t)nnz);
   int64_t pos = 0;
   for (int64_t src = 0; src < n_src; ++src) {
     for (int d = 0; d < D; ++d) {
@@ -225,6 +228,7 @@ extern "C" int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz,
         const int32_t i = s.order_host[(size_t)q];
         post[(size_t)pos] = (int32_t)indices_host[2 * (int64_t)i];
         sid[(size_t)pos] = syn_ids_host[i];
+        if (want_meta) meta[(size_t)pos] = (uint8_t)(syn_ids_host[i] | (d << 5));
         perm[(size_t)pos] = i;
         ++pos;
       }
@@ -261,6 +265,7 @@ extern "C" int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz,
   if ((rc = upload(h, &s.post, post.data(), post.size()))) return rc;
   if ((rc = upload(h, &s.sid, sid.data(), sid.size()))) return rc;
   if ((rc = upload(h, &s.perm, perm.data(), perm.size()))) return rc;
+  if (want_meta && (rc = upload(h, &s.meta, meta.data(), meta.size()))) return rc;
   if ((rc = upload(h, &s.in_ptr, in_ptr.data(), in_ptr.size()))) return rc;
   if ((rc = upload(h, &s.in_pre, in_pre.data(), in_pre.size()))) return rc;
   if ((rc = upload(h, &s.in_sid, in_sid.data(), in_sid.size()))) return rc;
@@ -415,6 +420,8 @@ extern "C" int v1g_set_option(V1GHandle* h, const char* name, long long value) {
     h->opt_force_global = value != 0;
   } else if (!strcmp(name, "force_smem_kernel")) {
     h->opt_force_smem_kernel = value != 0;
+  } else if (!strcmp(name, "no_meta")) {
+    h->opt_no_meta = value != 0;
   } else if (!strcmp(name, "no_q_pack")) {
     h->opt_no_q_pack = value != 0;
   } else if (!strcmp(name, "l2_window")) {

@@ -36,6 +36,7 @@ struct BwdArgs {
   const int32_t *rec_rowptr, *rec_post;
   const float* rec_w;
   const uint8_t* rec_sid;
+  const uint8_t* rec_meta;  // sid | (delay-1) << 5 per synapse, or NULL
   const int32_t *lgn_rowptr, *lgn_post;
   const uint8_t* lgn_sid;
   const int32_t *bkg_inptr, *bkg_inpre;
@@ -338,7 +339,12 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       for (int u = 0; u < U; ++u) {
         const int j = jb + u * 32 + lane;
         const bool v = j < j1;
-        if (a.csr_evict_first) {
+        if (a.rec_meta) {
+          // one byte carries the synapse type and the delay bucket
+          post[u] = v ? __ldcs(a.rec_post + j) : 0;
+          sid[u] = v ? (int)__ldcs(a.rec_meta + j) : 0;
+          w[u] = v ? __ldcs(a.rec_w + j) : 0.f;
+        } else if (a.csr_evict_first) {
           post[u] = v ? __ldcs(a.rec_post + j) : 0;
           sid[u] = v ? (int)__ldcs(a.rec_sid + j) : 0;
           w[u] = v ? __ldcs(a.rec_w + j) : 0.f;
@@ -378,8 +384,13 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           const int j = jb + u * 32 + lane;
           valid[u] = j < j1;
           int d = 1;
+          if (a.rec_meta) {
+            d += csid[u] >> 5;
+            csid[u] &= 31;
+          } else {
 #pragma unroll
-          for (int q = 1; q < DMAX; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
+            for (int q = 1; q < DMAX; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
+          }
           if (t + d >= T) valid[u] = false;  // no step after the rollout's end
           slot[u] = tk + d;
           if (slot[u] >= K) slot[u] -= K;
@@ -905,6 +916,7 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   const V1GSource& lsrc = h->src[V1G_SRC_LGN];
   const V1GSource& bk = h->src[V1G_SRC_BKG];
   a.rec_rowptr = rs.rowptr; a.rec_post = rs.post; a.rec_w = rs.w; a.rec_sid = rs.sid;
+  a.rec_meta = h->opt_no_meta ? nullptr : rs.meta;
   a.lgn_rowptr = lsrc.rowptr; a.lgn_post = lsrc.post; a.lgn_sid = lsrc.sid;
   a.bkg_inptr = bk.in_ptr; a.bkg_inpre = bk.in_pre; a.bkg_insid = bk.in_sid;
   a.decay = h->decay; a.cf = h->cf; a.asc_decay = h->asc_decay; a.basis = h->basis;

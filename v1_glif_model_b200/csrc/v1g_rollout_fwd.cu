@@ -472,6 +472,24 @@ size_t v1g_plan_rollout(const V1GHandle* h, int B, int per_item_floats, int per_
   return p->fixed_bytes;
 }
 
+namespace {
+// One thread waits, with the same bounded-wait helper the rollout kernels use, for a counter that
+// nothing increments.
+__global__ void bounded_wait_probe_kernel(unsigned long long* counter, long long polls, int32_t* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) v1g_wait(counter, 1ULL, polls, status);
+}
+}  // namespace
+
+extern "C" int v1g_selftest_bounded_wait(V1GHandle* h, long long polls, void* stream) {
+  if (!h || polls < 1 || polls > 100000000LL) return h ? v1g_fail(h, V1G_EINVAL, "polls outside 1..1e8") : V1G_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  V1G_CUDA(h, cudaMemsetAsync(h->barrier, 0, V1G_BARRIER_BYTES, st));
+  bounded_wait_probe_kernel<<<1, 32, 0, st>>>(h->barrier, polls, h->dev_status);
+  v1g_count_launches(1);
+  V1G_CUDA(h, cudaGetLastError());
+  return V1G_OK;
+}
+
 extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x,
                                const int32_t* bkg_counts, V1GState* state, uint8_t* z_out,
                                float* v_out, int32_t save_for_bwd, void* stream) {
