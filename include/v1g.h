@@ -235,6 +235,32 @@ int v1g_expadam_update(float* w, const float* grad, float* m, float* v, const ui
                        int64_t n, float lr, float beta1, float beta2, float eps, int64_t step,
                        float grad_scale, void* stream);
 
+/* ---- training in the library's own synapse order ---------------------------------------------
+ * The reference's training step (multi_training.py:483-520) is tape.gradient -> cross-replica sum
+ * -> ExponentiatedAdam.update_step -> SignedConstraint -> refresh of the compute copy.  These
+ * entry points do the same without converting gradients and weights to the caller's synapse
+ * order and back every step: gradients, moments and the update live in the internal order
+ * (presynaptic CSR for the recurrent and LGN sources, post-major table for the background), which
+ * is identical on every replica with the same connectivity, so one flat buffer can be all-reduced
+ * as it is.  v1g_get_weights converts back whenever the caller wants the weights. */
+
+/* sizes3[s] = number of synapses of source s; the flat buffers below are [rec | lgn | bkg]. */
+int v1g_train_layout(V1GHandle* h, int64_t* sizes3);
+
+/* v1g_rollout_bwd with the three weight gradients ACCUMULATED into grads_flat in internal order. */
+int v1g_rollout_bwd_internal(V1GHandle* h, const V1GLossSpec* loss, const float* g_z,
+                             const float* g_v, float* grads_flat, float* loss_out, void* stream);
+
+/* Exp-Adam + sign constraint (optimizers.py:353-376, models.py:419-427) on the sources whose bit
+ * is set in train_mask (bit 0 recurrent, 1 LGN, 2 background), in place on the weights the
+ * kernels read.  The sign mask is the sign of each weight at the first v1g_set_weights call. */
+int v1g_expadam_update_internal(V1GHandle* h, const float* grads_flat, float* m_flat, float* v_flat,
+                                int32_t train_mask, float lr, float beta1, float beta2, float eps,
+                                int64_t step, float grad_scale, void* stream);
+
+/* Current weights of a source in the caller's synapse order (device pointer, [nnz]). */
+int v1g_get_weights(V1GHandle* h, int source, float* w_out, void* stream);
+
 int v1g_get_counters(V1GHandle* h, V1GCounters* out_host);
 
 /* Waits for `stream` and returns the device-side status of the launches since the last call:

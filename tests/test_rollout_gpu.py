@@ -259,10 +259,31 @@ def test_training_step_updates_weights_with_sign_constraint():
     w0 = cell.recurrent_weight_values.clone()
     l0 = tr.step(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda())
     cell.synchronize()
-    w1 = cell.recurrent_weight_values
+    w1 = tr.weights()[0]
     assert not torch.equal(w0, w1)
     assert torch.all((w1 >= 0) == cell.recurrent_weight_positive | (w1 == 0))
     assert torch.isfinite(l0).all()
+
+
+def test_internal_order_training_equals_reference_order_training():
+    """Two optimiser steps in the kernels' own synapse order give the weights that the same steps
+    give through the caller's order (permute -> Exp-Adam -> permute back)."""
+    from v1_glif_model_b200.training import Trainer
+    results = []
+    for order in ("reference", "internal"):
+        cfg, dicts, orc, cell = _cells("small", **KW)
+        x, c = make_inputs(cfg)
+        tgt = torch.from_numpy(synth.make_rate_targets(cfg)).cuda() / 1000.0
+        vlo = torch.from_numpy((-20.0 / cell.voltage_scale).astype(np.float32)).cuda()
+        tr = Trainer(cell, dict(LOSS, rate_target=tgt, v_lo=vlo), learning_rate=5e-3,
+                     train_input=True, train_noise=True, order=order)
+        for _ in range(2):
+            losses = tr.step(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda())
+        cell.synchronize()
+        results.append([w.clone() for w in tr.weights()] + [losses.clone()])
+    for a, b in zip(results[0][:3], results[1][:3]):
+        assert rel_err(b, a) <= 1e-5
+    assert rel_err(results[1][3], results[0][3]) <= 1e-5
 
 
 def test_full_size_column_properties():

@@ -105,6 +105,7 @@ static void free_source(V1GSource& s) {
   cudaFree(s.sid);
   cudaFree(s.perm);
   cudaFree(s.meta);
+  cudaFree(s.pos_int);
   cudaFree(s.in_ptr);
   cudaFree(s.in_pre);
   cudaFree(s.in_sid);
@@ -341,6 +342,20 @@ extern "C" int v1g_set_neuron_params(V1GHandle* h, const float* decay, const flo
   return V1G_OK;
 }
 
+__global__ void sign_mask_kernel(const float* __restrict__ w, uint8_t* __restrict__ pos, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) pos[i] = w[i] >= 0.f ? 1 : 0;
+}
+
+// dst[perm[i]] = src[i]  (perm == nullptr: plain copy)
+__global__ void unpermute_kernel(const float* __restrict__ src, const int32_t* __restrict__ perm,
+                                 float* __restrict__ dst, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) dst[perm ? perm[i] : i] = src[i];
+}
+
 __global__ void permute_weights_kernel(const float* __restrict__ w_ref,
                                        const int32_t* __restrict__ perm, float* __restrict__ w,
                                        int64_t nnz) {
@@ -365,6 +380,69 @@ extern "C" int v1g_set_weights(V1GHandle* h, int source, const float* w, void* s
   if (s.in_perm) {
     permute_weights_kernel<<<blocks, threads, 0, st>>>(s.w_ref, s.in_perm, s.w_in, s.nnz);
     v1g_count_launches(1);
+  }
+  if (!s.pos_set) {
+    // the sign of each weight at construction is what SignedConstraint preserves (models.py:647-666)
+    if (!s.pos_int) V1G_CUDA(h, cudaMalloc((void**)&s.pos_int, (size_t)s.nnz));
+    const float* w_int = (source == V1G_SRC_BKG) ? s.gather_w() : s.w;
+    sign_mask_kernel<<<blocks, threads, 0, st>>>(w_int, s.pos_int, s.nnz);
+    v1g_count_launches(1);
+    s.pos_set = true;
+  }
+  V1G_CUDA(h, cudaGetLastError());
+  return V1G_OK;
+}
+
+extern "C" int v1g_train_layout(V1GHandle* h, int64_t* sizes3) {
+  if (!h || !sizes3) return V1G_EINVAL;
+  for (int s = 0; s < V1G_NSRC; ++s) sizes3[s] = h->src[s].nnz;
+  return V1G_OK;
+}
+
+extern "C" int v1g_get_weights(V1GHandle* h, int source, float* w_out, void* stream) {
+  if (!h || !w_out) return V1G_EINVAL;
+  if (source < 0 || source >= V1G_NSRC) return v1g_fail(h, V1G_EINVAL, "unknown source %d", source);
+  V1GSource& s = h->src[source];
+  if (!s.rowptr) return v1g_fail(h, V1G_ESTATE, "connectivity of source %d not set", source);
+  if (s.nnz == 0) return V1G_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int blocks = (int)std::min<int64_t>((s.nnz + 255) / 256, 148 * 16);
+  if (source == V1G_SRC_BKG)
+    unpermute_kernel<<<blocks, 256, 0, st>>>(s.gather_w(), s.in_perm, w_out, s.nnz);
+  else
+    unpermute_kernel<<<blocks, 256, 0, st>>>(s.w, s.perm, w_out, s.nnz);
+  v1g_count_launches(1);
+  V1G_CUDA(h, cudaGetLastError());
+  return V1G_OK;
+}
+
+extern "C" int v1g_expadam_update_internal(V1GHandle* h, const float* grads_flat, float* m_flat,
+                                           float* v_flat, int32_t train_mask, float lr, float beta1,
+                                           float beta2, float eps, int64_t step, float grad_scale,
+                                           void* stream) {
+  if (!h || !grads_flat || !m_flat || !v_flat) return V1G_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  int64_t off = 0;
+  for (int src = 0; src < V1G_NSRC; ++src) {
+    V1GSource& s = h->src[src];
+    if (((train_mask >> src) & 1) && s.nnz > 0) {
+      if (!s.pos_set) return v1g_fail(h, V1G_ESTATE, "weights of source %d not set", src);
+      float* w_int = (src == V1G_SRC_BKG) ? s.gather_w_mut() : s.w;
+      int rc = v1g_expadam_update(w_int, grads_flat + off, m_flat + off, v_flat + off, s.pos_int, s.nnz,
+                                  lr, beta1, beta2, eps, step, grad_scale, stream);
+      if (rc) return v1g_fail(h, rc, "v1g_expadam_update failed for source %d", src);
+      if (src == V1G_SRC_BKG) {
+        // the background weights also exist in caller's and CSR order (operator-level entry points)
+        const int blocks = (int)std::min<int64_t>((s.nnz + 255) / 256, 148 * 16);
+        if (s.in_perm) {
+          unpermute_kernel<<<blocks, 256, 0, st>>>(s.w_in, s.in_perm, s.w_ref, s.nnz);
+          v1g_count_launches(1);
+        }
+        permute_weights_kernel<<<blocks, 256, 0, st>>>(s.w_ref, s.perm, s.w, s.nnz);
+        v1g_count_launches(1);
+      }
+    }
+    off += s.nnz;
   }
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;

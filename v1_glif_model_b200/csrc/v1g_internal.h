@@ -29,6 +29,8 @@ struct V1GSource {
   float* w = nullptr;         // [nnz] weights in CSR order
   uint8_t* sid = nullptr;     // [nnz]
   int32_t* perm = nullptr;    // [nnz] CSR position -> position in the caller's arrays
+  uint8_t* pos_int = nullptr; // [nnz] sign mask (w >= 0 at the first v1g_set_weights), internal order
+  bool pos_set = false;
   uint8_t* meta = nullptr;    // [nnz] sid | (delay-1) << 5, only when there are at most 32 synapse types
   // post-major table in the caller's order (the reference sorts synapses by post, so this is a
   // plain row pointer over the caller's arrays)
@@ -42,6 +44,7 @@ struct V1GSource {
   float* w_in = nullptr;
   bool post_sorted = false;
   const float* gather_w() const { return in_perm ? w_in : w_ref; }
+  float* gather_w_mut() { return in_perm ? w_in : w_ref; }
   // host copy of the reference-numbered table for v1g_get_pre_ind_table
   std::vector<int32_t> order_host;
   std::vector<int64_t> row_splits_host;

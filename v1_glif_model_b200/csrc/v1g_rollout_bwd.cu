@@ -812,9 +812,12 @@ int launch_bwd_r(V1GHandle* h, const BwdArgs& a, int BP, bool proj, bool pack, i
 
 }  // namespace
 
-extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const float* g_z,
-                               const float* g_v, float* d_w_rec, float* d_w_lgn, float* d_w_bkg,
-                               float* loss_out, void* stream) {
+// internal_order: d_w_* are buffers in the library's own synapse order (presynaptic CSR for the
+// recurrent and LGN sources, gather-table order for the background) that the kernel accumulates
+// into directly; otherwise they are in the caller's order and filled through a permutation.
+static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* g_z, const float* g_v,
+                            float* d_w_rec, float* d_w_lgn, float* d_w_bkg, float* loss_out,
+                            bool internal_order, void* stream) {
   if (!h) return V1G_EINVAL;
   if (!h->tape_valid)
     return v1g_fail(h, V1G_ESTATE, "v1g_rollout_bwd needs a preceding v1g_rollout_fwd with save_for_bwd");
@@ -883,10 +886,13 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   float* sgrad = rate_coef + N;
   int* spike_count = (int*)(sgrad + (int64_t)B * std::max(nbins, 1));
   int* popcount = spike_count + N;
+  float* dw_int[V1G_NSRC] = {d_w_rec, d_w_lgn, d_w_bkg};
   for (int s = 0; s < V1G_NSRC; ++s) {
+    if (internal_order && dw_int[s]) continue;  // the caller's buffer is accumulated into directly
     const int64_t nnz = std::max<int64_t>(h->src[s].nnz, 1);
     if (!h->dw_csr[s]) V1G_CUDA(h, cudaMalloc((void**)&h->dw_csr[s], (size_t)nnz * sizeof(float)));
     V1G_CUDA(h, cudaMemsetAsync(h->dw_csr[s], 0, (size_t)nnz * sizeof(float), st));
+    dw_int[s] = h->dw_csr[s];
   }
   V1G_CUDA(h, cudaMemsetAsync(h->loss_scratch, 0, (size_t)ls_elems * sizeof(float), st));
   V1G_CUDA(h, cudaMemsetAsync(h->dy_ring, 0, (size_t)q_elems * sizeof(float), st));
@@ -940,7 +946,7 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   a.volt_coef = ls.voltage_cost * ls.loss_scale / ((float)B * (float)T * (float)N);
   a.v_lo = ls.v_lo;
   a.g_z = g_z; a.g_v = g_v;
-  a.dw_rec = h->dw_csr[V1G_SRC_REC]; a.dw_lgn = h->dw_csr[V1G_SRC_LGN]; a.dw_bkg = h->dw_csr[V1G_SRC_BKG];
+  a.dw_rec = dw_int[V1G_SRC_REC]; a.dw_lgn = dw_int[V1G_SRC_LGN]; a.dw_bkg = dw_int[V1G_SRC_BKG];
   a.loss_acc = acc;
   a.Q = h->dy_ring; a.state_ws = h->state_ws;
   a.barrier = h->barrier; a.status = h->dev_status; a.counters = h->counters;
@@ -984,6 +990,12 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
 
   // weight gradients back to the caller's synapse order, accumulated
   const int blocks = h->n_sms * 8;
+  if (internal_order) {
+    finish_loss_kernel<<<1, 32, 0, st>>>(acc, loss_out);
+    v1g_count_launches(1);
+    V1G_CUDA(h, cudaGetLastError());
+    return V1G_OK;
+  }
   if (d_w_rec && rs.nnz) permute_add_kernel<<<blocks, 256, 0, st>>>(h->dw_csr[V1G_SRC_REC], rs.perm, d_w_rec, rs.nnz);
   if (d_w_lgn && lsrc.nnz) permute_add_kernel<<<blocks, 256, 0, st>>>(h->dw_csr[V1G_SRC_LGN], lsrc.perm, d_w_lgn, lsrc.nnz);
   if (d_w_bkg && bk.nnz) permute_add_kernel<<<blocks, 256, 0, st>>>(h->dw_csr[V1G_SRC_BKG], bk.in_perm, d_w_bkg, bk.nnz);
@@ -991,4 +1003,21 @@ extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const floa
   v1g_count_launches(1 + ((d_w_rec && rs.nnz) ? 1 : 0) + ((d_w_lgn && lsrc.nnz) ? 1 : 0) + ((d_w_bkg && bk.nnz) ? 1 : 0));
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;
+}
+
+extern "C" int v1g_rollout_bwd(V1GHandle* h, const V1GLossSpec* loss, const float* g_z,
+                               const float* g_v, float* d_w_rec, float* d_w_lgn, float* d_w_bkg,
+                               float* loss_out, void* stream) {
+  return rollout_bwd_impl(h, loss, g_z, g_v, d_w_rec, d_w_lgn, d_w_bkg, loss_out, false, stream);
+}
+
+extern "C" int v1g_rollout_bwd_internal(V1GHandle* h, const V1GLossSpec* loss, const float* g_z,
+                                        const float* g_v, float* grads_flat, float* loss_out,
+                                        void* stream) {
+  if (!h) return V1G_EINVAL;
+  if (!grads_flat) return v1g_fail(h, V1G_EINVAL, "v1g_rollout_bwd_internal: null gradient buffer");
+  float* g0 = grads_flat;
+  float* g1 = g0 + h->src[V1G_SRC_REC].nnz;
+  float* g2 = g1 + h->src[V1G_SRC_LGN].nnz;
+  return rollout_bwd_impl(h, loss, g_z, g_v, g0, g1, g2, loss_out, true, stream);
 }

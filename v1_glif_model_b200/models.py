@@ -241,6 +241,38 @@ class V1Column:
 
     refresh_recurrent_weight_shadow = refresh_weights
 
+    def pull_weights(self):
+        """Copy the weights the kernels currently use back into the three weight tensors (needed
+        after updates made in the library's internal order, see ``training.Trainer``)."""
+        for src, w in ((_lib.SRC_REC, self.recurrent_weight_values),
+                       (_lib.SRC_LGN, self.input_weight_values),
+                       (_lib.SRC_BKG, self.bkg_input_weights)):
+            self._check(self._lib.v1g_get_weights(self._libh, src, _ptr(w), _stream()))
+
+    def train_layout(self):
+        sizes = (C.c_int64 * 3)()
+        self._check(self._lib.v1g_train_layout(self._libh, sizes))
+        return [int(v) for v in sizes]
+
+    def _loss_spec(self, loss):
+        loss = dict(loss or {})
+        return _lib.V1GLossSpec(
+            rate_target=loss["rate_target"].data_ptr() if loss.get("rate_target") is not None else None,
+            v_lo=loss["v_lo"].data_ptr() if loss.get("v_lo") is not None else None,
+            rate_cost=loss.get("rate_cost", 0.0), voltage_cost=loss.get("voltage_cost", 0.0),
+            sync_cost=loss.get("sync_cost", 0.0), fano_target=loss.get("fano_target", 1.0),
+            sync_bin=int(loss.get("sync_bin", 50)), loss_scale=loss.get("loss_scale", 1.0))
+
+    def backward_internal(self, loss, grads_flat, losses=None):
+        """BPTT with the gradients accumulated into ``grads_flat`` ([rec | lgn | bkg]) in the
+        library's internal synapse order."""
+        spec = self._loss_spec(loss)
+        if losses is None:
+            losses = torch.zeros((4,), dtype=torch.float32, device=self.device)
+        self._check(self._lib.v1g_rollout_bwd_internal(self._libh, C.byref(spec), None, None,
+                                                       _ptr(grads_flat), _ptr(losses), _stream()))
+        return losses
+
     def _state_struct(self, state):
         z_buf, v, r, asc, psc_rise, psc = state[:6]
         for t in (z_buf, v, r, asc, psc_rise, psc):

@@ -79,11 +79,19 @@ class ExponentiatedAdam:
 
 
 class Trainer:
-    """One replica of the data-parallel training loop (batch sharded over ranks)."""
+    """One replica of the data-parallel training loop (batch sharded over ranks).
+
+    ``order="internal"`` (default) keeps gradients, Adam moments and the update in the synapse
+    order of the kernels, which is the same on every replica, and skips the per-step conversions
+    to and from the caller's order; ``cell.pull_weights()`` (called by ``weights()``) converts
+    back on demand.  ``order="reference"`` goes through the caller's order every step.
+    """
 
     def __init__(self, cell, loss, learning_rate=1e-3, train_input=True, train_noise=False,
-                 group=None):
+                 group=None, order="internal"):
         self.cell = cell
+        self.order = order
+        self.lr = learning_rate
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.loss = dict(loss)
@@ -92,7 +100,13 @@ class Trainer:
         positives = [cell.recurrent_weight_positive, cell.input_weight_positive,
                      cell.bkg_input_weight_positive]
         self.trainable = [True, bool(train_input), bool(train_noise)]
-        self.grads = FlatGradients([w.numel() for w in weights], cell.device)
+        self.grads = FlatGradients(cell.train_layout(), cell.device)
+        self.train_mask = sum(1 << i for i, t in enumerate(self.trainable) if t)
+        if order == "internal":
+            self.m = torch.zeros_like(self.grads.flat)
+            self.v = torch.zeros_like(self.grads.flat)
+            self.iterations = 0
+            self._losses = torch.zeros((4,), dtype=torch.float32, device=cell.device)
         sel = [i for i, t in enumerate(self.trainable) if t]
         self.opt = ExponentiatedAdam([weights[i] for i in sel], [positives[i] for i in sel],
                                      learning_rate=learning_rate)
@@ -102,8 +116,25 @@ class Trainer:
         """Forward rollout, BPTT, gradient all-reduce, Exp-Adam update.  Returns losses[4]."""
         self.grads.zero_()
         self.cell.rollout(x, bkg_counts, return_z=False, return_v=False, save_for_bwd=True)
+        if self.order == "internal":
+            cell = self.cell
+            losses = cell.backward_internal(self.loss, self.grads.flat, self._losses)
+            self.grads.all_reduce(self.group)
+            self.iterations += 1
+            cell._check(cell._lib.v1g_expadam_update_internal(
+                cell._libh, self.grads.flat.data_ptr(), self.m.data_ptr(), self.v.data_ptr(),
+                self.train_mask, self.lr, 0.9, 0.999, 1e-11, self.iterations, 1.0,
+                C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            return losses
         _, _, _, losses = self.cell.backward(self.loss, accumulate_into=self.grads.views)
         self.grads.all_reduce(self.group)
         self.opt.apply_gradients([self.grads.views[i] for i in self._sel])
         self.cell.refresh_weights()
         return losses
+
+    def weights(self):
+        """The three weight tensors in the caller's synapse order, up to date."""
+        if self.order == "internal":
+            self.cell.pull_weights()
+        c = self.cell
+        return c.recurrent_weight_values, c.input_weight_values, c.bkg_input_weights
