@@ -104,7 +104,7 @@ static void free_source(V1GSource& s) {
   cudaFree(s.w);
   cudaFree(s.sid);
   cudaFree(s.perm);
-  cudaFree(s.meta);
+  cudaFree(s.syn8);
   cudaFree(s.pos_int);
   cudaFree(s.in_ptr);
   cudaFree(s.in_pre);
@@ -217,9 +217,10 @@ extern "C" int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz,
   }
   // Device CSR with the delay buckets of a source neuron made contiguous.
   std::vector<int32_t> rowptr((size_t)n_source_cols + 1), post((size_t)nnz), perm((size_t)nnz);
-  std::vector<uint8_t> sid((size_t)nnz), meta;
-  const bool want_meta = S <= 32 && D <= 8;
-  if (want_meta) meta.resize((size_t)nnz);
+  std::vector<uint8_t> sid((size_t)nnz);
+  std::vector<uint2> syn8;
+  const bool want_syn8 = source == V1G_SRC_REC && S <= 128 && D <= 8 && N < (1 << 22);
+  if (want_syn8) syn8.resize((size_t)nnz);
   int64_t pos = 0;
   for (int64_t src = 0; src < n_src; ++src) {
     for (int d = 0; d < D; ++d) {
@@ -229,7 +230,9 @@ extern "C" int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz,
         const int32_t i = s.order_host[(size_t)q];
         post[(size_t)pos] = (int32_t)indices_host[2 * (int64_t)i];
         sid[(size_t)pos] = syn_ids_host[i];
-        if (want_meta) meta[(size_t)pos] = (uint8_t)(syn_ids_host[i] | (d << 5));
+        if (want_syn8)
+          syn8[(size_t)pos] = make_uint2((uint32_t)indices_host[2 * (int64_t)i] |
+                                             ((uint32_t)syn_ids_host[i] << 22) | ((uint32_t)d << 29), 0u);
         perm[(size_t)pos] = i;
         ++pos;
       }
@@ -266,7 +269,7 @@ extern "C" int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz,
   if ((rc = upload(h, &s.post, post.data(), post.size()))) return rc;
   if ((rc = upload(h, &s.sid, sid.data(), sid.size()))) return rc;
   if ((rc = upload(h, &s.perm, perm.data(), perm.size()))) return rc;
-  if (want_meta && (rc = upload(h, &s.meta, meta.data(), meta.size()))) return rc;
+  if (want_syn8 && (rc = upload(h, &s.syn8, syn8.data(), syn8.size()))) return rc;
   if ((rc = upload(h, &s.in_ptr, in_ptr.data(), in_ptr.size()))) return rc;
   if ((rc = upload(h, &s.in_pre, in_pre.data(), in_pre.size()))) return rc;
   if ((rc = upload(h, &s.in_sid, in_sid.data(), in_sid.size()))) return rc;
@@ -364,6 +367,13 @@ __global__ void permute_weights_kernel(const float* __restrict__ w_ref,
   for (; i < nnz; i += stride) w[i] = w_ref[perm[i]];
 }
 
+// copy the weights into the packed synapse records of the backward gather
+__global__ void syn8_weights_kernel(const float* __restrict__ w, uint2* __restrict__ syn8, int64_t nnz) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < nnz; i += stride) syn8[i].y = __float_as_uint(w[i]);
+}
+
 extern "C" int v1g_set_weights(V1GHandle* h, int source, const float* w, void* stream) {
   if (!h) return V1G_EINVAL;
   if (source < 0 || source >= V1G_NSRC) return v1g_fail(h, V1G_EINVAL, "unknown source %d", source);
@@ -379,6 +389,10 @@ extern "C" int v1g_set_weights(V1GHandle* h, int source, const float* w, void* s
   v1g_count_launches(1);
   if (s.in_perm) {
     permute_weights_kernel<<<blocks, threads, 0, st>>>(s.w_ref, s.in_perm, s.w_in, s.nnz);
+    v1g_count_launches(1);
+  }
+  if (s.syn8) {
+    syn8_weights_kernel<<<blocks, threads, 0, st>>>(s.w, s.syn8, s.nnz);
     v1g_count_launches(1);
   }
   if (!s.pos_set) {
@@ -431,6 +445,11 @@ extern "C" int v1g_expadam_update_internal(V1GHandle* h, const float* grads_flat
       int rc = v1g_expadam_update(w_int, grads_flat + off, m_flat + off, v_flat + off, s.pos_int, s.nnz,
                                   lr, beta1, beta2, eps, step, grad_scale, stream);
       if (rc) return v1g_fail(h, rc, "v1g_expadam_update failed for source %d", src);
+      if (s.syn8) {
+        const int blocks = (int)std::min<int64_t>((s.nnz + 255) / 256, 148 * 16);
+        syn8_weights_kernel<<<blocks, 256, 0, st>>>(s.w, s.syn8, s.nnz);
+        v1g_count_launches(1);
+      }
       if (src == V1G_SRC_BKG) {
         // the background weights also exist in caller's and CSR order (operator-level entry points)
         const int blocks = (int)std::min<int64_t>((s.nnz + 255) / 256, 148 * 16);

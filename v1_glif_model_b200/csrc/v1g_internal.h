@@ -31,7 +31,9 @@ struct V1GSource {
   int32_t* perm = nullptr;    // [nnz] CSR position -> position in the caller's arrays
   uint8_t* pos_int = nullptr; // [nnz] sign mask (w >= 0 at the first v1g_set_weights), internal order
   bool pos_set = false;
-  uint8_t* meta = nullptr;    // [nnz] sid | (delay-1) << 5, only when there are at most 32 synapse types
+  // [nnz] packed synapse records for the backward gather (recurrent source only, when N < 2^22 and
+  // S <= 128): x = post | sid << 22 | (delay-1) << 29, y = bits of the weight (kept equal to w)
+  uint2* syn8 = nullptr;
   // post-major table in the caller's order (the reference sorts synapses by post, so this is a
   // plain row pointer over the caller's arrays)
   int32_t* in_ptr = nullptr;  // [N + 1]
@@ -114,7 +116,7 @@ struct V1GHandle {
   int opt_force_global = 0;   // keep rollout state in global memory even if it fits on chip
   long long opt_spin_limit = 4000000LL;
   int opt_force_smem_kernel = 0;  // never pick the register-resident forward kernel
-  int opt_no_meta = 0;            // derive delays from the row pointers instead of the meta byte
+  int opt_no_meta = 0;            // backward gather reads post / sid / w arrays instead of the packed records
   int opt_no_q_pack = 0;          // keep the backward Q rows in fp32 even for a batch of 5
   int opt_l2_window = 0;          // pin the backward Q ring in L2 with an access-policy window
   int opt_csr_evict_first = 1;    // read the backward synapse stream with evict-first loads

@@ -26,6 +26,7 @@
 // non-zero for non-spiking neurons), one warp per row, except rows whose B batch entries are all
 // refractory / outside the pseudo-derivative's support and did not spike (exactly zero result).
 #include <algorithm>
+#include <type_traits>
 
 #include "v1g_rollout_common.cuh"
 
@@ -36,7 +37,8 @@ struct BwdArgs {
   const int32_t *rec_rowptr, *rec_post;
   const float* rec_w;
   const uint8_t* rec_sid;
-  const uint8_t* rec_meta;  // sid | (delay-1) << 5 per synapse, or NULL
+  int rec_nnz;
+  const uint2* rec_syn8;  // packed records {post | sid << 22 | (delay-1) << 29, weight bits}, or NULL
   const int32_t *lgn_rowptr, *lgn_post;
   const uint8_t* lgn_sid;
   const int32_t *bkg_inptr, *bkg_inpre;
@@ -76,6 +78,9 @@ struct BwdArgs {
 #ifndef V1G_BWD_NT
 #define V1G_BWD_NT 512
 #endif
+#ifndef V1G_BWD_STAGES
+#define V1G_BWD_STAGES 2  // Q-row buffers of the gather pipeline (registers: 20 per stage)
+#endif
 constexpr int NT = V1G_BWD_NT;
 constexpr int NW = NT / 32;
 
@@ -112,9 +117,10 @@ __device__ __forceinline__ float4 pack_row5(const float (&v)[8]) {
   return make_float4(__uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z), __uint_as_float(w.w));
 }
 
+// the 16-byte words of a Q row -> its BP_ batch values
 template <int BP_, bool PACK>
-__device__ __forceinline__ void load_row(const float* p, float (&q)[BP_]) {
-  const float4 a = __ldcg((const float4*)p);
+__device__ __forceinline__ void unpack_row(const float4 (&raw)[PACK ? 1 : BP_ / 4], float (&q)[BP_]) {
+  const float4 a = raw[0];
   if (PACK) {
     const unsigned w0 = __float_as_uint(a.x), w1 = __float_as_uint(a.y), w2 = __float_as_uint(a.z),
                    w3 = __float_as_uint(a.w);
@@ -129,9 +135,17 @@ __device__ __forceinline__ void load_row(const float* p, float (&q)[BP_]) {
   }
   q[0] = a.x; q[1] = a.y; q[2] = a.z; q[3] = a.w;
   if (BP_ == 8) {
-    const float4 b = __ldcg((const float4*)p + 1);
+    const float4 b = raw[(BP_ / 4 - 1) % (PACK ? 1 : BP_ / 4)];
     q[4 % BP_] = b.x; q[5 % BP_] = b.y; q[6 % BP_] = b.z; q[7 % BP_] = b.w;
   }
+}
+
+template <int BP_, bool PACK>
+__device__ __forceinline__ void load_row(const float* p, float (&q)[BP_]) {
+  float4 raw[PACK ? 1 : BP_ / 4];
+#pragma unroll
+  for (int v = 0; v < (PACK ? 1 : BP_ / 4); ++v) raw[v] = __ldcg((const float4*)p + v);
+  unpack_row<BP_, PACK>(raw, q);
 }
 
 template <int R_, int BP_, bool PROJ, int DT, bool PACK>
@@ -161,7 +175,9 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   uint8_t* zmask_s = (uint8_t*)take(chunkP);           // batch rows that spiked at this step
   int* s_cnt = (int*)take(sizeof(int) * nb);
   int* s_misc = (int*)take(sizeof(int) * 4);  // [1] abort flag, [2] rows queued, [3] next queue slot
+  int* slot_s = (int*)take(sizeof(int) * 8);  // first Q row of step t+1+d, d = 0..7
   uint16_t* rowq_s = (uint16_t*)take(sizeof(uint16_t) * chunkP);  // rows to walk this step
+  int4* rowd_s = (int4*)take(sizeof(int4) * chunkP);  // the same rows as {first synapse, end, row | spike mask << 16, 0}
   int32_t* rp_s = (int32_t*)take(sizeof(int32_t) * ((size_t)chunkP * D + 1));  // row pointers of the slice
   float* c_decay = (float*)take(sizeof(float) * chunkP);  // per-neuron constants of the slice
   float* c_cf = (float*)take(sizeof(float) * chunkP);
@@ -232,36 +248,59 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   const bool prof = a.phase_ns != nullptr && tid == 0;
   const unsigned long long ph_start = prof ? gtime_b() : 0;
   const int gw = blockIdx.x * NW + warp, gnw = gridDim.x * NW;
+  const bool fast_rows = PROJ && a.rec_syn8 != nullptr;  // packed-record gather
 
-  // weight gradient of the LGN events of step tt from Q(tt)
+  // Weight gradient of the LGN events of step tt from Q(tt).  One warp per event; the (up to 128)
+  // synapses of a pass are loaded together so that the three dependent accesses (record, Q row,
+  // atomic) are each paid once per pass.
   auto lgn_dw = [&](int tt) {
     const int seg_per_t = B * a.lgn_nseg;
     const int e0 = a.lgn_off[(int64_t)tt * seg_per_t], e1 = a.lgn_off[(int64_t)(tt + 1) * seg_per_t];
     const float* Qs = a.Q + (int64_t)(tt % K) * Np * C * QW;
+    constexpr int UL = 4;
     for (int e = e0 + gw; e < e1; e += gnw) {
       const uint32_t ent = a.lgn_entries[e];
       const int b = ent >> 24, u = ent & 0xffffff;
       const int j0 = a.lgn_rowptr[u], j1 = a.lgn_rowptr[u + 1];
-      for (int j = j0 + lane; j < j1; j += 32) {
-        const int post = a.lgn_post[j], sid = a.lgn_sid[j];
-        float val = 0.f;
-        if (PROJ) {
-          float q[BP_];
-          load_row<BP_, PACK>(Qs + ((int64_t)post * C + sid) * QW, q);
+      for (int jb = j0; jb < j1; jb += 32 * UL) {
+        int post[UL], sid[UL];
 #pragma unroll
-          for (int bb = 0; bb < BP_; ++bb) val = (bb == b) ? q[bb] : val;
+        for (int q = 0; q < UL; ++q) {
+          const int j = jb + q * 32 + lane;
+          post[q] = j < j1 ? a.lgn_post[j] : 0;
+          sid[q] = j < j1 ? (int)a.lgn_sid[j] : 0;
+        }
+        float val[UL];
+        if (PROJ) {
+          float qv[UL][BP_];
+#pragma unroll
+          for (int q = 0; q < UL; ++q) load_row<BP_, PACK>(Qs + ((int64_t)post[q] * C + sid[q]) * QW, qv[q]);
+#pragma unroll
+          for (int q = 0; q < UL; ++q) {
+            val[q] = 0.f;
+#pragma unroll
+            for (int bb = 0; bb < BP_; ++bb) val[q] = (bb == b) ? qv[q][bb] : val[q];
+          }
         } else {
 #pragma unroll
-          for (int r = 0; r < R_; ++r) {
-            float q[BP_];
-            load_row<BP_, PACK>(Qs + ((int64_t)post * C + r) * QW, q);
-            float qb = 0.f;
+          for (int q = 0; q < UL; ++q) {
+            val[q] = 0.f;
 #pragma unroll
-            for (int bb = 0; bb < BP_; ++bb) qb = (bb == b) ? q[bb] : qb;
-            val += qb * basis_s[sid * R_ + r];
+            for (int r = 0; r < R_; ++r) {
+              float qr[BP_];
+              load_row<BP_, PACK>(Qs + ((int64_t)post[q] * C + r) * QW, qr);
+              float qb = 0.f;
+#pragma unroll
+              for (int bb = 0; bb < BP_; ++bb) qb = (bb == b) ? qr[bb] : qb;
+              val[q] += qb * basis_s[sid[q] * R_ + r];
+            }
           }
         }
-        atomicAdd(a.dw_lgn + j, val);
+#pragma unroll
+        for (int q = 0; q < UL; ++q) {
+          const int j = jb + q * 32 + lane;
+          if (j < j1) atomicAdd(a.dw_lgn + j, val[q]);
+        }
       }
       if (lane == 0) c_dw += (unsigned long long)(j1 - j0);
     }
@@ -281,6 +320,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       s_misc[2] = 0;  // row queue of this step
       s_misc[3] = 0;
     }
+    if (tid < 8) slot_s[tid] = ((t + 1 + tid) % K) * Np * C;
     __syncthreads();
     if (s_misc[1]) {
       ok = false;
@@ -316,9 +356,17 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       }
       zmask_s[k] = (uint8_t)zm;
       need_s[k] = (uint8_t)(need | (zm ? 1u : 0u));
-      if (need | zm)
-        rowq_s[atomicAdd(&s_misc[2], 1)] = (uint16_t)k;  // queue the row (order is irrelevant)
-      else
+      if (need | zm) {
+        const int qpos = atomicAdd(&s_misc[2], 1);  // queue the row (order is irrelevant)
+        rowq_s[qpos] = (uint16_t)k;
+        if (fast_rows) {
+          const int j0 = rp_s[k * D], j1 = rp_s[k * D + D];
+          rowd_s[qpos] = make_int4(j0, j1, k | (int)(zm << 16), 0);
+          c_rows += (unsigned long long)D;
+          c_events += (unsigned long long)(j1 - j0);
+          if (zm) c_dw += (unsigned long long)(j1 - j0) * __popc(zm);
+        }
+      } else
         for (int b = 0; b < B; ++b) gz_s[b * chunkP + k] = 0.f;  // row is not walked
     }
     if (t >= 2)
@@ -339,12 +387,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       for (int u = 0; u < U; ++u) {
         const int j = jb + u * 32 + lane;
         const bool v = j < j1;
-        if (a.rec_meta) {
-          // one byte carries the synapse type and the delay bucket
-          post[u] = v ? __ldcs(a.rec_post + j) : 0;
-          sid[u] = v ? (int)__ldcs(a.rec_meta + j) : 0;
-          w[u] = v ? __ldcs(a.rec_w + j) : 0.f;
-        } else if (a.csr_evict_first) {
+        if (a.csr_evict_first) {
           post[u] = v ? __ldcs(a.rec_post + j) : 0;
           sid[u] = v ? (int)__ldcs(a.rec_sid + j) : 0;
           w[u] = v ? __ldcs(a.rec_w + j) : 0.f;
@@ -355,12 +398,171 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         }
       }
     };
+    // sum the BP_ accumulators over the warp: each exchange halves the values a lane carries
+    // (9 shuffles for 8 accumulators instead of 40); lane l ends with the total of batch row
+    // ((l >> 2) & 1) | ((l >> 3) & 1) << 1 | ((l >> 4) & 1) << 2
+    auto reduce_store = [&](const float (&acc)[BP_], int k) {
+      float a4[4];
+      if (BP_ == 8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const bool hi = lane & 16;
+          const float recv = __shfl_xor_sync(0xffffffffu, hi ? acc[i] : acc[(i + 4) % BP_], 16);
+          a4[i] = (hi ? acc[(i + 4) % BP_] : acc[i]) + recv;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a4[i] = acc[i] + __shfl_xor_sync(0xffffffffu, acc[i], 16);
+      }
+      float a2[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const bool hi = lane & 8;
+        const float recv = __shfl_xor_sync(0xffffffffu, hi ? a4[i] : a4[i + 2], 8);
+        a2[i] = (hi ? a4[i + 2] : a4[i]) + recv;
+      }
+      float a1;
+      {
+        const bool hi = lane & 4;
+        const float recv = __shfl_xor_sync(0xffffffffu, hi ? a2[0] : a2[1], 4);
+        a1 = (hi ? a2[1] : a2[0]) + recv;
+      }
+      a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+      a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+      int bsel = ((lane >> 2) & 1) | (((lane >> 3) & 1) << 1);
+      if (BP_ == 8) bsel |= ((lane >> 4) & 1) << 2;
+      if ((lane & 3) == 0 && (BP_ == 8 || lane < 16) && bsel < B) gz_s[bsel * chunkP + k] = a1;
+    };
+    // The LGN events of step t+1 first (Q(t+1) is complete): the few warps that hold one start on
+    // the row queue a little later and simply take fewer rows.
+#if !defined(V1G_DIAG) || V1G_DIAG != 5
+    if (t + 1 < T) lgn_dw(t + 1);
+#endif
     // warps take rows from the queue one at a time, so a warp that drew long rows takes fewer
     const int nq = s_misc[2];
+    auto pop_row = [&]() {
+      int q = 0;
+      if (lane == 0) q = atomicAdd(&s_misc[3], 1);
+      return __shfl_sync(0xffffffffu, q, 0);
+    };
+    if (fast_rows) {
+      // Packed-record path.  The unit of work is a pass: up to UF*32 consecutive synapses of one
+      // row, one 8-byte record per synapse.  Warps draw rows from the queue of row descriptors
+      // written in phase A.  Each warp keeps the records of the pass after next
+      // and the Q rows of the next pass in flight while it accumulates the current one.  Registers
+      // that receive a load are never copied while the load is in flight (a copy would wait for
+      // it): the loop body is written out once per Q buffer, NS buffers in rotation.
+      // The Q row index comes from a per-step table of the D slot bases.  Steps past the end of
+      // the rollout need no test: their ring slots still hold the zeros of the initial clear.
+      // Lanes past the end of a row read a neighbouring record (always inside the array) and get
+      // weight zero.
+      constexpr int NB = PACK ? 5 : BP_;     // batch values a row really carries
+      constexpr int QV = QW / 4;             // 16-byte words per Q row
+      constexpr int UF = QV == 1 ? 4 : 2;    // 32-synapse groups per pass
+      constexpr int NS = V1G_BWD_STAGES;
+      struct Pass { int jb, j1, kz, fl; };   // kz = row | spike mask << 16; fl: 1 first pass of its row, 4 valid
+      const int jmax = a.rec_nnz - 1;
+      Pass pr{0, 0, 0, 0};
+      Pass ps_[NS];
+      uint2 rec[UF];
+      float4 qS[NS][UF][QV];
+      float wS[NS][UF];
+      float acc[BP_];
+#pragma unroll
+      for (int i = 0; i < NS; ++i) ps_[i] = Pass{0, 0, 0, 0};
+#pragma unroll
+      for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
+      auto issue_rec = [&]() {  // advance pr to the following pass and request its records
+        if (pr.fl && pr.jb + 32 * UF < pr.j1) {
+          pr.jb += 32 * UF;
+          pr.fl = 4;
+        } else {
+          const int q = pop_row();  // warps that drew long rows, or rows with spikes, take fewer
+          if (q < nq) {
+            const int4 d = rowd_s[q];
+            pr = Pass{d.x, d.y, d.z, 5};
+          } else {
+            pr = Pass{0, 0, 0, 0};
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UF; ++u) rec[u] = __ldcs(a.rec_syn8 + min(pr.jb + u * 32 + lane, jmax));
+      };
+      auto issue_q = [&](const Pass& ps, float4 (&q)[UF][QV], float (&w)[UF]) {  // Q rows of the pass in rec
+#pragma unroll
+        for (int u = 0; u < UF; ++u) {
+          const unsigned w0 = rec[u].x;
+          const unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + ((w0 >> 22) & 127u);
+          const float4* qp = (const float4*)(a.Q + row * (unsigned)QW);  // < 2^31 words, checked by the host
+#pragma unroll
+          for (int v = 0; v < QV; ++v) q[u][v] = __ldcg(qp + v);
+          w[u] = (ps.jb + u * 32 + lane < ps.j1) ? __uint_as_float(rec[u].y) : 0.f;
+        }
+      };
+      auto compute = [&](const Pass& ps, const float4 (&q)[UF][QV], const float (&w)[UF]) {
+        if (ps.fl & 1) {
+#pragma unroll
+          for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
+        }
+        const unsigned zm = (unsigned)ps.kz >> 16;
+        if (!zm) {
+#pragma unroll
+          for (int u = 0; u < UF; ++u) {
+            float pj[BP_];
+            unpack_row<BP_, PACK>(q[u], pj);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
+          }
+        } else {
+          // the source neuron spiked at this step in the batch rows of zm: weight gradient
+#pragma unroll
+          for (int u = 0; u < UF; ++u) {
+            float pj[BP_];
+            unpack_row<BP_, PACK>(q[u], pj);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
+            const int j = ps.jb + u * 32 + lane;
+            if (j < ps.j1) {
+              float dwv = 0.f;
+#pragma unroll
+              for (int b = 0; b < NB; ++b)
+                if (zm & (1u << b)) dwv += pj[b];
+              a.dw_rec[j] += dwv;  // this lane is the only writer of the synapse
+            }
+          }
+        }
+        if (ps.jb + 32 * UF >= ps.j1) reduce_store(acc, ps.kz & 0xffff);
+      };
+      // one turn of the pipeline with buffer I: false when the warp has no further pass
+      auto turn = [&](auto I) -> bool {
+        constexpr int i = decltype(I)::value;
+        if (!pr.fl) {
+          // accumulate what is still in flight, oldest first
+#pragma unroll
+          for (int o = 1; o < NS; ++o)
+            if (ps_[(i + o) % NS].fl) compute(ps_[(i + o) % NS], qS[(i + o) % NS], wS[(i + o) % NS]);
+          return false;
+        }
+        ps_[i] = pr;
+        issue_q(ps_[i], qS[i], wS[i]);
+        issue_rec();
+        constexpr int x = (i + 1) % NS;  // the oldest pass
+        if (ps_[x].fl) {
+          compute(ps_[x], qS[x], wS[x]);
+          ps_[x].fl = 0;
+        }
+        return true;
+      };
+      issue_rec();
+      for (;;) {
+        if (!turn(std::integral_constant<int, 0>{})) break;
+        if (!turn(std::integral_constant<int, 1 % NS>{})) break;
+        if (NS > 2 && !turn(std::integral_constant<int, 2 % NS>{})) break;
+        if (NS > 3 && !turn(std::integral_constant<int, 3 % NS>{})) break;
+      }
+    } else
     for (;;) {
-      int qi = 0;
-      if (lane == 0) qi = atomicAdd(&s_misc[3], 1);
-      qi = __shfl_sync(0xffffffffu, qi, 0);
+      const int qi = pop_row();
       if (qi >= nq) break;
       const int k = rowq_s[qi];
       int cpost[U], csid[U];
@@ -384,13 +586,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           const int j = jb + u * 32 + lane;
           valid[u] = j < j1;
           int d = 1;
-          if (a.rec_meta) {
-            d += csid[u] >> 5;
-            csid[u] &= 31;
-          } else {
 #pragma unroll
-            for (int q = 1; q < DMAX; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
-          }
+          for (int q = 1; q < DMAX; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
           if (t + d >= T) valid[u] = false;  // no step after the rollout's end
           slot[u] = tk + d;
           if (slot[u] >= K) slot[u] -= K;
@@ -433,48 +630,13 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           }
         }
       }
-      // sum the BP_ accumulators over the warp: each exchange halves the values a lane carries
-      // (9 shuffles for 8 accumulators instead of 40); lane l ends with the total of batch row
-      // ((l >> 2) & 1) | ((l >> 3) & 1) << 1 | ((l >> 4) & 1) << 2
-      float a4[4];
-      if (BP_ == 8) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const bool hi = lane & 16;
-          const float recv = __shfl_xor_sync(0xffffffffu, hi ? acc[i] : acc[(i + 4) % BP_], 16);
-          a4[i] = (hi ? acc[(i + 4) % BP_] : acc[i]) + recv;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) a4[i] = acc[i] + __shfl_xor_sync(0xffffffffu, acc[i], 16);
-      }
-      float a2[2];
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const bool hi = lane & 8;
-        const float recv = __shfl_xor_sync(0xffffffffu, hi ? a4[i] : a4[i + 2], 8);
-        a2[i] = (hi ? a4[i + 2] : a4[i]) + recv;
-      }
-      float a1;
-      {
-        const bool hi = lane & 4;
-        const float recv = __shfl_xor_sync(0xffffffffu, hi ? a2[0] : a2[1], 4);
-        a1 = (hi ? a2[1] : a2[0]) + recv;
-      }
-      a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
-      a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
-      {
-        int bsel = ((lane >> 2) & 1) | (((lane >> 3) & 1) << 1);
-        if (BP_ == 8) bsel |= ((lane >> 4) & 1) << 2;
-        if ((lane & 3) == 0 && (BP_ == 8 || lane < 16) && bsel < B) gz_s[bsel * chunkP + k] = a1;
-      }
+      reduce_store(acc, k);
       if (lane == 0) {
         c_rows += (unsigned long long)D;
         c_events += (unsigned long long)(j1 - j0);
         if (zm) c_dw += (unsigned long long)(j1 - j0) * __popc(zm);
       }
     }
-    if (t + 1 < T) lgn_dw(t + 1);
     __syncthreads();
     const unsigned long long ph2 = prof ? gtime_b() : 0;
 
@@ -844,8 +1006,8 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   auto al = [](size_t b) { return (b + 15) & ~(size_t)15; };
   const size_t plane = (size_t)B * plan.chunkP;
   size_t smem = al(sizeof(float) * S * R) + 2 * al(sizeof(float) * plane) + al(plane) +
-                2 * al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 4) +
-                al(sizeof(uint16_t) * plan.chunkP) +
+                2 * al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 4) + al(sizeof(int) * 8) +
+                al(sizeof(uint16_t) * plan.chunkP) + al(sizeof(int4) * plan.chunkP) +
                 al(sizeof(int32_t) * ((size_t)plan.chunkP * D + 1)) + 6 * al(sizeof(float) * plan.chunkP) +
                 al(sizeof(int) * (plan.chunkP + 1));
   const size_t state_bytes = al(sizeof(float) * plane * (3 + 2 * R));
@@ -922,7 +1084,8 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   const V1GSource& lsrc = h->src[V1G_SRC_LGN];
   const V1GSource& bk = h->src[V1G_SRC_BKG];
   a.rec_rowptr = rs.rowptr; a.rec_post = rs.post; a.rec_w = rs.w; a.rec_sid = rs.sid;
-  a.rec_meta = h->opt_no_meta ? nullptr : rs.meta;
+  a.rec_syn8 = h->opt_no_meta ? nullptr : rs.syn8;
+  a.rec_nnz = (int)rs.nnz;
   a.lgn_rowptr = lsrc.rowptr; a.lgn_post = lsrc.post; a.lgn_sid = lsrc.sid;
   a.bkg_inptr = bk.in_ptr; a.bkg_inpre = bk.in_pre; a.bkg_insid = bk.in_sid;
   a.decay = h->decay; a.cf = h->cf; a.asc_decay = h->asc_decay; a.basis = h->basis;
