@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   const int cn = min(a.chunk, N - n0);
   const int nb = B * a.n_bkg;
 
+  const bool fast_rows = PROJ && a.rec_syn8 != nullptr;  // packed-record gather
   unsigned char* sp_ = smem_raw;
   auto take = [&](size_t bytes) {
     unsigned char* p = sp_;
@@ -168,9 +169,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   };
   const size_t plane = (size_t)B * chunkP;
   float* basis_s = (float*)take(sizeof(float) * a.S * R_);
-  float* gz_s = (float*)take(sizeof(float) * plane);   // gathered spike gradient [b][k]
-  float* tv_s = (float*)take(sizeof(float) * plane);   // v(t) of the step [b][k]
-  uint8_t* tz_s = (uint8_t*)take(plane);               // spike / refractory bits of the step
+  // per-step planes [parity of the step][b][k]
+  float* gz_s = (float*)take(sizeof(float) * 2 * plane);   // gathered spike gradient
+  float* tv_s = (float*)take(sizeof(float) * 2 * plane);   // v(t)
+  uint8_t* tz_s = (uint8_t*)take(2 * plane);               // spike / refractory bits
   uint8_t* need_s = (uint8_t*)take(chunkP);            // row must be walked
   uint8_t* zmask_s = (uint8_t*)take(chunkP);           // batch rows that spiked at this step
   int* s_cnt = (int*)take(sizeof(int) * nb);
@@ -178,13 +180,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   int* slot_s = (int*)take(sizeof(int) * 8);  // first Q row of step t+1+d, d = 0..7
   uint16_t* rowq_s = (uint16_t*)take(sizeof(uint16_t) * chunkP);  // rows to walk this step
   int4* rowd_s = (int4*)take(sizeof(int4) * chunkP);  // the same rows as {first synapse, end, row | spike mask << 16, 0}
-  int32_t* rp_s = (int32_t*)take(sizeof(int32_t) * ((size_t)chunkP * D + 1));  // row pointers of the slice
-  float* c_decay = (float*)take(sizeof(float) * chunkP);  // per-neuron constants of the slice
-  float* c_cf = (float*)take(sizeof(float) * chunkP);
-  float* c_ad0 = (float*)take(sizeof(float) * chunkP);
-  float* c_ad1 = (float*)take(sizeof(float) * chunkP);
-  float* c_rc = (float*)take(sizeof(float) * chunkP);
-  float* c_vlo = (float*)take(sizeof(float) * chunkP);
+  // row pointers of the slice: on chip for the gather that reads them per row pass, from global
+  // memory (two loads per neuron and step) for the packed-record gather
+  int32_t* rp_s = (int32_t*)take(fast_rows ? 0 : sizeof(int32_t) * ((size_t)chunkP * D + 1));
+  const int32_t* rpx = fast_rows ? a.rec_rowptr + (int64_t)n0 * D : rp_s;
   int* bkptr_s = (int*)take(sizeof(int) * (chunkP + 1));  // background in-synapse ranges, slice-relative
   // background in-synapses of the slice and their weight-gradient accumulators; on chip when they
   // fit, otherwise the global tables are used directly
@@ -208,16 +207,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   float* G_pr = G_p + plane * R_;  // [r][b][k]
 
   for (int i = tid; i < a.S * R_; i += NT) basis_s[i] = a.basis[i];
-  for (int i = tid; i <= cn * D; i += NT) rp_s[i] = a.rec_rowptr[(int64_t)n0 * D + i];
-  for (int k = tid; k < cn; k += NT) {
-    const int n = n0 + k;
-    c_decay[k] = a.decay[n];
-    c_cf[k] = a.cf[n];
-    c_ad0[k] = a.asc_decay[2 * n];
-    c_ad1[k] = a.asc_decay[2 * n + 1];
-    c_rc[k] = a.rate_coef ? a.rate_coef[n] : 0.f;
-    c_vlo[k] = a.v_lo ? a.v_lo[n] : 0.f;
-  }
+  if (!fast_rows)
+    for (int i = tid; i <= cn * D; i += NT) rp_s[i] = a.rec_rowptr[(int64_t)n0 * D + i];
   const int bk_base = a.bkg_inptr[n0];
   const int bk_m = a.bkg_inptr[n0 + cn] - bk_base;
   for (int k = tid; k <= cn; k += NT) bkptr_s[k] = a.bkg_inptr[n0 + k] - bk_base;
@@ -248,7 +239,6 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   const bool prof = a.phase_ns != nullptr && tid == 0;
   const unsigned long long ph_start = prof ? gtime_b() : 0;
   const int gw = blockIdx.x * NW + warp, gnw = gridDim.x * NW;
-  const bool fast_rows = PROJ && a.rec_syn8 != nullptr;  // packed-record gather
 
   // Weight gradient of the LGN events of step tt from Q(tt).  One warp per event; the (up to 128)
   // synapses of a pass are loaded together so that the three dependent accesses (record, Q row,
@@ -306,31 +296,13 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     }
   };
 
-  for (int it = 0; it < T && ok; ++it) {
-    const int t = T - 1 - it;
-    const unsigned long long ph0 = prof ? gtime_b() : 0;
-    if (tid == 0 && it >= 2) {
-      // every block must have finished iteration it-3 (phase it-2): Q(t+1 .. t+D) is complete
-      const unsigned long long target = v1g_phase_target(it - 2, G);
-      if (seen < target)
-        seen = v1g_wait(v1g_phase_counter(a.barrier, it - 2), target, a.spin_limit, a.status);
-      if (seen < target) s_misc[1] = 1;
-    }
-    if (tid == 0) {
-      s_misc[2] = 0;  // row queue of this step
-      s_misc[3] = 0;
-    }
-    if (tid < 8) slot_s[tid] = ((t + 1 + tid) % K) * Np * C;
-    __syncthreads();
-    if (s_misc[1]) {
-      ok = false;
-      break;
-    }
-    if (tid == 0 && it >= 1) v1g_arrive(v1g_phase_counter(a.barrier, it));
-
-    // ---------------- phase A: this step's tape, row flags, counts of step t-2 ----------------
-    for (int k = tid; k < cn; k += NT) {
-      const int n = n0 + k;
+  // Tape of step ts into the planes of its parity: v, spike / refractory bits, the rows that must be
+  // walked (queue and descriptors) and zeros in the spike-gradient plane for those that need not.
+  auto load_step = [&](int ts, float* tvp, uint8_t* tzp, float* gzp, bool queue) {
+    for (int k0 = 0; k0 < cn; k0 += NT) {
+      const int k = k0 + tid;
+      const bool act = k < cn;
+      const int n = n0 + (act ? k : 0);
       // all tape loads of the neuron are issued before any of them is used
       float vv[BP_];
       unsigned zz[BP_];
@@ -338,8 +310,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       for (int b = 0; b < BP_; ++b) {
         vv[b] = 0.f;
         zz[b] = 2u;
-        if (b < B) {
-          const int64_t ti = ((int64_t)t * B + b) * N + n;
+        if (b < B && act) {
+          const int64_t ti = ((int64_t)ts * B + b) * N + n;
           vv[b] = __ldcs(a.tape_v + ti);
           zz[b] = __ldcs(a.tape_zr + ti);
         }
@@ -347,28 +319,86 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       unsigned zm = 0, need = 0;
 #pragma unroll
       for (int b = 0; b < BP_; ++b) {
-        if (b < B) {
-          tv_s[b * chunkP + k] = vv[b];
-          tz_s[b * chunkP + k] = (uint8_t)zz[b];
+        if (b < B && act) {
+          tvp[b * chunkP + k] = vv[b];
+          tzp[b * chunkP + k] = (uint8_t)zz[b];
           zm |= (zz[b] & 1u) << b;
           if (!(zz[b] & 2u) && pseudo_h(vv[b] - 1.f, a) != 0.f) need = 1;
         }
       }
-      zmask_s[k] = (uint8_t)zm;
-      need_s[k] = (uint8_t)(need | (zm ? 1u : 0u));
-      if (need | zm) {
-        const int qpos = atomicAdd(&s_misc[2], 1);  // queue the row (order is irrelevant)
-        rowq_s[qpos] = (uint16_t)k;
-        if (fast_rows) {
-          const int j0 = rp_s[k * D], j1 = rp_s[k * D + D];
-          rowd_s[qpos] = make_int4(j0, j1, k | (int)(zm << 16), 0);
-          c_rows += (unsigned long long)D;
-          c_events += (unsigned long long)(j1 - j0);
-          if (zm) c_dw += (unsigned long long)(j1 - j0) * __popc(zm);
+      if (!queue) continue;
+      const bool walk = act && (need | zm);
+      if (act) {
+        zmask_s[k] = (uint8_t)zm;
+        need_s[k] = (uint8_t)(walk ? 1u : 0u);
+        if (!walk)
+          for (int b = 0; b < B; ++b) gzp[b * chunkP + k] = 0.f;  // row is not walked
+      }
+      // queue the rows to walk: one shared-memory atomic per warp (order is irrelevant)
+      const unsigned wm = __ballot_sync(0xffffffffu, walk);
+      if (wm) {
+        int base = 0;
+        if (lane == 0) base = atomicAdd(&s_misc[2], __popc(wm));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (walk) {
+          const int qpos = base + __popc(wm & ((1u << lane) - 1u));
+          rowq_s[qpos] = (uint16_t)k;
+          if (fast_rows) {
+            const int j0 = rpx[k * D], j1 = rpx[k * D + D];
+            rowd_s[qpos] = make_int4(j0, j1, k | (int)(zm << 16), 0);
+            c_rows += (unsigned long long)D;
+            c_events += (unsigned long long)(j1 - j0);
+            if (zm) c_dw += (unsigned long long)(j1 - j0) * __popc(zm);
+          }
         }
-      } else
-        for (int b = 0; b < B; ++b) gz_s[b * chunkP + k] = 0.f;  // row is not walked
+      }
     }
+  };
+
+  // The loop runs one iteration per step t, newest first.  An iteration loads the tape of step t-1,
+  // then every warp does its share of the dense adjoint of step t and goes straight on to the gather
+  // of step t-1 (spike gradients of step t-1, needed by the next iteration): the two have no
+  // dependence on each other, the dense part is bound by instruction issue and the gather by L2
+  // requests, so running them without a barrier in between lets them overlap.  Per-step planes
+  // (v, bits, spike gradient) are double-buffered by step parity.
+  // Gather(t-1) reads Q(t .. t-1+D); Q(t) was published by the dense part of step t+2, so every block
+  // must have finished iteration it-2 (phase it-1).  A block is then at most one iteration ahead of
+  // the slowest one and writes Q(t-3) at the earliest: D+3 ring slots suffice.
+  if (T >= 1) {
+    // prologue: tape of the last step; its spike gradient from later steps is zero
+    load_step(T - 1, tv_s + ((T - 1) & 1) * plane, tz_s + ((T - 1) & 1) * plane, gz_s + ((T - 1) & 1) * plane, false);
+    __syncthreads();
+    for (int i = tid; i < (int)plane; i += NT) gz_s[((T - 1) & 1) * plane + i] = 0.f;
+    __syncthreads();
+  }
+  for (int it = 0; it < T && ok; ++it) {
+    const int t = T - 1 - it;   // step of the dense adjoint
+    const int tg = t - 1;       // step of the gather (none in the last iteration)
+    float* const tvC = tv_s + (t & 1) * plane;
+    uint8_t* const tzC = tz_s + (t & 1) * plane;
+    float* const gzC = gz_s + (t & 1) * plane;
+    float* const gzB = gz_s + ((t & 1) ^ 1) * plane;
+    const unsigned long long ph0 = prof ? gtime_b() : 0;
+    if (tid == 0 && it >= 1) {
+      const unsigned long long target = v1g_phase_target(it - 1, G);
+      if (seen < target)
+        seen = v1g_wait(v1g_phase_counter(a.barrier, it - 1), target, a.spin_limit, a.status);
+      if (seen < target) s_misc[1] = 1;
+    }
+    if (tid == 0) {
+      s_misc[2] = 0;  // row queue of this step
+      s_misc[3] = 0;
+    }
+    if (tid < 8) slot_s[tid] = ((tg + 1 + tid) % K) * Np * C;
+    __syncthreads();
+    if (s_misc[1]) {
+      ok = false;
+      break;
+    }
+    if (tid == 0 && it >= 1) v1g_arrive(v1g_phase_counter(a.barrier, it));
+
+    // ---------------- phase A: tape of step t-1, row flags, counts of step t-2 ----------------
+    if (tg >= 0) load_step(tg, tv_s + ((t & 1) ^ 1) * plane, tz_s + ((t & 1) ^ 1) * plane, gzB, true);
     if (t >= 2)
       for (int i = tid; i < nb; i += NT) {
         const int b = i / a.n_bkg, j = i - b * a.n_bkg;
@@ -377,276 +407,13 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     __syncthreads();
     const unsigned long long ph1 = prof ? gtime_b() : 0;
 
-    // ---------------- phase B: gather over the out-synapses of every needed neuron ----------------
-    if (tid == 0) seen = (it >= 1) ? v1g_ld_acquire(v1g_phase_counter(a.barrier, it - 1)) : 0;
-    const int tk = t % K;
-    constexpr int U = PROJ ? 4 : 1;  // row iterations (32 synapses each) kept in flight per warp
-    // one pass = U*32 consecutive synapses of a row, lane l holding synapses jb + u*32 + l
-    auto load_pass = [&](int jb, int j1, int (&post)[U], int (&sid)[U], float (&w)[U]) {
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int j = jb + u * 32 + lane;
-        const bool v = j < j1;
-        if (a.csr_evict_first) {
-          post[u] = v ? __ldcs(a.rec_post + j) : 0;
-          sid[u] = v ? (int)__ldcs(a.rec_sid + j) : 0;
-          w[u] = v ? __ldcs(a.rec_w + j) : 0.f;
-        } else {
-          post[u] = v ? a.rec_post[j] : 0;
-          sid[u] = v ? (int)a.rec_sid[j] : 0;
-          w[u] = v ? a.rec_w[j] : 0.f;
-        }
-      }
-    };
-    // sum the BP_ accumulators over the warp: each exchange halves the values a lane carries
-    // (9 shuffles for 8 accumulators instead of 40); lane l ends with the total of batch row
-    // ((l >> 2) & 1) | ((l >> 3) & 1) << 1 | ((l >> 4) & 1) << 2
-    auto reduce_store = [&](const float (&acc)[BP_], int k) {
-      float a4[4];
-      if (BP_ == 8) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const bool hi = lane & 16;
-          const float recv = __shfl_xor_sync(0xffffffffu, hi ? acc[i] : acc[(i + 4) % BP_], 16);
-          a4[i] = (hi ? acc[(i + 4) % BP_] : acc[i]) + recv;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) a4[i] = acc[i] + __shfl_xor_sync(0xffffffffu, acc[i], 16);
-      }
-      float a2[2];
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const bool hi = lane & 8;
-        const float recv = __shfl_xor_sync(0xffffffffu, hi ? a4[i] : a4[i + 2], 8);
-        a2[i] = (hi ? a4[i + 2] : a4[i]) + recv;
-      }
-      float a1;
-      {
-        const bool hi = lane & 4;
-        const float recv = __shfl_xor_sync(0xffffffffu, hi ? a2[0] : a2[1], 4);
-        a1 = (hi ? a2[1] : a2[0]) + recv;
-      }
-      a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
-      a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
-      int bsel = ((lane >> 2) & 1) | (((lane >> 3) & 1) << 1);
-      if (BP_ == 8) bsel |= ((lane >> 4) & 1) << 2;
-      if ((lane & 3) == 0 && (BP_ == 8 || lane < 16) && bsel < B) gz_s[bsel * chunkP + k] = a1;
-    };
-    // The LGN events of step t+1 first (Q(t+1) is complete): the few warps that hold one start on
-    // the row queue a little later and simply take fewer rows.
-#if !defined(V1G_DIAG) || V1G_DIAG != 5
-    if (t + 1 < T) lgn_dw(t + 1);
-#endif
-    // warps take rows from the queue one at a time, so a warp that drew long rows takes fewer
-    const int nq = s_misc[2];
-    auto pop_row = [&]() {
-      int q = 0;
-      if (lane == 0) q = atomicAdd(&s_misc[3], 1);
-      return __shfl_sync(0xffffffffu, q, 0);
-    };
-    if (fast_rows) {
-      // Packed-record path.  The unit of work is a pass: up to UF*32 consecutive synapses of one
-      // row, one 8-byte record per synapse.  Warps draw rows from the queue of row descriptors
-      // written in phase A.  Each warp keeps the records of the pass after next
-      // and the Q rows of the next pass in flight while it accumulates the current one.  Registers
-      // that receive a load are never copied while the load is in flight (a copy would wait for
-      // it): the loop body is written out once per Q buffer, NS buffers in rotation.
-      // The Q row index comes from a per-step table of the D slot bases.  Steps past the end of
-      // the rollout need no test: their ring slots still hold the zeros of the initial clear.
-      // Lanes past the end of a row read a neighbouring record (always inside the array) and get
-      // weight zero.
-      constexpr int NB = PACK ? 5 : BP_;     // batch values a row really carries
-      constexpr int QV = QW / 4;             // 16-byte words per Q row
-      constexpr int UF = QV == 1 ? 4 : 2;    // 32-synapse groups per pass
-      constexpr int NS = V1G_BWD_STAGES;
-      struct Pass { int jb, j1, kz, fl; };   // kz = row | spike mask << 16; fl: 1 first pass of its row, 4 valid
-      const int jmax = a.rec_nnz - 1;
-      Pass pr{0, 0, 0, 0};
-      Pass ps_[NS];
-      uint2 rec[UF];
-      float4 qS[NS][UF][QV];
-      float wS[NS][UF];
-      float acc[BP_];
-#pragma unroll
-      for (int i = 0; i < NS; ++i) ps_[i] = Pass{0, 0, 0, 0};
-#pragma unroll
-      for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
-      auto issue_rec = [&]() {  // advance pr to the following pass and request its records
-        if (pr.fl && pr.jb + 32 * UF < pr.j1) {
-          pr.jb += 32 * UF;
-          pr.fl = 4;
-        } else {
-          const int q = pop_row();  // warps that drew long rows, or rows with spikes, take fewer
-          if (q < nq) {
-            const int4 d = rowd_s[q];
-            pr = Pass{d.x, d.y, d.z, 5};
-          } else {
-            pr = Pass{0, 0, 0, 0};
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < UF; ++u) rec[u] = __ldcs(a.rec_syn8 + min(pr.jb + u * 32 + lane, jmax));
-      };
-      auto issue_q = [&](const Pass& ps, float4 (&q)[UF][QV], float (&w)[UF]) {  // Q rows of the pass in rec
-#pragma unroll
-        for (int u = 0; u < UF; ++u) {
-          const unsigned w0 = rec[u].x;
-          const unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + ((w0 >> 22) & 127u);
-          const float4* qp = (const float4*)(a.Q + row * (unsigned)QW);  // < 2^31 words, checked by the host
-#pragma unroll
-          for (int v = 0; v < QV; ++v) q[u][v] = __ldcg(qp + v);
-          w[u] = (ps.jb + u * 32 + lane < ps.j1) ? __uint_as_float(rec[u].y) : 0.f;
-        }
-      };
-      auto compute = [&](const Pass& ps, const float4 (&q)[UF][QV], const float (&w)[UF]) {
-        if (ps.fl & 1) {
-#pragma unroll
-          for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
-        }
-        const unsigned zm = (unsigned)ps.kz >> 16;
-        if (!zm) {
-#pragma unroll
-          for (int u = 0; u < UF; ++u) {
-            float pj[BP_];
-            unpack_row<BP_, PACK>(q[u], pj);
-#pragma unroll
-            for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
-          }
-        } else {
-          // the source neuron spiked at this step in the batch rows of zm: weight gradient
-#pragma unroll
-          for (int u = 0; u < UF; ++u) {
-            float pj[BP_];
-            unpack_row<BP_, PACK>(q[u], pj);
-#pragma unroll
-            for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
-            const int j = ps.jb + u * 32 + lane;
-            if (j < ps.j1) {
-              float dwv = 0.f;
-#pragma unroll
-              for (int b = 0; b < NB; ++b)
-                if (zm & (1u << b)) dwv += pj[b];
-              a.dw_rec[j] += dwv;  // this lane is the only writer of the synapse
-            }
-          }
-        }
-        if (ps.jb + 32 * UF >= ps.j1) reduce_store(acc, ps.kz & 0xffff);
-      };
-      // one turn of the pipeline with buffer I: false when the warp has no further pass
-      auto turn = [&](auto I) -> bool {
-        constexpr int i = decltype(I)::value;
-        if (!pr.fl) {
-          // accumulate what is still in flight, oldest first
-#pragma unroll
-          for (int o = 1; o < NS; ++o)
-            if (ps_[(i + o) % NS].fl) compute(ps_[(i + o) % NS], qS[(i + o) % NS], wS[(i + o) % NS]);
-          return false;
-        }
-        ps_[i] = pr;
-        issue_q(ps_[i], qS[i], wS[i]);
-        issue_rec();
-        constexpr int x = (i + 1) % NS;  // the oldest pass
-        if (ps_[x].fl) {
-          compute(ps_[x], qS[x], wS[x]);
-          ps_[x].fl = 0;
-        }
-        return true;
-      };
-      issue_rec();
-      for (;;) {
-        if (!turn(std::integral_constant<int, 0>{})) break;
-        if (!turn(std::integral_constant<int, 1 % NS>{})) break;
-        if (NS > 2 && !turn(std::integral_constant<int, 2 % NS>{})) break;
-        if (NS > 3 && !turn(std::integral_constant<int, 3 % NS>{})) break;
-      }
-    } else
-    for (;;) {
-      const int qi = pop_row();
-      if (qi >= nq) break;
-      const int k = rowq_s[qi];
-      int cpost[U], csid[U];
-      float cw[U];
-      load_pass(rp_s[k * D], rp_s[k * D + D], cpost, csid, cw);
-      const unsigned zm = zmask_s[k];
-      const int32_t* rp = rp_s + k * D;
-      int bound[DMAX + 1];
-#pragma unroll
-      for (int d = 0; d <= DMAX; ++d) bound[d] = rp[d <= D ? d : D];
-      const int j0 = bound[0], j1 = rp[D];
-      float acc[BP_];
-#pragma unroll
-      for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
-      for (int jb = j0; jb < j1; jb += 32 * U) {
-        if (jb != j0) load_pass(jb, j1, cpost, csid, cw);  // rows longer than one pass
-        int slot[U];
-        bool valid[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int j = jb + u * 32 + lane;
-          valid[u] = j < j1;
-          int d = 1;
-#pragma unroll
-          for (int q = 1; q < DMAX; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
-          if (t + d >= T) valid[u] = false;  // no step after the rollout's end
-          slot[u] = tk + d;
-          if (slot[u] >= K) slot[u] -= K;
-          if (!valid[u]) {
-            slot[u] = tk;
-            cw[u] = 0.f;
-            cpost[u] = 0;
-            csid[u] = 0;
-          }
-        }
-        float pj[U][BP_];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const float* Qp = a.Q + (unsigned)((slot[u] * Np + cpost[u]) * C) * QW;  // < 2^31, checked by the host
-          if (PROJ) {
-            load_row<BP_, PACK>(Qp + csid[u] * QW, pj[u]);
-          } else {
-#pragma unroll
-            for (int b = 0; b < BP_; ++b) pj[u][b] = 0.f;
-#pragma unroll
-            for (int r = 0; r < R_; ++r) {
-              float q[BP_];
-              load_row<BP_, PACK>(Qp + r * QW, q);
-              const float bs = basis_s[csid[u] * R_ + r];
-#pragma unroll
-              for (int b = 0; b < BP_; ++b) pj[u][b] += q[b] * bs;
-            }
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-#pragma unroll
-          for (int b = 0; b < BP_; ++b) acc[b] += cw[u] * pj[u][b];
-          if (zm && valid[u]) {
-            float dwv = 0.f;
-#pragma unroll
-            for (int b = 0; b < BP_; ++b)
-              if (zm & (1u << b)) dwv += pj[u][b];
-            a.dw_rec[jb + u * 32 + lane] += dwv;  // this lane is the only writer of the synapse
-          }
-        }
-      }
-      reduce_store(acc, k);
-      if (lane == 0) {
-        c_rows += (unsigned long long)D;
-        c_events += (unsigned long long)(j1 - j0);
-        if (zm) c_dw += (unsigned long long)(j1 - j0) * __popc(zm);
-      }
-    }
-    __syncthreads();
-    const unsigned long long ph2 = prof ? gtime_b() : 0;
-
-    // ---------------- phase C: dense adjoint, publish Q(t-2), background weight gradient ----------------
+    // ---------------- dense adjoint of step t, publish Q(t-2), background weight gradient ----------------
     const int bin = (a.sgrad && a.sync_bin > 0 && t / a.sync_bin < a.nbins) ? t / a.sync_bin : -1;
     float* Qw = a.Q + (int64_t)((t + K - 2) % K) * Np * C * QW;
     for (int k = tid; k < cn; k += NT) {
       const int n = n0 + k;
-      const float k_decay = c_decay[k], k_cf = c_cf[k], k_ad0 = c_ad0[k], k_ad1 = c_ad1[k];
-      const float rc = c_rc[k], vlo = c_vlo[k];
+      const float k_decay = a.decay[n], k_cf = a.cf[n], k_ad0 = a.asc_decay[2 * n], k_ad1 = a.asc_decay[2 * n + 1];
+      const float rc = a.rate_coef ? a.rate_coef[n] : 0.f, vlo = a.v_lo ? a.v_lo[n] : 0.f;
       float dyv[BP_][R_];  // dy(t-2) of every batch row of this neuron
 #pragma unroll
       for (int b = 0; b < BP_; ++b) {
@@ -654,12 +421,12 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         for (int r = 0; r < R_; ++r) dyv[b][r] = 0.f;
         if (b < B) {
           const int si = b * chunkP + k;
-          const float v = tv_s[si];
-          const unsigned zr = tz_s[si];
+          const float v = tvC[si];
+          const unsigned zr = tzC[si];
           const bool free_ = !(zr & 2u);
           const int64_t oi = ((int64_t)b * T + t) * N + n;
           float gz = rc + (bin >= 0 ? a.sgrad[b * a.nbins + bin] : 0.f) + (a.g_z ? a.g_z[oi] : 0.f);
-          gz += a.rec_factor * gz_s[si];
+          gz += a.rec_factor * gzC[si];
           float gv = G_v[si] + (a.g_v ? a.g_v[oi] : 0.f);
           if (a.volt_coef != 0.f) {
             const float hi = fmaxf(v - 1.f, 0.f), lo = fmaxf(vlo - v, 0.f);
@@ -736,14 +503,276 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         }
       }
     }
+    const unsigned long long ph2 = prof ? gtime_b() : 0;
+    // ---------------- gather of step t-1 over the out-synapses of every needed neuron ----------------
+    if (tid == 0) seen = v1g_ld_acquire(v1g_phase_counter(a.barrier, it));
+    const int tk = (tg + K) % K;
+    constexpr int U = PROJ ? 4 : 1;  // row iterations (32 synapses each) kept in flight per warp
+    // one pass = U*32 consecutive synapses of a row, lane l holding synapses jb + u*32 + l
+    auto load_pass = [&](int jb, int j1, int (&post)[U], int (&sid)[U], float (&w)[U]) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int j = jb + u * 32 + lane;
+        const bool v = j < j1;
+        if (a.csr_evict_first) {
+          post[u] = v ? __ldcs(a.rec_post + j) : 0;
+          sid[u] = v ? (int)__ldcs(a.rec_sid + j) : 0;
+          w[u] = v ? __ldcs(a.rec_w + j) : 0.f;
+        } else {
+          post[u] = v ? a.rec_post[j] : 0;
+          sid[u] = v ? (int)a.rec_sid[j] : 0;
+          w[u] = v ? a.rec_w[j] : 0.f;
+        }
+      }
+    };
+    // sum the BP_ accumulators over the warp: each exchange halves the values a lane carries
+    // (9 shuffles for 8 accumulators instead of 40); lane l ends with the total of batch row
+    // ((l >> 2) & 1) | ((l >> 3) & 1) << 1 | ((l >> 4) & 1) << 2
+    auto reduce_store = [&](const float (&acc)[BP_], int k) {
+      float a4[4];
+      if (BP_ == 8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const bool hi = lane & 16;
+          const float recv = __shfl_xor_sync(0xffffffffu, hi ? acc[i] : acc[(i + 4) % BP_], 16);
+          a4[i] = (hi ? acc[(i + 4) % BP_] : acc[i]) + recv;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a4[i] = acc[i] + __shfl_xor_sync(0xffffffffu, acc[i], 16);
+      }
+      float a2[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const bool hi = lane & 8;
+        const float recv = __shfl_xor_sync(0xffffffffu, hi ? a4[i] : a4[i + 2], 8);
+        a2[i] = (hi ? a4[i + 2] : a4[i]) + recv;
+      }
+      float a1;
+      {
+        const bool hi = lane & 4;
+        const float recv = __shfl_xor_sync(0xffffffffu, hi ? a2[0] : a2[1], 4);
+        a1 = (hi ? a2[1] : a2[0]) + recv;
+      }
+      a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+      a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+      int bsel = ((lane >> 2) & 1) | (((lane >> 3) & 1) << 1);
+      if (BP_ == 8) bsel |= ((lane >> 4) & 1) << 2;
+      if ((lane & 3) == 0 && (BP_ == 8 || lane < 16) && bsel < B) gzB[bsel * chunkP + k] = a1;
+    };
+    // The LGN events of step t first (Q(t) is complete, and all zero in the first two iterations):
+    // the few warps that hold one start on the row queue a little later and simply take fewer rows.
+    if (it >= 2) lgn_dw(t);
+    // warps take rows from the queue one at a time, so a warp that drew long rows takes fewer
+    const int nq = tg >= 0 ? s_misc[2] : 0;
+    auto pop_row = [&]() {
+      int q = 0;
+      if (lane == 0) q = atomicAdd(&s_misc[3], 1);
+      return __shfl_sync(0xffffffffu, q, 0);
+    };
+    if (fast_rows) {
+      // Packed-record path.  The unit of work is a pass: up to UF*32 consecutive synapses of one
+      // row, one 8-byte record per synapse.  Warps draw rows from the queue of row descriptors
+      // written in phase A.  Each warp keeps the records of the pass after next
+      // and the Q rows of the next pass in flight while it accumulates the current one.  Registers
+      // that receive a load are never copied while the load is in flight (a copy would wait for
+      // it): the loop body is written out once per Q buffer, NS buffers in rotation.
+      // The Q row index comes from a per-step table of the D slot bases.  Steps past the end of
+      // the rollout need no test: their ring slots still hold the zeros of the initial clear.
+      // Lanes past the end of a row read a neighbouring record (always inside the array) and get
+      // weight zero.
+      constexpr int NB = PACK ? 5 : BP_;     // batch values a row really carries
+      constexpr int QV = QW / 4;             // 16-byte words per Q row
+      constexpr int UF = QV == 1 ? 4 : 2;    // 32-synapse groups per pass
+      constexpr int NS = V1G_BWD_STAGES;
+      struct Pass { int jb, j1, kz, fl; };   // kz = row | spike mask << 16; fl: 1 first pass of its row, 4 valid
+      const int jmax = a.rec_nnz - 1;
+      Pass pr{0, 0, 0, 0};
+      Pass ps_[NS];
+      uint2 rec[UF];
+      float4 qS[NS][UF][QV];
+      float wS[NS][UF];
+      float acc[BP_];
+#pragma unroll
+      for (int i = 0; i < NS; ++i) ps_[i] = Pass{0, 0, 0, 0};
+#pragma unroll
+      for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
+      auto issue_rec = [&]() {  // advance pr to the following pass and request its records
+        if (pr.fl && pr.jb + 32 * UF < pr.j1) {
+          pr.jb += 32 * UF;
+          pr.fl = 4;
+        } else {
+          const int q = pop_row();  // warps that drew long rows, or rows with spikes, take fewer
+          if (q < nq) {
+            const int4 d = rowd_s[q];
+            pr = Pass{d.x, d.y, d.z, 5};
+          } else {
+            pr = Pass{0, 0, 0, 0};
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UF; ++u) rec[u] = __ldcs(a.rec_syn8 + min(pr.jb + u * 32 + lane, jmax));
+      };
+      auto issue_q = [&](const Pass& ps, float4 (&q)[UF][QV], float (&w)[UF]) {  // Q rows of the pass in rec
+#pragma unroll
+        for (int u = 0; u < UF; ++u) {
+          const bool in_row = ps.jb + u * 32 + lane < ps.j1;
+          const unsigned w0 = rec[u].x;
+          unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + ((w0 >> 22) & 127u);
+          row = in_row ? row : 0u;  // lanes past the end of the row share one request
+          const float4* qp = (const float4*)(a.Q + row * (unsigned)QW);  // < 2^31 words, checked by the host
+#pragma unroll
+          for (int v = 0; v < QV; ++v) q[u][v] = __ldcg(qp + v);
+          w[u] = in_row ? __uint_as_float(rec[u].y) : 0.f;
+        }
+      };
+      auto compute = [&](const Pass& ps, const float4 (&q)[UF][QV], const float (&w)[UF]) {
+        if (ps.fl & 1) {
+#pragma unroll
+          for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
+        }
+        const unsigned zm = (unsigned)ps.kz >> 16;
+        if (!zm) {
+#pragma unroll
+          for (int u = 0; u < UF; ++u) {
+            float pj[BP_];
+            unpack_row<BP_, PACK>(q[u], pj);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
+          }
+        } else {
+          // the source neuron spiked at this step in the batch rows of zm: weight gradient
+#pragma unroll
+          for (int u = 0; u < UF; ++u) {
+            float pj[BP_];
+            unpack_row<BP_, PACK>(q[u], pj);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
+            const int j = ps.jb + u * 32 + lane;
+            if (j < ps.j1) {
+              float dwv = 0.f;
+#pragma unroll
+              for (int b = 0; b < NB; ++b)
+                if (zm & (1u << b)) dwv += pj[b];
+              a.dw_rec[j] += dwv;  // this lane is the only writer of the synapse
+            }
+          }
+        }
+        if (ps.jb + 32 * UF >= ps.j1) reduce_store(acc, ps.kz & 0xffff);
+      };
+      // one turn of the pipeline with buffer I: false when the warp has no further pass
+      auto turn = [&](auto I) -> bool {
+        constexpr int i = decltype(I)::value;
+        if (!pr.fl) {
+          // accumulate what is still in flight, oldest first
+#pragma unroll
+          for (int o = 1; o < NS; ++o)
+            if (ps_[(i + o) % NS].fl) compute(ps_[(i + o) % NS], qS[(i + o) % NS], wS[(i + o) % NS]);
+          return false;
+        }
+        ps_[i] = pr;
+        issue_q(ps_[i], qS[i], wS[i]);
+        issue_rec();
+        constexpr int x = (i + 1) % NS;  // the oldest pass
+        if (ps_[x].fl) {
+          compute(ps_[x], qS[x], wS[x]);
+          ps_[x].fl = 0;
+        }
+        return true;
+      };
+      issue_rec();
+      for (;;) {
+        if (!turn(std::integral_constant<int, 0>{})) break;
+        if (!turn(std::integral_constant<int, 1 % NS>{})) break;
+        if (NS > 2 && !turn(std::integral_constant<int, 2 % NS>{})) break;
+        if (NS > 3 && !turn(std::integral_constant<int, 3 % NS>{})) break;
+      }
+    } else
+    for (;;) {
+      const int qi = pop_row();
+      if (qi >= nq) break;
+      const int k = rowq_s[qi];
+      int cpost[U], csid[U];
+      float cw[U];
+      load_pass(rpx[k * D], rpx[k * D + D], cpost, csid, cw);
+      const unsigned zm = zmask_s[k];
+      const int32_t* rp = rpx + k * D;
+      int bound[DMAX + 1];
+#pragma unroll
+      for (int d = 0; d <= DMAX; ++d) bound[d] = rp[d <= D ? d : D];
+      const int j0 = bound[0], j1 = rp[D];
+      float acc[BP_];
+#pragma unroll
+      for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
+      for (int jb = j0; jb < j1; jb += 32 * U) {
+        if (jb != j0) load_pass(jb, j1, cpost, csid, cw);  // rows longer than one pass
+        int slot[U];
+        bool valid[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int j = jb + u * 32 + lane;
+          valid[u] = j < j1;
+          int d = 1;
+#pragma unroll
+          for (int q = 1; q < DMAX; ++q) d += (q < D && j >= bound[q]) ? 1 : 0;
+          if (tg + d >= T) valid[u] = false;  // no step after the rollout's end
+          slot[u] = tk + d;
+          if (slot[u] >= K) slot[u] -= K;
+          if (!valid[u]) {
+            slot[u] = tk;
+            cw[u] = 0.f;
+            cpost[u] = 0;
+            csid[u] = 0;
+          }
+        }
+        float pj[U][BP_];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const float* Qp = a.Q + (unsigned)((slot[u] * Np + cpost[u]) * C) * QW;  // < 2^31, checked by the host
+          if (PROJ) {
+            load_row<BP_, PACK>(Qp + csid[u] * QW, pj[u]);
+          } else {
+#pragma unroll
+            for (int b = 0; b < BP_; ++b) pj[u][b] = 0.f;
+#pragma unroll
+            for (int r = 0; r < R_; ++r) {
+              float q[BP_];
+              load_row<BP_, PACK>(Qp + r * QW, q);
+              const float bs = basis_s[csid[u] * R_ + r];
+#pragma unroll
+              for (int b = 0; b < BP_; ++b) pj[u][b] += q[b] * bs;
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int b = 0; b < BP_; ++b) acc[b] += cw[u] * pj[u][b];
+          if (zm && valid[u]) {
+            float dwv = 0.f;
+#pragma unroll
+            for (int b = 0; b < BP_; ++b)
+              if (zm & (1u << b)) dwv += pj[u][b];
+            a.dw_rec[jb + u * 32 + lane] += dwv;  // this lane is the only writer of the synapse
+          }
+        }
+      }
+      reduce_store(acc, k);
+      if (lane == 0) {
+        c_rows += (unsigned long long)D;
+        c_events += (unsigned long long)(j1 - j0);
+        if (zm) c_dw += (unsigned long long)(j1 - j0) * __popc(zm);
+      }
+    }
+        __syncthreads();
     if (prof) {
       const unsigned long long ph3 = gtime_b();
       ph_a += ph1 - ph0;
-      ph_b += ph2 - ph1;
-      ph_c += ph3 - ph2;
+      ph_c += ph2 - ph1;
+      ph_b += ph3 - ph2;
     }
   }
-  // ---- full barrier, then the LGN events of step 0 (Q(0) was published at step 2) ----
+  // ---- full barrier: Q(0..D-1) of every block is in the ring ----
   __syncthreads();
   if (tid == 0) {
     if (ok && T >= 1) v1g_arrive(v1g_phase_counter(a.barrier, T));
@@ -755,12 +784,11 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   }
   __syncthreads();
   ok = ok && !s_misc[1];
-  if (ok && T >= 1) lgn_dw(0);
   // Spikes that were pending in the initial z_buf (emitted at step -(kb+1), bit kb) are delivered
   // at steps 0..D-1 and contribute to the recurrent weight gradient; Q(0..D-1) is still in the ring.
   if (ok && a.hist0) {
     for (int k = warp; k < cn; k += NW) {
-      const int32_t* rp = rp_s + k * D;
+      const int32_t* rp = rpx + k * D;
       const int j0 = rp[0], j1 = rp[D];
       for (int b = 0; b < B; ++b) {
         const unsigned hbits = a.hist0[(int64_t)b * N + n0 + k];
@@ -985,7 +1013,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
     return v1g_fail(h, V1G_ESTATE, "v1g_rollout_bwd needs a preceding v1g_rollout_fwd with save_for_bwd");
   cudaStream_t st = (cudaStream_t)stream;
   const V1GConfig& c = h->cfg;
-  const int N = c.n_neurons, R = c.n_receptors, D = c.max_delay, K = D + 6, S = c.n_syn_types;
+  const int N = c.n_neurons, R = c.n_receptors, D = c.max_delay, K = D + 3, S = c.n_syn_types;
   const int B = h->tape_B, T = h->tape_T;
   if (R != 4 && R != 5)
     return v1g_fail(h, V1G_ERANGE, "backward rollout is built for 4 or 5 receptor channels, got %d", R);
@@ -1002,13 +1030,15 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
 
   V1GRolloutPlan plan;
   v1g_plan_rollout(h, B, 3 + 2 * R, 0, 0, &plan);
+  plan.chunkP = (plan.chunk + 3) & ~3;  // planes only need 16-byte alignment here
   if (plan.chunkP > 65535) return v1g_fail(h, V1G_ERANGE, "slice of %d neurons per block exceeds 65535", plan.chunkP);
   auto al = [](size_t b) { return (b + 15) & ~(size_t)15; };
   const size_t plane = (size_t)B * plan.chunkP;
-  size_t smem = al(sizeof(float) * S * R) + 2 * al(sizeof(float) * plane) + al(plane) +
+  const bool fast = proj && !h->opt_no_meta && h->src[V1G_SRC_REC].syn8 != nullptr;  // packed-record gather
+  size_t smem = al(sizeof(float) * S * R) + 2 * al(sizeof(float) * 2 * plane) + al(2 * plane) +
                 2 * al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 4) + al(sizeof(int) * 8) +
                 al(sizeof(uint16_t) * plan.chunkP) + al(sizeof(int4) * plan.chunkP) +
-                al(sizeof(int32_t) * ((size_t)plan.chunkP * D + 1)) + 6 * al(sizeof(float) * plan.chunkP) +
+                (fast ? 0 : al(sizeof(int32_t) * ((size_t)plan.chunkP * D + 1))) +
                 al(sizeof(int) * (plan.chunkP + 1));
   const size_t state_bytes = al(sizeof(float) * plane * (3 + 2 * R));
   int state_in_smem = 0;
