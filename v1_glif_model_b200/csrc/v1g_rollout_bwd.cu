@@ -78,6 +78,9 @@ struct BwdArgs {
 #ifndef V1G_BWD_NT
 #define V1G_BWD_NT 512
 #endif
+#ifndef V1G_BWD_GROUPS
+#define V1G_BWD_GROUPS 4  // 32-synapse groups of a gather pass with 16-byte Q rows (3, 5, 6 measured slower)
+#endif
 #ifndef V1G_BWD_STAGES
 #define V1G_BWD_STAGES 2  // Q-row buffers of the gather pipeline (registers: 20 per stage)
 #endif
@@ -583,7 +586,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       // weight zero.
       constexpr int NB = PACK ? 5 : BP_;     // batch values a row really carries
       constexpr int QV = QW / 4;             // 16-byte words per Q row
-      constexpr int UF = QV == 1 ? 4 : 2;    // 32-synapse groups per pass
+      constexpr int UF = QV == 1 ? V1G_BWD_GROUPS : 2;  // 32-synapse groups per pass
       constexpr int NS = V1G_BWD_STAGES;
       struct Pass { int jb, j1, kz, fl; };   // kz = row | spike mask << 16; fl: 1 first pass of its row, 4 valid
       const int jmax = a.rec_nnz - 1;
