@@ -45,7 +45,7 @@ struct BwdArgs {
   const uint8_t* bkg_insid;
   const float *decay, *cf, *asc_decay, *basis;
   float sd[V1G_MAX_RECEPTORS], pinit[V1G_MAX_RECEPTORS], dtsd[V1G_MAX_RECEPTORS];
-  float lr_scale, vd_keep, rec_factor, damp, width, gauss_std;
+  float lr_scale, vd_keep, rec_factor, damp, inv_width, gauss_std;
   int gauss, hard_reset, csr_evict_first;
   // saved forward
   const float* tape_v;
@@ -86,6 +86,7 @@ struct BwdArgs {
 #endif
 constexpr int NT = V1G_BWD_NT;
 constexpr int NW = NT / 32;
+constexpr int BAR_TID = NT - 32;  // the thread that talks to the grid-wide phase counters
 
 __device__ __forceinline__ unsigned long long gtime_b() {
   unsigned long long t;
@@ -96,7 +97,7 @@ __device__ __forceinline__ unsigned long long gtime_b() {
 __device__ __forceinline__ float pseudo_h(float vs, const BwdArgs& a) {
   if (a.gauss) return expf(-(vs * vs) / (a.gauss_std * a.gauss_std)) * a.damp;
   float x = fabsf(vs);
-  if (a.width != 1.f) x = x / a.width;
+  x = x * a.inv_width;
   return a.damp * fmaxf(1.f - x, 0.f);
 }
 
@@ -178,8 +179,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   uint8_t* tz_s = (uint8_t*)take(2 * plane);               // spike / refractory bits
   uint8_t* need_s = (uint8_t*)take(chunkP);            // row must be walked
   uint8_t* zmask_s = (uint8_t*)take(chunkP);           // batch rows that spiked at this step
-  int* s_cnt = (int*)take(sizeof(int) * nb);
-  int* s_misc = (int*)take(sizeof(int) * 4);  // [1] abort flag, [2] rows queued, [3] next queue slot
+  float* s_cnt = (float*)take(sizeof(float) * nb);  // background counts of step t-2, as floats
+  int* s_misc = (int*)take(sizeof(int) * 8);  // [1] abort flag, [2+p] rows queued, [4+p] next queue slot (p = parity of the iteration)
   int* slot_s = (int*)take(sizeof(int) * 8);  // first Q row of step t+1+d, d = 0..7
   uint16_t* rowq_s = (uint16_t*)take(sizeof(uint16_t) * chunkP);  // rows to walk this step
   int4* rowd_s = (int4*)take(sizeof(int4) * chunkP);  // the same rows as {first synapse, end, row | spike mask << 16, 0}
@@ -229,7 +230,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     bk_dw = bk_dw_s;
   }
   for (int i = tid; i < (int)plane * (3 + 2 * R_); i += NT) base[i] = 0.f;
-  if (tid < 4) s_misc[tid] = 0;
+  if (tid < 8) s_misc[tid] = 0;
   __syncthreads();
   if (tid == 0) v1g_arrive(v1g_phase_counter(a.barrier, 0));
 
@@ -301,6 +302,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
 
   // Tape of step ts into the planes of its parity: v, spike / refractory bits, the rows that must be
   // walked (queue and descriptors) and zeros in the spike-gradient plane for those that need not.
+  int* q_cnt_cur = s_misc + 2;  // queue counter of the current iteration
   auto load_step = [&](int ts, float* tvp, uint8_t* tzp, float* gzp, bool queue) {
     for (int k0 = 0; k0 < cn; k0 += NT) {
       const int k = k0 + tid;
@@ -341,7 +343,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       const unsigned wm = __ballot_sync(0xffffffffu, walk);
       if (wm) {
         int base = 0;
-        if (lane == 0) base = atomicAdd(&s_misc[2], __popc(wm));
+        if (lane == 0) base = atomicAdd(q_cnt_cur, __popc(wm));
         base = __shfl_sync(0xffffffffu, base, 0);
         if (walk) {
           const int qpos = base + __popc(wm & ((1u << lane) - 1u));
@@ -382,32 +384,37 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     float* const gzC = gz_s + (t & 1) * plane;
     float* const gzB = gz_s + ((t & 1) ^ 1) * plane;
     const unsigned long long ph0 = prof ? gtime_b() : 0;
-    if (tid == 0 && it >= 1) {
+    int* const q_cnt = s_misc + 2 + (it & 1);  // rows queued / next queue slot of this iteration
+    int* const q_pop = s_misc + 4 + (it & 1);
+    if (tid == 0) {
+      s_misc[2 + ((it + 1) & 1)] = 0;  // the counters of the next iteration
+      s_misc[4 + ((it + 1) & 1)] = 0;
+    }
+    if (tid < 8) slot_s[tid] = ((tg + 1 + tid) % K) * Np * C;
+    // Lagged barrier, by a thread of the last warp (which owns no neuron when the slice has fewer
+    // neurons than the block has threads) while the others load the tape: this block has finished
+    // iteration it-1; every block must have finished iteration it-2 before the gather below.
+    if (tid == BAR_TID && it >= 1) {
+      v1g_arrive(v1g_phase_counter(a.barrier, it));
       const unsigned long long target = v1g_phase_target(it - 1, G);
       if (seen < target)
         seen = v1g_wait(v1g_phase_counter(a.barrier, it - 1), target, a.spin_limit, a.status);
       if (seen < target) s_misc[1] = 1;
     }
-    if (tid == 0) {
-      s_misc[2] = 0;  // row queue of this step
-      s_misc[3] = 0;
-    }
-    if (tid < 8) slot_s[tid] = ((tg + 1 + tid) % K) * Np * C;
+
+    // ---------------- phase A: tape of step t-1, row flags, counts of step t-2 ----------------
+    q_cnt_cur = q_cnt;
+    if (tg >= 0) load_step(tg, tv_s + ((t & 1) ^ 1) * plane, tz_s + ((t & 1) ^ 1) * plane, gzB, true);
+    if (t >= 2)
+      for (int i = tid; i < nb; i += NT) {
+        const int b = i / a.n_bkg, j = i - b * a.n_bkg;
+        s_cnt[i] = (float)a.bkg_counts[((int64_t)b * T + (t - 2)) * a.n_bkg + j];
+      }
     __syncthreads();
     if (s_misc[1]) {
       ok = false;
       break;
     }
-    if (tid == 0 && it >= 1) v1g_arrive(v1g_phase_counter(a.barrier, it));
-
-    // ---------------- phase A: tape of step t-1, row flags, counts of step t-2 ----------------
-    if (tg >= 0) load_step(tg, tv_s + ((t & 1) ^ 1) * plane, tz_s + ((t & 1) ^ 1) * plane, gzB, true);
-    if (t >= 2)
-      for (int i = tid; i < nb; i += NT) {
-        const int b = i / a.n_bkg, j = i - b * a.n_bkg;
-        s_cnt[i] = a.bkg_counts[((int64_t)b * T + (t - 2)) * a.n_bkg + j];
-      }
-    __syncthreads();
     const unsigned long long ph1 = prof ? gtime_b() : 0;
 
     // ---------------- dense adjoint of step t, publish Q(t-2), background weight gradient ----------------
@@ -485,30 +492,31 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
               __stcg(qd + c * 2 + 1, make_float4(row[4 % BP_], row[5 % BP_], row[6 % BP_], row[7 % BP_]));
           }
         }
-        // background weight gradient of step t-2 for the synapses this thread owns
+        // background weight gradient of step t-2 for the synapses this thread owns (branch-free:
+        // a zero count contributes zero)
         for (int j = bkptr_s[k]; j < bkptr_s[k + 1]; ++j) {
           const int pre = bk_pre[j];
           const float* bs = basis_s + (int)bk_sid[j] * R_;
+          float bsr[R_];
+#pragma unroll
+          for (int r = 0; r < R_; ++r) bsr[r] = bs[r];
           float accw = 0.f;
 #pragma unroll
           for (int b = 0; b < BP_; ++b) {
             if (b < B) {
-              const int cnt = s_cnt[b * a.n_bkg + pre];
-              if (cnt > 0) {
-                float s2 = 0.f;
+              float s2 = 0.f;
 #pragma unroll
-                for (int r = 0; r < R_; ++r) s2 += dyv[b][r] * bs[r];
-                accw += s2 * (float)cnt;
-              }
+              for (int r = 0; r < R_; ++r) s2 += dyv[b][r] * bsr[r];
+              accw += s2 * s_cnt[b * a.n_bkg + pre];
             }
           }
-          if (accw != 0.f) bk_dw[j] += accw;
+          if (a.bkg_in_smem || accw != 0.f) bk_dw[j] += accw;
         }
       }
     }
     const unsigned long long ph2 = prof ? gtime_b() : 0;
     // ---------------- gather of step t-1 over the out-synapses of every needed neuron ----------------
-    if (tid == 0) seen = v1g_ld_acquire(v1g_phase_counter(a.barrier, it));
+    if (tid == BAR_TID) seen = v1g_ld_acquire(v1g_phase_counter(a.barrier, it));
     const int tk = (tg + K) % K;
     constexpr int U = PROJ ? 4 : 1;  // row iterations (32 synapses each) kept in flight per warp
     // one pass = U*32 consecutive synapses of a row, lane l holding synapses jb + u*32 + l
@@ -567,10 +575,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     // the few warps that hold one start on the row queue a little later and simply take fewer rows.
     if (it >= 2) lgn_dw(t);
     // warps take rows from the queue one at a time, so a warp that drew long rows takes fewer
-    const int nq = tg >= 0 ? s_misc[2] : 0;
+    const int nq = tg >= 0 ? *q_cnt : 0;
     auto pop_row = [&]() {
       int q = 0;
-      if (lane == 0) q = atomicAdd(&s_misc[3], 1);
+      if (lane == 0) q = atomicAdd(q_pop, 1);
       return __shfl_sync(0xffffffffu, q, 0);
     };
     if (fast_rows) {
@@ -1039,7 +1047,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   const size_t plane = (size_t)B * plan.chunkP;
   const bool fast = proj && !h->opt_no_meta && h->src[V1G_SRC_REC].syn8 != nullptr;  // packed-record gather
   size_t smem = al(sizeof(float) * S * R) + 2 * al(sizeof(float) * 2 * plane) + al(2 * plane) +
-                2 * al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 4) + al(sizeof(int) * 8) +
+                2 * al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 8) + al(sizeof(int) * 8) +
                 al(sizeof(uint16_t) * plan.chunkP) + al(sizeof(int4) * plan.chunkP) +
                 (fast ? 0 : al(sizeof(int32_t) * ((size_t)plan.chunkP * D + 1))) +
                 al(sizeof(int) * (plan.chunkP + 1));
@@ -1128,7 +1136,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
     a.dtsd[r] = c.dt * a.sd[r];
   }
   a.lr_scale = c.lr_scale; a.vd_keep = h->vd_keep; a.rec_factor = h->rec_grad_factor;
-  a.damp = c.dampening_factor; a.width = c.pseudo_width; a.gauss_std = c.gauss_std;
+  a.damp = c.dampening_factor; a.inv_width = 1.f / c.pseudo_width; a.gauss_std = c.gauss_std;
   a.gauss = (c.flags & V1G_FLAG_PSEUDO_GAUSS) ? 1 : 0;
   a.hard_reset = (c.flags & V1G_FLAG_HARD_RESET) ? 1 : 0;
   a.csr_evict_first = h->opt_csr_evict_first;
