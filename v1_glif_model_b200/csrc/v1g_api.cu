@@ -132,6 +132,7 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   cudaFree(h->d_count);
   if (h->h_count) cudaFreeHost(h->h_count);
   cudaFree(h->lgn_entries);
+  cudaFree(h->lgn_ent4);
   cudaFree(h->lgn_offsets);
   cudaFree(h->ring);
   cudaFree(h->state_ws);
@@ -219,7 +220,7 @@ extern "C" int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz,
   std::vector<int32_t> rowptr((size_t)n_source_cols + 1), post((size_t)nnz), perm((size_t)nnz);
   std::vector<uint8_t> sid((size_t)nnz);
   std::vector<uint2> syn8;
-  const bool want_syn8 = source == V1G_SRC_REC && S <= 128 && D <= 8 && N < (1 << 22);
+  const bool want_syn8 = source != V1G_SRC_BKG && S <= 128 && D <= 8 && N < (1 << 22);
   if (want_syn8) syn8.resize((size_t)nnz);
   int64_t pos = 0;
   for (int64_t src = 0; src < n_src; ++src) {

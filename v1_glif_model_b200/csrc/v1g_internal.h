@@ -31,8 +31,8 @@ struct V1GSource {
   int32_t* perm = nullptr;    // [nnz] CSR position -> position in the caller's arrays
   uint8_t* pos_int = nullptr; // [nnz] sign mask (w >= 0 at the first v1g_set_weights), internal order
   bool pos_set = false;
-  // [nnz] packed synapse records for the backward gather (recurrent source only, when N < 2^22 and
-  // S <= 128): x = post | sid << 22 | (delay-1) << 29, y = bits of the weight (kept equal to w)
+  // [nnz] packed synapse records for the rollout kernels (recurrent and LGN sources, when N < 2^22
+  // and S <= 128): x = post | sid << 22 | (delay-1) << 29, y = bits of the weight (kept equal to w)
   uint2* syn8 = nullptr;
   // post-major table in the caller's order (the reference sorts synapses by post, so this is a
   // plain row pointer over the caller's arrays)
@@ -78,6 +78,8 @@ struct V1GHandle {
   int32_t* d_count = nullptr;  // device int for counts
   int32_t* h_count = nullptr;  // pinned host mirror
   uint32_t* lgn_entries = nullptr;
+  uint4* lgn_ent4 = nullptr;  // the same events resolved: {batch row << 24 | unit, first synapse, end, 0}
+  int64_t lgn_ent4_cap = 0;
   int64_t lgn_entries_cap = 0;
   int32_t* lgn_offsets = nullptr;  // [T*B*nseg + 1]
   int64_t lgn_offsets_cap = 0;

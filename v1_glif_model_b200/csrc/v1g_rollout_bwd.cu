@@ -52,7 +52,7 @@ struct BwdArgs {
   const uint8_t* tape_zr;
   const uint8_t* hist0;  // initial spike-history bits [B][N], or NULL for a zero initial state
   const int32_t* lgn_off;
-  const uint32_t* lgn_entries;
+  const uint4* lgn_ent4;  // {batch row << 24 | unit, first synapse, end, 0} per event
   int lgn_nseg;
   const int32_t* bkg_counts;
   // loss
@@ -253,9 +253,9 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     const float* Qs = a.Q + (int64_t)(tt % K) * Np * C * QW;
     constexpr int UL = 4;
     for (int e = e0 + gw; e < e1; e += gnw) {
-      const uint32_t ent = a.lgn_entries[e];
-      const int b = ent >> 24, u = ent & 0xffffff;
-      const int j0 = a.lgn_rowptr[u], j1 = a.lgn_rowptr[u + 1];
+      const uint4 ent = a.lgn_ent4[e];
+      const int b = ent.x >> 24;
+      const int j0 = (int)ent.y, j1 = (int)ent.z;
       for (int jb = j0; jb < j1; jb += 32 * UL) {
         int post[UL], sid[UL];
 #pragma unroll
@@ -1142,7 +1142,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   a.csr_evict_first = h->opt_csr_evict_first;
   a.tape_v = h->tape_v; a.tape_zr = h->tape_zr;
   a.hist0 = h->tape_has_hist0 ? h->tape_hist0 : nullptr;
-  a.lgn_off = h->lgn_offsets; a.lgn_entries = h->lgn_entries; a.lgn_nseg = h->lgn_nseg;
+  a.lgn_off = h->lgn_offsets; a.lgn_ent4 = h->lgn_ent4; a.lgn_nseg = h->lgn_nseg;
   a.bkg_counts = h->tape_counts;
   a.rate_coef = want_rate ? rate_coef : nullptr;
   a.sgrad = want_sync ? sgrad : nullptr;

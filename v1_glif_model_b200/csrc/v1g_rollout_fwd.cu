@@ -25,6 +25,19 @@ namespace {
 constexpr int NT = 768;
 
 // bit d-1 of hist0[b*N+n] = neuron n of batch row b spiked d steps before the rollout starts
+// LGN event list with the bounds of each event's synapse row, so that the rollout kernels need no
+// dependent row-pointer load per event
+__global__ void lgn_resolve_kernel(const uint32_t* __restrict__ entries, int64_t n,
+                                   const int32_t* __restrict__ rowptr, uint4* __restrict__ out) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const uint32_t ent = entries[i];
+    const uint32_t u = ent & 0xffffffu;
+    out[i] = make_uint4(ent, (uint32_t)rowptr[u], (uint32_t)rowptr[u + 1], 0u);
+  }
+}
+
 __global__ void __launch_bounds__(256) hist0_kernel(const float* __restrict__ z_buf, int B, int D, int N,
                                                     uint8_t* __restrict__ hist0) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -165,8 +178,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
     v1g_walk_rec<R_>(a, basis_s, lane, b, a.rec_rowptr + (int64_t)n * D, te, c_rec_ev);
   };
   auto scatter_lgn = [&](int tt) {
-    v1g_scatter_lgn<R_>(a, basis_s, lane, blockIdx.x * NW + warp, gridDim.x * NW, tt, c_lgn_rows,
-                        c_lgn_ev);
+    v1g_scatter_lgn<R_>(a, basis_s, lane, blockIdx.x * NW + warp, gridDim.x * NW, v1g_lgn_begin(a, tt),
+                        v1g_lgn_begin(a, tt + 1), tt % a.K, c_lgn_rows, c_lgn_ev);
   };
 
   // ---- prologue: pending deliveries of the initial spike buffer, LGN events of step 0 ----
@@ -523,6 +536,13 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
   if ((rc = v1g_compact_fill(h, V1G_COMPACT_U8_PACKED, x, B * T, c.n_lgn, T, h->lgn_offsets,
                              h->lgn_entries, n_lgn_events, st)))
     return rc;
+  if ((rc = v1g_reserve(h, &h->lgn_ent4, &h->lgn_ent4_cap, n_lgn_events + 1))) return rc;
+  if (n_lgn_events > 0) {
+    lgn_resolve_kernel<<<(unsigned)std::min<int64_t>((n_lgn_events + 255) / 256, 148 * 8), 256, 0, st>>>(
+        h->lgn_entries, n_lgn_events, h->src[V1G_SRC_LGN].rowptr, h->lgn_ent4);
+    v1g_count_launches(1);
+    V1G_CUDA(h, cudaGetLastError());
+  }
   h->lgn_nseg = nseg;
 
   // ---- plan ----
@@ -602,7 +622,9 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
   }
   a.lr_scale = c.lr_scale; a.vd_keep = h->vd_keep; a.vd_drop = h->vd_drop;
   a.hard_reset = (c.flags & V1G_FLAG_HARD_RESET) ? 1 : 0;
-  a.lgn_off = h->lgn_offsets; a.lgn_entries = h->lgn_entries; a.lgn_nseg = nseg;
+  a.lgn_off = h->lgn_offsets; a.lgn_entries = h->lgn_entries; a.lgn_ent4 = h->lgn_ent4; a.lgn_nseg = nseg;
+  a.rec_syn8 = h->opt_no_meta ? nullptr : h->src[V1G_SRC_REC].syn8;
+  a.lgn_syn8 = h->opt_no_meta ? nullptr : h->src[V1G_SRC_LGN].syn8;
   a.bkg_counts = bkg_counts;
   if (state) a.st = *state; else a.st = V1GState{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   a.state_ws = h->state_ws;

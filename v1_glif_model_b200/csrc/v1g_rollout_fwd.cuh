@@ -25,6 +25,9 @@ struct FwdArgs {
   // inputs
   const int32_t* lgn_off;  // exclusive offsets per (t, b, seg) segment
   const uint32_t* lgn_entries;
+  const uint4* lgn_ent4;  // {batch row << 24 | unit, first synapse, end, 0} per event
+  // packed synapse records {post | sid << 22 | (delay-1) << 29, weight bits}, or NULL
+  const uint2 *rec_syn8, *lgn_syn8;
   int lgn_nseg;
   const int32_t* bkg_counts;  // [B][T][n_bkg]
   // state (reference layouts, all NULL = zero state / no write-back)
@@ -87,32 +90,82 @@ __device__ __forceinline__ void v1g_walk_rec(const FwdArgs& a, const float* basi
   if (lane == 0) events += (unsigned long long)(j1 - j0);
 }
 
-// LGN events of step tt into ring slot tt mod K; the list is shared by all warps of the grid
-// (gw = global warp index, gnw = warps in the grid).
+// first event of step tt in the time-major LGN list (tt = T gives the end of the list)
+__device__ __forceinline__ int v1g_lgn_begin(const FwdArgs& a, int tt) {
+  return a.lgn_off[(int64_t)tt * a.B * a.lgn_nseg];
+}
+
+// LGN events [e0, e1) of one step into ring slot `slot`; the list is shared by all warps of the grid
+// (gw = global warp index, gnw = warps in the grid).  Each event carries the bounds of its row.
 template <int R_>
 __device__ __forceinline__ void v1g_scatter_lgn(const FwdArgs& a, const float* basis_s, int lane,
-                                                int gw, int gnw, int tt, unsigned long long& rows,
-                                                unsigned long long& events) {
-  const int seg_per_t = a.B * a.lgn_nseg;
-  const int e0 = a.lgn_off[(int64_t)tt * seg_per_t], e1 = a.lgn_off[(int64_t)(tt + 1) * seg_per_t];
-  const int slot = tt % a.K;
+                                                int gw, int gnw, int e0, int e1, int slot,
+                                                unsigned long long& rows, unsigned long long& events) {
+  constexpr int UL = 3;  // 32-synapse groups whose loads are in flight together
   for (int e = e0 + gw; e < e1; e += gnw) {
-    const uint32_t ent = a.lgn_entries[e];
-    const int b = ent >> 24, u = ent & 0xffffff;
-    const int j0 = a.lgn_rowptr[u], j1 = a.lgn_rowptr[u + 1];
-    for (int j = j0 + lane; j < j1; j += 32) {
-      const float wv = a.lgn_w[j];
-      const float* bs = basis_s + (int)a.lgn_sid[j] * R_;
-      float* dst = a.ring + ((int64_t)(slot * a.B + b) * R_) * a.Np + a.lgn_post[j];
+    const uint4 ent = a.lgn_ent4[e];
+    const int b = ent.x >> 24;
+    const int j0 = (int)ent.y, j1 = (int)ent.z;
+    float* const ring_b = a.ring + ((int64_t)(slot * a.B + b) * R_) * a.Np;
+    for (int jb = j0; jb < j1; jb += 32 * UL) {
+      float wv[UL];
+      int sid[UL], post[UL];
 #pragma unroll
-      for (int r = 0; r < R_; ++r) {
-        const float c = wv * bs[r];
-        if (c != 0.f) atomicAdd(dst + (int64_t)r * a.Np, c);
+      for (int q = 0; q < UL; ++q) {
+        const int j = jb + q * 32 + lane;
+        const bool in = j < j1;
+        wv[q] = in ? a.lgn_w[j] : 0.f;
+        sid[q] = in ? (int)a.lgn_sid[j] : 0;
+        post[q] = in ? a.lgn_post[j] : 0;
+      }
+#pragma unroll
+      for (int q = 0; q < UL; ++q) {
+        const float* bs = basis_s + sid[q] * R_;
+        float* dst = ring_b + post[q];
+#pragma unroll
+        for (int r = 0; r < R_; ++r) {
+          const float c = wv[q] * bs[r];
+          if (c != 0.f) atomicAdd(dst + (int64_t)r * a.Np, c);
+        }
       }
     }
     if (lane == 0) {
       rows += 1;
       events += (unsigned long long)(j1 - j0);
+    }
+  }
+}
+
+// Packed-record form of the two walks above: one 8-byte load per synapse, the (up to 128) synapses
+// of a pass requested together, so that a warp pays one memory latency per pass before its atomics.
+// Synapses [j0, j1) of one source row; te = step of emission (delay from the record), slot0 = ring
+// slot of step te.
+template <int R_>
+__device__ __forceinline__ void v1g_scatter_row8(const FwdArgs& a, const uint2* __restrict__ syn8,
+                                                 const float* basis_s, int lane, int b, int j0, int j1,
+                                                 int slot0, bool delayed) {
+  constexpr int UL = 4;
+  const int K = a.K;
+  for (int jb = j0; jb < j1; jb += 32 * UL) {
+    uint2 rec[UL];
+#pragma unroll
+    for (int q = 0; q < UL; ++q) {
+      const int j = jb + q * 32 + lane;
+      rec[q] = j < j1 ? __ldg(syn8 + j) : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int q = 0; q < UL; ++q) {
+      const unsigned x = rec[q].x;
+      const float wv = __uint_as_float(rec[q].y);  // zero for the lanes past the end of the row
+      int slot = slot0 + (delayed ? (int)(x >> 29) + 1 : 0);
+      if (slot >= K) slot -= K;
+      const float* bs = basis_s + ((x >> 22) & 127u) * R_;
+      float* dst = a.ring + ((int64_t)(slot * a.B + b) * R_) * a.Np + (x & 0x3fffffu);
+#pragma unroll
+      for (int r = 0; r < R_; ++r) {
+        const float c = wv * bs[r];
+        if (c != 0.f) atomicAdd(dst + (int64_t)r * a.Np, c);
+      }
     }
   }
 }

@@ -10,6 +10,14 @@
 
 namespace {
 
+// asynchronous global -> shared copies of 4 and 16 bytes (both addresses aligned to the size)
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+
 constexpr int NT = V1G_NT_REG;
 constexpr int NW = NT / 32;
 
@@ -33,7 +41,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
   float* basis_s = (float*)take(sizeof(float) * a.S * R_);
   uint32_t* spk_list = (uint32_t*)take(sizeof(uint32_t) * B_ * NT);
   int* s_cnt = (int*)take(sizeof(int) * 2 * nb);
-  int* s_misc = (int*)take(sizeof(int) * 4);
+  // [1] abort, [2],[3] spike counts by parity, [8 + 2*(s&3)], [9 + 2*(s&3)] bounds of the LGN events of step s
+  int* s_misc = (int*)take(sizeof(int) * 16);
+  int2* rowb_s = (int2*)take(sizeof(int2) * NT);   // [first, end) of each neuron's out-synapses
+  uint4* lgn_ent_s = (uint4*)take(sizeof(uint4) * 2 * NW);  // per warp: its first LGN event of the next two steps
   uint2* bk_s = (uint2*)take(sizeof(uint2) * a.bkg_cap);  // (pre | sid << 24, weight bits)
   float* pr_s = (float*)take(sizeof(float) * B_ * R_ * NT) + tid;  // [b][r][tid]
 #define PR(b, r) pr_s[((b)*R_ + (r)) * NT]
@@ -82,7 +93,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
       rh[b] = hist | ((unsigned)(uint8_t)a.st.r[g] << 8);
     }
   }
-  if (tid < 4) s_misc[tid] = 0;
+  if (tid < 16) s_misc[tid] = 0;
+  rowb_s[tid] = active ? make_int2(a.rec_rowptr[(int64_t)n * D], a.rec_rowptr[(int64_t)n * D + D]) : make_int2(0, 0);
   __syncthreads();
 
   unsigned long long c_spikes = 0, c_rec_ev = 0, c_lgn_rows = 0, c_lgn_ev = 0, c_bkg_ev = 0,
@@ -105,7 +117,24 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
       }
     }
   }
-  if (a.T > 0) v1g_scatter_lgn<R_>(a, basis_s, lane, gw, gnw, 0, c_lgn_rows, c_lgn_ev);
+  if (a.T > 0)
+    v1g_scatter_lgn<R_>(a, basis_s, lane, gw, gnw, v1g_lgn_begin(a, 0), v1g_lgn_begin(a, 1), 0, c_lgn_rows, c_lgn_ev);
+  // LGN hand-over: the bounds of the events of steps 1 and 2, and every warp's first event of step 1
+  const bool lgn8 = a.lgn_syn8 != nullptr;
+  if (tid == 0) {
+    for (int s = 1; s <= 2; ++s) {
+      s_misc[8 + 2 * (s & 3)] = s < a.T ? v1g_lgn_begin(a, s) : 0;
+      s_misc[9 + 2 * (s & 3)] = s < a.T ? v1g_lgn_begin(a, s + 1) : 0;
+    }
+  }
+  if (lane == 0) {
+    uint4 ent = make_uint4(0u, 0u, 0u, 0u);
+    if (a.T > 1) {
+      const int e = v1g_lgn_begin(a, 1) + gw;
+      if (e < v1g_lgn_begin(a, 2)) ent = a.lgn_ent4[e];
+    }
+    lgn_ent_s[(1 & 1) * NW + warp] = ent;
+  }
   __syncthreads();
   if (tid == 0) v1g_arrive(v1g_phase_counter(a.barrier, 0));
 
@@ -245,11 +274,60 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
     const int nspk = *nspk_p;
     for (int e = warp; e < nspk; e += NW) {
       const uint32_t ent = spk_list[e];
-      v1g_walk_rec<R_>(a, basis_s, lane, (int)(ent >> 24),
-                       a.rec_rowptr + (int64_t)(n0 + (int)(ent & 0xffffff)) * D, t, c_rec_ev);
+      if (a.rec_syn8) {
+        const int2 rb = rowb_s[ent & 0xffffffu];
+        v1g_scatter_row8<R_>(a, a.rec_syn8, basis_s, lane, (int)(ent >> 24), rb.x, rb.y, t % K, true);
+        if (lane == 0) c_rec_ev += (unsigned long long)(rb.y - rb.x);
+      } else {
+        v1g_walk_rec<R_>(a, basis_s, lane, (int)(ent >> 24),
+                         a.rec_rowptr + (int64_t)(n0 + (int)(ent & 0xffffff)) * D, t, c_rec_ev);
+      }
     }
     if (tid == 0) c_spikes += (unsigned long long)nspk;
-    if (t + 1 < a.T) v1g_scatter_lgn<R_>(a, basis_s, lane, gw, gnw, t + 1, c_lgn_rows, c_lgn_ev);
+    // LGN events of step t+1.  Dependent loads are spread over iterations and handed over in shared
+    // memory: thread 0 fetches the bounds of the events of step t+3, every warp fetches its first
+    // event of step t+2 (bounds known since the previous iteration), and what is left for now is
+    // event (prefetched, with the bounds of its synapse row) -> synapse records -> atomics.
+    // (asynchronous copies straight into shared memory: no register holds a value in flight)
+    if (tid == 0) {
+      int* bd = &s_misc[8 + 2 * ((t + 3) & 3)];
+      if (t + 3 < a.T) {
+        const int64_t spt = (int64_t)a.B * a.lgn_nseg;
+        cp_async_4(bd, a.lgn_off + (int64_t)(t + 3) * spt);
+        cp_async_4(bd + 1, a.lgn_off + (int64_t)(t + 4) * spt);
+      } else {
+        bd[0] = bd[1] = 0;
+      }
+    }
+    if (lane == 0) {
+      uint4* dst = &lgn_ent_s[(t & 1) * NW + warp];  // read in the next iteration (step t+2)
+      const int e = s_misc[8 + 2 * ((t + 2) & 3)] + gw;
+      if (t + 2 < a.T && e < s_misc[9 + 2 * ((t + 2) & 3)])
+        cp_async_16(dst, a.lgn_ent4 + e);
+      else
+        *dst = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (t + 1 < a.T) {
+      const int slot1 = (t + 1) % K;
+      const int e0 = s_misc[8 + 2 * ((t + 1) & 3)], e1 = s_misc[9 + 2 * ((t + 1) & 3)];
+      if (lgn8) {
+        uint4 ent = lgn_ent_s[((t + 1) & 1) * NW + warp];
+        ent.x = __shfl_sync(0xffffffffu, ent.x, 0);
+        ent.y = __shfl_sync(0xffffffffu, ent.y, 0);
+        ent.z = __shfl_sync(0xffffffffu, ent.z, 0);
+        for (int e = e0 + gw; e < e1; e += gnw) {
+          if (e != e0 + gw) ent = a.lgn_ent4[e];  // more events than warps in the grid
+          v1g_scatter_row8<R_>(a, a.lgn_syn8, basis_s, lane, (int)(ent.x >> 24), (int)ent.y, (int)ent.z, slot1, false);
+          if (lane == 0) {
+            c_lgn_rows += 1;
+            c_lgn_ev += (unsigned long long)(ent.z - ent.y);
+          }
+        }
+      } else {
+        v1g_scatter_lgn<R_>(a, basis_s, lane, gw, gnw, e0, e1, slot1, c_lgn_rows, c_lgn_ev);
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");  // own copies landed; the barrier at the top of the next iteration publishes them
     if (prof) {
       const unsigned long long ph3 = gtime();
       ph_barrier += ph1 - ph0;
@@ -375,7 +453,8 @@ size_t v1g_fwd_reg_smem(const V1GHandle* h, int B, int chunkP, int bkg_cap) {
   auto al = [](size_t b) { return (b + 15) & ~(size_t)15; };
   const V1GConfig& c = h->cfg;
   return al(sizeof(float) * c.n_syn_types * c.n_receptors) + al(sizeof(uint32_t) * B * NT) +
-         al(sizeof(int) * 2 * B * c.n_bkg) + al(sizeof(int) * 4) + al(sizeof(uint2) * bkg_cap) +
+         al(sizeof(int) * 2 * B * c.n_bkg) + al(sizeof(int) * 16) + al(sizeof(int2) * NT) + al(sizeof(uint4) * 2 * NW) +
+         al(sizeof(uint2) * bkg_cap) +
          al(sizeof(float) * B * c.n_receptors * NT);
 }
 
