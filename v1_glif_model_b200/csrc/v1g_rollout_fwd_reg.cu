@@ -148,19 +148,19 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
 
   // background input of one batch row of this neuron: sum over its in-synapses of
   // (w * count) * basis[sid, :] (models.py:890-934 in post-major form)
+  unsigned c_bkg32 = 0;  // delivered background events of this thread (widened at the end)
   auto bkg_gather = [&](int b, const int* cnt_s, float (&Gs)[R_]) {
 #pragma unroll
     for (int r = 0; r < R_; ++r) Gs[r] = 0.f;
+    // branch-free: a zero count adds +0 to every channel, which leaves the sums unchanged
     for (int j = bj0; j < bj1; ++j) {
       const uint2 e = bk_s[j];
       const int cnt = cnt_s[b * a.n_bkg + (int)(e.x & 0xffffffu)];
-      if (cnt > 0) {
-        const float wc = __uint_as_float(e.y) * (float)cnt;
-        const float* bs = basis_s + (e.x >> 24) * R_;
+      const float wc = __uint_as_float(e.y) * (float)cnt;
+      const float* bs = basis_s + (e.x >> 24) * R_;
 #pragma unroll
-        for (int r = 0; r < R_; ++r) Gs[r] += wc * bs[r];
-        c_bkg_ev += 1;
-      }
+      for (int r = 0; r < R_; ++r) Gs[r] += wc * bs[r];
+      c_bkg32 += cnt > 0 ? 1u : 0u;
     }
   };
 
@@ -182,14 +182,15 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
     const bool consume = t >= 2;
     const int slot = consume ? (t - 2) % K : 0;
     const int* cnt_s = s_cnt + (t & 1) * nb;
-    int cnt_next[2] = {0, 0};
     if (t >= 1) {
+      // counts of step t-1 for the next iteration, copied asynchronously into the other buffer
+      int* cnt_n = s_cnt + ((t + 1) & 1) * nb;
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         const int i = tid + q * NT;
         if (i < nb) {
           const int b = i / a.n_bkg, j = i - b * a.n_bkg;
-          cnt_next[q] = a.bkg_counts[((int64_t)b * a.T + (t - 1)) * a.n_bkg + j];
+          cp_async_4(cnt_n + i, a.bkg_counts + ((int64_t)b * a.T + (t - 1)) * a.n_bkg + j);
         }
       }
     }
@@ -256,14 +257,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
         if (z) spk_list[atomicAdd(nspk_p, 1)] = ((uint32_t)b << 24) | (uint32_t)tid;
       }
     }
-    {
-      int* cnt_n = s_cnt + ((t + 1) & 1) * nb;
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const int ii = tid + q * NT;
-        if (ii < nb) cnt_n[ii] = cnt_next[q];
-      }
-    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
     const unsigned long long ph2 = prof ? gtime() : 0;
     // ---------------- scatter phase ----------------
@@ -401,7 +395,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
   c_rec_ev = v1g_warp_sum(c_rec_ev);
   c_lgn_rows = v1g_warp_sum(c_lgn_rows);
   c_lgn_ev = v1g_warp_sum(c_lgn_ev);
-  c_bkg_ev = v1g_warp_sum(c_bkg_ev);
+  c_bkg_ev = v1g_warp_sum(c_bkg_ev + (unsigned long long)c_bkg32);
   c_bkg_rows = v1g_warp_sum(c_bkg_rows);
   if (lane == 0) {
     V1GCounters* c = (V1GCounters*)a.counters;
