@@ -1053,7 +1053,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
                 al(sizeof(int) * (plan.chunkP + 1));
   const size_t state_bytes = al(sizeof(float) * plane * (3 + 2 * R));
   int state_in_smem = 0;
-  if (!h->opt_force_global && smem + state_bytes <= (size_t)h->smem_optin) {
+  if (!h->opt_force_global && smem + state_bytes <= std::min<size_t>((size_t)h->smem_optin, 195 * 1024)) {
     state_in_smem = 1;
     smem += state_bytes;
   }
@@ -1066,8 +1066,11 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
     }
   }
   const size_t bkg_bytes = al(sizeof(int) * bkg_cap) + al(sizeof(float) * bkg_cap) + al(bkg_cap);
+  // The L1 cache is what is left of the SM's 256 KB after the shared-memory carve-out, and it holds
+  // the sectors of the gather's loads in flight: with less than ~60 KB of it the gather runs at half
+  // speed.  The background tables therefore go on chip only while the block stays below 195 KB.
   int bkg_in_smem = 0;
-  if (smem + bkg_bytes <= (size_t)h->smem_optin) {
+  if (smem + bkg_bytes <= std::min<size_t>((size_t)h->smem_optin, 195 * 1024)) {
     bkg_in_smem = 1;
     smem += bkg_bytes;
   }
