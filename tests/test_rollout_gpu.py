@@ -51,6 +51,7 @@ def _compare_rollout(cfg, orc, cell, x, c):
     ("small", (("rollout_chunk", 32),), {}),
     ("small", (("rollout_chunk", 64), ("force_smem_kernel", 1)), {}),
     ("small", (("rollout_chunk", 96), ("state_in_global", 1)), {}),
+    ("small", (("no_meta", 1),), {}),                      # plain post / sid / w arrays instead of packed records
     ("small", (), dict(hard_reset=True)),
     ("small", (), dict(dense_basis=True)),
     ("small", (("force_smem_kernel", 1),), dict(dense_basis=True, n_receptors=4)),
@@ -144,6 +145,7 @@ def _oracle_grads(orc, cfg, x, c, vscale, dtype, g_z=None, g_v=None, loss=LOSS):
     ("small", (), {}),
     ("small", (("rollout_chunk", 32),), {}),
     ("small", (("rollout_chunk", 64), ("state_in_global", 1)), {}),
+    ("small", (("no_meta", 1),), {}),                      # gather over plain arrays instead of packed records
     ("small", (), dict(dense_basis=True)),
     ("small", (), dict(n_receptors=4)),
     ("small", (), dict(pseudo_gauss=True, gauss_std=0.3)),
@@ -165,7 +167,7 @@ def test_bptt_gradients_match_oracle_autograd(name, options, kw):
         assert rel_err(got, want) <= TOL_GRAD
 
 
-@pytest.mark.parametrize("options", [(), (("no_q_pack", 1),), (("rollout_chunk", 64),)])
+@pytest.mark.parametrize("options", [(), (("no_q_pack", 1),), (("rollout_chunk", 64),), (("no_meta", 1),)])
 def test_bptt_batch_of_five(options):
     """Batch 5 stores the backward Q rows as five 24-bit floats per 16-byte row (7.6e-6 relative
     rounding); the gradients must stay inside the 1e-4 bar, as they do with fp32 rows."""
