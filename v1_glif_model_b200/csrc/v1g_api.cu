@@ -133,6 +133,7 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   if (h->h_count) cudaFreeHost(h->h_count);
   cudaFree(h->lgn_entries);
   cudaFree(h->lgn_ent4);
+  cudaFree(h->tape_stats);
   cudaFree(h->lgn_offsets);
   cudaFree(h->ring);
   cudaFree(h->state_ws);

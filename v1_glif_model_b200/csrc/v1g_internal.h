@@ -100,6 +100,10 @@ struct V1GHandle {
   bool tape_has_hist0 = false;
   int tape_B = 0, tape_T = 0;
   bool tape_valid = false;
+  // spike statistics of the saved rollout, counted by the forward kernel: [N] spikes per neuron
+  // (all batch rows and steps) followed by [T*B] population spikes per (step, batch row)
+  int32_t* tape_stats = nullptr;
+  int64_t tape_stats_cap = 0;
   const int32_t* tape_counts = nullptr;  // caller's bkg counts of the saved rollout
   // backward scratch
   float* dy_ring = nullptr;

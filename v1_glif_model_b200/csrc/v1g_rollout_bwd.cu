@@ -861,29 +861,6 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
 
 // ---- loss preparation over the saved spikes ------------------------------------------------
 
-// spike_count[n] += spikes of neuron n (all b, t); popcount[t*B + b] = population spikes
-__global__ void __launch_bounds__(256) spike_stats_kernel(const uint8_t* __restrict__ zr, int T,
-                                                          int B, int N, int* __restrict__ spike_count,
-                                                          int* __restrict__ popcount) {
-  const int64_t row = blockIdx.x;  // t*B + b
-  const uint8_t* p = zr + row * N;
-  int cnt = 0;
-  for (int n = threadIdx.x; n < N; n += blockDim.x)
-    if (p[n] & 1) {
-      ++cnt;
-      atomicAdd(spike_count + n, 1);
-    }
-  __shared__ int ws[8];
-  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_down_sync(0xffffffffu, cnt, o);
-  if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = cnt;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int s = 0;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += ws[w];
-    popcount[row] = s;
-  }
-}
-
 // rate_coef[n] = rate_cost*ls*2*(m_n - target_n)/(N*B*T); loss[1] = rate loss
 __global__ void __launch_bounds__(256) rate_loss_kernel(const int* __restrict__ spike_count,
                                                         const float* __restrict__ target, int N,
@@ -1106,8 +1083,10 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
 
   const bool want_rate = ls.rate_cost != 0.f, want_sync = nbins >= 1;
   if (want_rate || want_sync) {
-    spike_stats_kernel<<<(unsigned)(T * B), 256, 0, st>>>(h->tape_zr, T, B, N, spike_count, popcount);
-    v1g_count_launches(1 + (want_rate ? 1 : 0) + (want_sync ? 1 : 0));
+    // spike counts per neuron and per (step, batch row) come from the forward kernel
+    spike_count = h->tape_stats;
+    popcount = h->tape_stats + N;
+    v1g_count_launches((want_rate ? 1 : 0) + (want_sync ? 1 : 0));
     if (want_rate)
       rate_loss_kernel<<<(N + 255) / 256, 256, 0, st>>>(spike_count, ls.rate_target, N,
                                                        1.f / ((float)B * (float)T),

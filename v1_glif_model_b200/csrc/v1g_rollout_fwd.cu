@@ -350,6 +350,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
     const int nspk = *nspk_p;
     for (int e = warp; e < nspk; e += NW) {
       const uint32_t ent = spk_list[e];
+      if (a.stat_neuron && lane == 0) {
+        atomicAdd(a.stat_neuron + n0 + (int)(ent & 0xffffff), 1);
+        atomicAdd(a.stat_pop + t * B + (int)(ent >> 24), 1);
+      }
       walk_rec((int)(ent >> 24), n0 + (int)(ent & 0xffffff), t);
     }
     if (tid == 0) c_spikes += (unsigned long long)nspk;
@@ -593,6 +597,11 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
       h->tape_cap = need;
     }
   }
+  if (save_for_bwd) {
+    const int64_t ns = (int64_t)N + (int64_t)T * B;
+    if ((rc = v1g_reserve(h, &h->tape_stats, &h->tape_stats_cap, ns))) return rc;
+    V1G_CUDA(h, cudaMemsetAsync(h->tape_stats, 0, (size_t)ns * sizeof(int32_t), st));
+  }
   h->tape_has_hist0 = false;
   if (save_for_bwd && state) {
     if ((rc = v1g_reserve(h, &h->tape_hist0, &h->tape_hist0_cap, (int64_t)B * N))) return rc;
@@ -626,6 +635,8 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
   a.rec_syn8 = h->opt_no_meta ? nullptr : h->src[V1G_SRC_REC].syn8;
   a.lgn_syn8 = h->opt_no_meta ? nullptr : h->src[V1G_SRC_LGN].syn8;
   a.bkg_counts = bkg_counts;
+  a.stat_neuron = save_for_bwd ? h->tape_stats : nullptr;
+  a.stat_pop = save_for_bwd ? h->tape_stats + N : nullptr;
   if (state) a.st = *state; else a.st = V1GState{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   a.state_ws = h->state_ws;
   a.z_out = z_out; a.v_out = v_out;

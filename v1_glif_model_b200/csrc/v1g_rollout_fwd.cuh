@@ -30,6 +30,9 @@ struct FwdArgs {
   const uint2 *rec_syn8, *lgn_syn8;
   int lgn_nseg;
   const int32_t* bkg_counts;  // [B][T][n_bkg]
+  // spike statistics for the loss terms (with the tape, else NULL): spikes per neuron, population
+  // spikes per (step, batch row)
+  int32_t *stat_neuron, *stat_pop;
   // state (reference layouts, all NULL = zero state / no write-back)
   V1GState st;
   float* state_ws;

@@ -268,6 +268,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
     const int nspk = *nspk_p;
     for (int e = warp; e < nspk; e += NW) {
       const uint32_t ent = spk_list[e];
+      if (a.stat_neuron && lane == 0) {
+        atomicAdd(a.stat_neuron + n0 + (int)(ent & 0xffffffu), 1);
+        atomicAdd(a.stat_pop + t * B_ + (int)(ent >> 24), 1);
+      }
       if (a.rec_syn8) {
         const int2 rb = rowb_s[ent & 0xffffffu];
         v1g_scatter_row8<R_>(a, a.rec_syn8, basis_s, lane, (int)(ent >> 24), rb.x, rb.y, t % K, true);
