@@ -177,7 +177,6 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   float* gz_s = (float*)take(sizeof(float) * 2 * plane);   // gathered spike gradient
   float* tv_s = (float*)take(sizeof(float) * 2 * plane);   // v(t)
   uint8_t* tz_s = (uint8_t*)take(2 * plane);               // spike / refractory bits
-  uint8_t* need_s = (uint8_t*)take(chunkP);            // row must be walked
   uint8_t* zmask_s = (uint8_t*)take(chunkP);           // batch rows that spiked at this step
   float* s_cnt = (float*)take(sizeof(float) * nb);  // background counts of step t-2, as floats
   int* s_misc = (int*)take(sizeof(int) * 8);  // [1] abort flag, [2+p] rows queued, [4+p] next queue slot (p = parity of the iteration)
@@ -335,7 +334,6 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       const bool walk = act && (need | zm);
       if (act) {
         zmask_s[k] = (uint8_t)zm;
-        need_s[k] = (uint8_t)(walk ? 1u : 0u);
         if (!walk)
           for (int b = 0; b < B; ++b) gzp[b * chunkP + k] = 0.f;  // row is not walked
       }
@@ -1024,7 +1022,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   const size_t plane = (size_t)B * plan.chunkP;
   const bool fast = proj && !h->opt_no_meta && h->src[V1G_SRC_REC].syn8 != nullptr;  // packed-record gather
   size_t smem = al(sizeof(float) * S * R) + 2 * al(sizeof(float) * 2 * plane) + al(2 * plane) +
-                2 * al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 8) + al(sizeof(int) * 8) +
+                al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 8) + al(sizeof(int) * 8) +
                 al(sizeof(uint16_t) * plan.chunkP) + al(sizeof(int4) * plan.chunkP) +
                 (fast ? 0 : al(sizeof(int32_t) * ((size_t)plan.chunkP * D + 1))) +
                 al(sizeof(int) * (plan.chunkP + 1));

@@ -20,35 +20,6 @@ __device__ __forceinline__ unsigned long long v1g_ld_acquire(const unsigned long
   return v;
 }
 
-// Grid-wide barrier on a monotonically increasing counter.  Every block adds 1 and waits until
-// the counter reaches `target` (= number of barriers passed so far x grid size).  The wait is
-// bounded: after `spin_limit` polls the block records V1G_DEV_BARRIER_TIMEOUT in the device
-// status word and every block that sees a non-zero status leaves its time loop, so a lost block
-// can never hang the GPU.  Requires a cooperative launch (all blocks co-resident).
-__device__ __forceinline__ bool v1g_grid_barrier(unsigned long long* bar, unsigned long long target,
-                                                 long long spin_limit, int32_t* status,
-                                                 int* s_abort) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(bar, 1ULL);
-    long long spins = 0;
-    bool ok = true;
-    while (v1g_ld_acquire(bar) < target) {
-      if (++spins > spin_limit) {
-        ok = false;
-        break;
-      }
-    }
-    if (!ok) atomicExch(status, V1G_DEV_BARRIER_TIMEOUT);
-    if (*((volatile int32_t*)status) != V1G_DEV_OK) ok = false;
-    *s_abort = ok ? 0 : 1;
-    __threadfence();
-  }
-  __syncthreads();
-  return *s_abort == 0;
-}
-
 // Lagged synchronisation uses one counter per phase, rotating over V1G_PHASES cache lines.  A
 // single running sum would not do: with blocks allowed to run ahead, fast blocks could push the
 // sum past a target while a slow block has not arrived yet.  Counter p % V1G_PHASES receives one
