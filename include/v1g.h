@@ -278,8 +278,13 @@ int v1g_selftest_bounded_wait(V1GHandle* h, long long polls, void* stream);
 
 /* Tuning knobs, mainly for tests: "rollout_chunk" (neurons per thread block in the rollout
  * kernels, multiple of 32, 0 = automatic), "state_in_global" (1 = keep the rollout state in
- * global memory even when it fits in shared memory), "spin_limit" (iterations a grid-barrier wait
- * may spin before giving up).  No counterpart in the reference. */
+ * global memory even when it fits in shared memory), "force_smem_kernel" (1 = the general forward
+ * kernel even where the register-resident one applies), "spin_limit" (iterations a grid-barrier
+ * wait may spin before giving up), "no_meta" (1 = the rollout kernels read the plain post / sid /
+ * weight arrays instead of the packed 8-byte synapse records), "no_q_pack" (1 = fp32 rows in the
+ * backward ring for a batch of 5 instead of 24-bit floats), "phase_timers" (1 = per-block phase
+ * times, read with v1g_get_phase_times), "l2_window", "csr_evict_first" (cache-policy
+ * experiments).  No counterpart in the reference. */
 int v1g_set_option(V1GHandle* h, const char* name, long long value);
 
 /* Device time in ms of the last forward (which = 0) or backward (which = 1) rollout kernel,
