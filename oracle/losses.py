@@ -5,7 +5,9 @@ These are the simplified losses of the benchmark configurations, modelled on the
 factor of ``SynchronizationLoss.pop_fano_tf`` (``loss_functions.py:964-981``) and a per-neuron
 mean-rate regulariser (``loss_functions.py:873-889``), written with differentiable torch ops so
 that autograd supplies the reference gradients.  All are multiplied by ``loss_scale``
-(1/replicas, ``multi_training.py:427-429``).
+(1/replicas, ``multi_training.py:427-429``).  ``rate_distribution_loss`` is the reference's own
+firing-rate target in full; it is pinned against the reference's code by
+``tests/golden/reference_rate_loss.npz``.
 """
 import torch
 
@@ -37,3 +39,45 @@ def sync_loss(z, bin_steps, cost, fano_target=1.0, loss_scale=1.0):
     var = ((pop - mean[:, None]) ** 2).mean(dim=1)
     fano = var / torch.clamp(mean, min=1e-7)
     return cost * loss_scale * (fano.mean() - fano_target) ** 2
+
+
+def huber_quantile(u, tau, kappa):
+    """Quantile-Huber penalty (``loss_functions.py:626-633``): ``|tau - [u <= 0]|`` times
+    ``u^2 / (2 kappa)`` inside ``|u| <= kappa`` and ``|u| - kappa/2`` outside."""
+    abs_u = u.abs()
+    num = (tau - (u <= 0).to(u.dtype)).abs()
+    return torch.where(abs_u <= kappa, num / (2 * kappa) * u ** 2, num * (abs_u - 0.5 * kappa))
+
+
+def rate_distribution_loss(z, groups, cost, kappa=0.002, pre_delay=0, post_delay=0, loss_scale=1.0):
+    """The reference's firing-rate target (``SpikeRateDistributionTarget.__call__``,
+    ``loss_functions.py:873-889``, with ``compute_spike_rate_target_loss`` /
+    ``compute_spike_rate_distribution_loss``, ``:635-681``).
+
+    ``rates`` = mean of the spikes over batch and the steps ``[pre_delay, T - post_delay)``
+    (``spike_trimming``, ``:604-611``).  For every population ``(neuron_ids, sorted_targets)`` the
+    rates of its neurons are sorted and compared, rank by rank, with the sorted target sample:
+    ``u_i = sorted_rate_i - target_i``, ``tau_i = (i + 1) / n``, penalty ``huber_quantile``; the
+    penalties of all populations are summed and divided by the number of neurons covered.
+
+    The reference shuffles a population's rates before sorting, so which of several neurons with
+    EQUAL rates gets which rank is random there; here the sort is stable, i.e. equal rates keep
+    the order of ``neuron_ids``.  The loss value does not depend on that choice, the gradient of
+    tied neurons does.
+    """
+    t = z.shape[1]
+    zt = z[:, pre_delay:t - post_delay if post_delay else t, :]
+    rates = zt.mean(dim=(0, 1))
+    total = z.sum() * 0.0
+    count = 0
+    for neuron_ids, targets in groups:
+        if len(neuron_ids) == 0:
+            continue
+        ids = torch.as_tensor(neuron_ids, dtype=torch.long)
+        tg = torch.as_tensor(targets, dtype=rates.dtype)
+        srt = torch.sort(rates[ids], stable=True).values
+        n = ids.numel()
+        tau = (torch.arange(n, dtype=rates.dtype) + 1) / n
+        total = total + huber_quantile(srt - tg, tau, kappa).sum()
+        count += n
+    return cost * loss_scale * total / max(count, 1)

@@ -1,0 +1,81 @@
+"""Golden vectors for the firing-rate target from the reference's OWN loss code (run from the repo
+root, in a container that has the reference tree):
+
+    python tests/golden/run_reference_losses.py /path/to/V1_GLIF_model
+
+Imports ``v1_model_utils/loss_functions.py`` unmodified over ``tf_standin`` (its ``other_v1_utils``
+import, which needs h5py, is satisfied by an empty module: none of the functions used here touch
+it), and evaluates ``spike_trimming`` -> mean over batch and time ->
+``compute_spike_rate_target_loss`` x ``rate_cost`` - the body of
+``SpikeRateDistributionTarget.__call__`` - on seeded spikes of the 600-neuron synthetic net, with
+one population per node type.  Writes ``tests/golden/reference_rate_loss.npz`` (spikes, populations,
+loss, gradient with respect to the spikes' per-neuron rates).  ``tests/test_oracle_pinning.py``
+checks ``oracle/losses.py::rate_distribution_loss`` against it.
+
+The stand-in's ``tf.random.shuffle`` is the identity and its ``tf.sort`` is stable, so neurons with
+equal rates keep the order of ``neuron_ids`` (the reference orders them at random).
+"""
+import importlib.util
+import os
+import sys
+import tempfile
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, HERE)
+
+import tf_standin  # noqa: E402
+from v1_glif_model_b200 import synth  # noqa: E402
+
+RATE_COST, PRE_DELAY, POST_DELAY = 100.0, 5, 3
+
+
+def load_reference_losses(ref_root):
+    os.environ.setdefault("NUMBA_CACHE_DIR", tempfile.mkdtemp(prefix="numba_cache_"))
+    tf_standin.install()
+    sys.modules.setdefault("other_v1_utils", types.ModuleType("other_v1_utils"))
+    spec = importlib.util.spec_from_file_location(
+        "reference_losses", os.path.join(ref_root, "v1_model_utils", "loss_functions.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    lf = load_reference_losses(ref_root)
+    cfg = synth.CONFIGS["small"]
+    net, _, _ = synth.make_network(cfg, 3)
+    groups = synth.make_rate_groups(cfg, net, 3)
+    rng = np.random.Generator(np.random.PCG64(99))
+    b, t, n = 2, 40, cfg.n_neurons
+    p = rng.lognormal(np.log(0.02), 1.0, n).clip(0.0, 0.5)           # per-neuron spike probability
+    z = (rng.random((b, t, n)) < p[None, None, :]).astype(np.float64)
+    zt = torch.from_numpy(z).requires_grad_(True)
+    target_rates = {
+        f"type{i}": dict(neuron_ids=torch.from_numpy(ids.astype(np.int64)),
+                         sorted_target_rates=torch.from_numpy(tg.astype(np.float64)))
+        for i, (ids, tg) in enumerate(groups)}
+    trimmed = lf.spike_trimming(zt, pre_delay=PRE_DELAY, post_delay=POST_DELAY, trim=True)
+    rates = trimmed.mean(dim=(0, 1))
+    loss = lf.compute_spike_rate_target_loss(rates, target_rates, dtype=torch.float64) * RATE_COST
+    loss.backward()
+    out = os.path.join(HERE, "reference_rate_loss.npz")
+    np.savez_compressed(
+        out, z=z.astype(np.uint8), loss=loss.item(), grad_z=zt.grad.numpy(),
+        rate_cost=RATE_COST, pre_delay=PRE_DELAY, post_delay=POST_DELAY, kappa=0.002,
+        group_sizes=np.array([len(g[0]) for g in groups], dtype=np.int64),
+        group_neurons=np.concatenate([g[0] for g in groups]).astype(np.int32),
+        group_targets=np.concatenate([g[1] for g in groups]).astype(np.float32))
+    ties = sum(int(len(np.unique(z[:, PRE_DELAY:t - POST_DELAY, g[0]].sum((0, 1)))) < len(g[0])) for g in groups)
+    print(f"wrote {out}: loss {loss.item():.6e}, populations {len(groups)}, with ties {ties}")
+
+
+if __name__ == "__main__":
+    main()

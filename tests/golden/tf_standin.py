@@ -243,11 +243,24 @@ def install():
                                   softmax=lambda x, axis=-1: torch.softmax(x, dim=axis))
     tf.sparse = types.SimpleNamespace(SparseTensor=SparseTensor,
                                       sparse_dense_matmul=_sparse_dense_matmul)
+    # tf.random.shuffle is the identity here and tf.sort is stable: where the reference shuffles before
+    # a sort (rate-distribution loss), entries with equal keys keep their listed order
     tf.random = types.SimpleNamespace(
-        stateless_poisson=lambda shape, seed, lam, dtype=torch.int32: _POISSON[0].to(dtype))
+        stateless_poisson=lambda shape, seed, lam, dtype=torch.int32: _POISSON[0].to(dtype),
+        shuffle=lambda x, seed=None: x)
+    tf.sort = lambda x, axis=-1, direction="ASCENDING": torch.sort(
+        x, dim=axis, descending=(direction == "DESCENDING"), stable=True).values
+    tf.range = lambda *a, **kw: torch.arange(*[_i(v) for v in a], dtype=kw.get("dtype", torch.int64))
+    tf.size = lambda x: torch.tensor(x.numel(), dtype=torch.int32)
     tf.distribute = types.SimpleNamespace(get_replica_context=lambda: None)
-    keras = types.SimpleNamespace(
-        layers=types.SimpleNamespace(Layer=_Layer), constraints=types.SimpleNamespace(Constraint=_Constraint))
+    layers = types.ModuleType("tensorflow.keras.layers")
+    layers.Layer = _Layer
+    keras = types.ModuleType("tensorflow.keras")
+    keras.layers = layers
+    keras.constraints = types.SimpleNamespace(Constraint=_Constraint)
+    keras.regularizers = types.SimpleNamespace(Regularizer=object)
     tf.keras = keras
     sys.modules["tensorflow"] = tf
+    sys.modules["tensorflow.keras"] = keras
+    sys.modules["tensorflow.keras.layers"] = layers
     return tf

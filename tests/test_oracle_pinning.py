@@ -83,3 +83,25 @@ def test_cuda_path_equals_reference_cell(name):
     cell.synchronize()
     for got, key in zip(grads[:3], ("dw_rec", "dw_lgn", "dw_bkg")):
         assert rel_err(got, g[key]) <= TOL_GRAD
+
+
+def _rate_fixture():
+    f = np.load(os.path.join(ROOT, "tests", "golden", "reference_rate_loss.npz"))
+    sizes = f["group_sizes"]
+    offs = np.concatenate([[0], np.cumsum(sizes)])
+    groups = [(f["group_neurons"][offs[i]:offs[i + 1]], f["group_targets"][offs[i]:offs[i + 1]])
+              for i in range(len(sizes))]
+    return f, groups
+
+
+def test_oracle_rate_distribution_loss_equals_reference_loss_code():
+    """``oracle/losses.py::rate_distribution_loss`` against the value and gradient the reference's
+    ``compute_spike_rate_target_loss`` produced for the same spikes (fp64)."""
+    from oracle import losses
+    f, groups = _rate_fixture()
+    z = torch.from_numpy(f["z"].astype(np.float64)).requires_grad_(True)
+    loss = losses.rate_distribution_loss(z, groups, float(f["rate_cost"]), kappa=float(f["kappa"]),
+                                         pre_delay=int(f["pre_delay"]), post_delay=int(f["post_delay"]))
+    loss.backward()
+    assert abs(loss.item() - float(f["loss"])) <= 1e-12 * abs(float(f["loss"]))
+    assert rel_err(z.grad, torch.from_numpy(f["grad_z"])) <= 1e-12

@@ -205,3 +205,28 @@ def make_rate_targets(cfg: SynthConfig | str, seed: int = 0) -> np.ndarray:
         cfg = CONFIGS[cfg]
     rng = np.random.Generator(np.random.PCG64(seed + 15485863))
     return rng.lognormal(np.log(3.0), 0.8, cfg.n_neurons).astype(np.float32)
+
+
+def make_rate_groups(cfg: SynthConfig | str, network, seed: int = 0):
+    """Populations and sorted target-rate samples for the rate-distribution loss, in the form of the
+    reference's ``target_rates`` dictionary (``loss_functions.py:819-871``): one population per node
+    type, ``(neuron_ids int32[n], sorted_targets float32[n])`` with targets in spikes per ms.
+
+    Each population's sample is drawn by inverse-transform sampling from a lognormal "recorded"
+    distribution (median 2-6 Hz by type, sigma 0.9, 200 recorded units plus one silent unit) and
+    sorted, which is what the reference does with the Neuropixels rates (``:613-624``); none of
+    those recordings is used here.
+    """
+    if isinstance(cfg, str):
+        cfg = CONFIGS[cfg]
+    rng = np.random.Generator(np.random.PCG64(seed + 32452843))
+    type_ids = np.asarray(network["node_type_ids"])
+    groups = []
+    for ty in np.unique(type_ids):
+        ids = np.nonzero(type_ids == ty)[0].astype(np.int32)
+        recorded = np.append(rng.lognormal(np.log(rng.uniform(2.0, 6.0)), 0.9, 200) / 1000.0, 0.0)
+        recorded.sort()
+        pct = np.linspace(0.0, 1.0, recorded.size)
+        sample = np.sort(np.interp(rng.uniform(0.0, 1.0, ids.size), pct, recorded))
+        groups.append((ids, sample.astype(np.float32)))
+    return groups
