@@ -77,14 +77,23 @@ typedef struct V1GState {
   float* psc;      /* [B, N*R] */
 } V1GState;
 
-/* In-kernel loss specification of the training rollout (BASELINE configurations 2 and 4).
- *   rate     : rate_cost * mean_n (mean_{b,t} z[b,t,n] - target[n])^2, target in spikes/step
+/* In-kernel loss specification of the training rollout.
+ *   rate     : with n_rate_groups == 0 the form of BASELINE configurations 2 and 4,
+ *                rate_cost * mean_n (mean_{b,t} z[b,t,n] - target[n])^2, target in spikes/step;
+ *              with n_rate_groups > 0 the reference's own firing-rate target
+ *              (SpikeRateDistributionTarget.__call__, loss_functions.py:873-889, with
+ *              compute_spike_rate_target_loss and huber_quantile_loss, :626-681): rates are the mean
+ *              over the batch and the steps [rate_pre_delay, T - rate_post_delay); per population the
+ *              sorted rates are compared rank by rank with the sorted target sample through the
+ *              quantile-Huber penalty (kappa = rate_kappa, 0 -> 0.002), summed over populations,
+ *              divided by the neurons covered and multiplied by rate_cost.  Neurons with equal
+ *              rates keep their listed order (the reference orders them at random).
  *   voltage  : voltage_cost * mean_{b,t,n} (relu(v-1)^2 + relu(v_lo[n]-v)^2)
  *   synchrony: sync_cost * (mean_b Fano_b - fano_target)^2, Fano_b = var/mean over bins of the
  *              population spike count in bins of sync_bin steps (loss_functions.py:964-981)
  * All costs are multiplied by loss_scale (1/replicas, multi_training.py:427-429). */
 typedef struct V1GLossSpec {
-  const float* rate_target; /* [N] device, may be NULL when rate_cost == 0 */
+  const float* rate_target; /* [N] device, may be NULL when rate_cost == 0 or populations are given */
   const float* v_lo;        /* [N] device, lower voltage bound in scaled units */
   float rate_cost;
   float voltage_cost;
@@ -92,6 +101,15 @@ typedef struct V1GLossSpec {
   float fano_target;
   int32_t sync_bin;
   float loss_scale;
+  /* populations of the rate-distribution target (all device pointers); the reference's
+   * target_rates dictionary flattened: population g owns positions [offsets[g], offsets[g+1]) */
+  int32_t n_rate_groups;
+  int32_t n_rate_neurons;            /* = offsets[n_rate_groups] */
+  const int32_t* rate_group_offsets; /* [n_rate_groups + 1] */
+  const int32_t* rate_group_neurons; /* [n_rate_neurons] neuron ids ("neuron_ids") */
+  const float* rate_group_targets;   /* [n_rate_neurons] "sorted_target_rates", ascending per population, spikes/step */
+  float rate_kappa;
+  int32_t rate_pre_delay, rate_post_delay;
 } V1GLossSpec;
 
 /* Event counters of the last rollout (for the roofline's algorithmic bytes). */

@@ -167,6 +167,33 @@ def test_bptt_gradients_match_oracle_autograd(name, options, kw):
         assert rel_err(got, want) <= TOL_GRAD
 
 
+@pytest.mark.parametrize("pre,post", [(0, 0), (5, 3)])
+def test_bptt_with_rate_distribution_target(pre, post):
+    """The reference's firing-rate target (sorted rates per population against sorted target samples,
+    quantile-Huber penalty, ``loss_functions.py:626-681, 873-889``) evaluated on the device from the
+    saved spikes: loss value and weight gradients against autograd through the oracle's form of it,
+    which is pinned to the reference's code by tests/golden/reference_rate_loss.npz."""
+    from oracle import losses as OL
+    cfg, dicts, orc, cell = _cells("small", **KW)
+    x, c = make_inputs(cfg)
+    groups = synth.make_rate_groups(cfg, dicts[0], 0)
+    cost = 50.0
+    z, v, _ = orc.rollout(torch.from_numpy(x), torch.from_numpy(c).long())
+    vlo = torch.from_numpy(-20.0 / cell.voltage_scale).float()
+    total = OL.rate_distribution_loss(z, groups, cost, kappa=0.002, pre_delay=pre, post_delay=post) + \
+        OL.voltage_loss(v, vlo, LOSS["voltage_cost"])
+    total.backward()
+    want = [orc.recurrent_weight_values.grad, orc.input_weight_values.grad, orc.bkg_input_weights.grad]
+    zc, _ = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), save_for_bwd=True)
+    assert torch.equal(zc.cpu().float(), z.detach())
+    grads = cell.backward(dict(rate_cost=cost, rate_groups=groups, rate_kappa=0.002, rate_pre_delay=pre,
+                               rate_post_delay=post, voltage_cost=LOSS["voltage_cost"], v_lo=vlo.cuda()))
+    cell.synchronize()
+    assert abs(float(grads[3][0]) - total.item()) <= 1e-4 * abs(total.item())
+    for got, w in zip(grads[:3], want):
+        assert rel_err(got, w) <= TOL_GRAD
+
+
 @pytest.mark.parametrize("options", [(), (("no_q_pack", 1),), (("rollout_chunk", 64),), (("no_meta", 1),)])
 def test_bptt_batch_of_five(options):
     """Batch 5 stores the backward Q rows as five 24-bit floats per 16-byte row (7.6e-6 relative

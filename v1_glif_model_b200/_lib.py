@@ -32,7 +32,11 @@ class V1GState(C.Structure):
 class V1GLossSpec(C.Structure):
     _fields_ = [("rate_target", C.c_void_p), ("v_lo", C.c_void_p), ("rate_cost", C.c_float),
                 ("voltage_cost", C.c_float), ("sync_cost", C.c_float), ("fano_target", C.c_float),
-                ("sync_bin", C.c_int32), ("loss_scale", C.c_float)]
+                ("sync_bin", C.c_int32), ("loss_scale", C.c_float),
+                ("n_rate_groups", C.c_int32), ("n_rate_neurons", C.c_int32),
+                ("rate_group_offsets", C.c_void_p), ("rate_group_neurons", C.c_void_p),
+                ("rate_group_targets", C.c_void_p), ("rate_kappa", C.c_float),
+                ("rate_pre_delay", C.c_int32), ("rate_post_delay", C.c_int32)]
 
 
 class V1GCounters(C.Structure):

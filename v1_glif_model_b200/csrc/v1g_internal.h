@@ -109,6 +109,8 @@ struct V1GHandle {
   float* dy_ring = nullptr;
   int64_t dy_ring_cap = 0;
   float* dw_csr[V1G_NSRC] = {nullptr, nullptr, nullptr};
+  int32_t* rate_scratch = nullptr;  // sort buffers of the rate-distribution target
+  int64_t rate_scratch_cap = 0;
   float* loss_scratch = nullptr;  // rate sums [N], pop counts [B][T], bin grads, partial losses
   int64_t loss_scratch_cap = 0;
   // staging for the host-buffer entry point
@@ -166,6 +168,10 @@ int v1g_reserve(V1GHandle* h, T** p, int64_t* cap, int64_t need) {
   *cap = need;
   return V1G_OK;
 }
+
+// ---- rate-distribution target (v1g_losses.cu) ----
+int v1g_rate_distribution_loss(V1GHandle* h, const V1GLossSpec* ls, const int32_t* count, int B, int T,
+                               float* rate_coef, float* loss_acc, cudaStream_t st);
 
 // ---- ordered compaction (v1g_compact.cu) ----
 // Input viewed as [n_rows][n_cols]; positives are listed in output order.  time_major_T > 0:

@@ -57,6 +57,7 @@ struct BwdArgs {
   const int32_t* bkg_counts;
   // loss
   const float* rate_coef;  // [N] dL/dz contribution of the rate term, or NULL
+  int rate_t0, rate_t1;    // steps whose spikes enter the rate term
   const float* sgrad;      // [B][nbins] dL/d(bin count), or NULL
   int sync_bin, nbins;
   float volt_coef;  // voltage_cost * loss_scale / (B*T*N); gradient is 2*volt_coef*(...)
@@ -421,7 +422,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     for (int k = tid; k < cn; k += NT) {
       const int n = n0 + k;
       const float k_decay = a.decay[n], k_cf = a.cf[n], k_ad0 = a.asc_decay[2 * n], k_ad1 = a.asc_decay[2 * n + 1];
-      const float rc = a.rate_coef ? a.rate_coef[n] : 0.f, vlo = a.v_lo ? a.v_lo[n] : 0.f;
+      const float rc = (a.rate_coef && t >= a.rate_t0 && t < a.rate_t1) ? a.rate_coef[n] : 0.f;
+      const float vlo = a.v_lo ? a.v_lo[n] : 0.f;
       float dyv[BP_][R_];  // dy(t-2) of every batch row of this neuron
 #pragma unroll
       for (int b = 0; b < BP_; ++b) {
@@ -1005,7 +1007,9 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
     return v1g_fail(h, V1G_ERANGE, "backward rollout is built for 4 or 5 receptor channels, got %d", R);
   V1GLossSpec ls;
   if (loss) ls = *loss; else ls = V1GLossSpec{nullptr, nullptr, 0.f, 0.f, 0.f, 1.f, 50, 1.f};
-  if (ls.rate_cost != 0.f && !ls.rate_target) return v1g_fail(h, V1G_EINVAL, "rate_cost without rate_target");
+  const bool rate_groups = ls.n_rate_groups > 0;
+  if (ls.rate_cost != 0.f && !ls.rate_target && !rate_groups)
+    return v1g_fail(h, V1G_EINVAL, "rate_cost without rate_target or rate populations");
   const bool proj = S <= 8;
   const int C = proj ? S : R;
   const int BP = B <= 4 ? 4 : 8;
@@ -1084,11 +1088,14 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
     // spike counts per neuron and per (step, batch row) come from the forward kernel
     spike_count = h->tape_stats;
     popcount = h->tape_stats + N;
-    v1g_count_launches((want_rate ? 1 : 0) + (want_sync ? 1 : 0));
-    if (want_rate)
+    v1g_count_launches(((want_rate && !rate_groups) ? 1 : 0) + (want_sync ? 1 : 0));
+    if (want_rate && rate_groups) {
+      if ((rc = v1g_rate_distribution_loss(h, &ls, spike_count, B, T, rate_coef, acc + 1, st))) return rc;
+    } else if (want_rate) {
       rate_loss_kernel<<<(N + 255) / 256, 256, 0, st>>>(spike_count, ls.rate_target, N,
                                                        1.f / ((float)B * (float)T),
                                                        ls.rate_cost * ls.loss_scale, rate_coef, acc);
+    }
     if (want_sync)
       sync_loss_kernel<<<1, 256, sizeof(float) * (B * nbins + 3 * B), st>>>(
           popcount, T, B, ls.sync_bin, nbins, ls.sync_cost * ls.loss_scale, ls.fano_target, sgrad, acc);
@@ -1125,6 +1132,8 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   a.lgn_off = h->lgn_offsets; a.lgn_ent4 = h->lgn_ent4; a.lgn_nseg = h->lgn_nseg;
   a.bkg_counts = h->tape_counts;
   a.rate_coef = want_rate ? rate_coef : nullptr;
+  a.rate_t0 = rate_groups ? std::max(ls.rate_pre_delay, 0) : 0;
+  a.rate_t1 = rate_groups ? T - std::max(ls.rate_post_delay, 0) : T;
   a.sgrad = want_sync ? sgrad : nullptr;
   a.sync_bin = ls.sync_bin; a.nbins = nbins;
   a.volt_coef = ls.voltage_cost * ls.loss_scale / ((float)B * (float)T * (float)N);

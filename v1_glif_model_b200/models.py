@@ -255,13 +255,38 @@ class V1Column:
         return [int(v) for v in sizes]
 
     def _loss_spec(self, loss):
+        """``V1GLossSpec`` from a dict with any of ``rate_target`` (tensor [N], spikes/step),
+        ``v_lo`` (tensor [N]), ``rate_cost``, ``voltage_cost``, ``sync_cost``, ``fano_target``,
+        ``sync_bin``, ``loss_scale`` and, for the reference's rate-distribution target
+        (``loss_functions.py:782-889``), ``rate_groups`` = list of ``(neuron_ids, sorted_targets)``
+        with ``rate_kappa``, ``rate_pre_delay``, ``rate_post_delay``."""
         loss = dict(loss or {})
-        return _lib.V1GLossSpec(
+        spec = _lib.V1GLossSpec(
             rate_target=loss["rate_target"].data_ptr() if loss.get("rate_target") is not None else None,
             v_lo=loss["v_lo"].data_ptr() if loss.get("v_lo") is not None else None,
             rate_cost=loss.get("rate_cost", 0.0), voltage_cost=loss.get("voltage_cost", 0.0),
             sync_cost=loss.get("sync_cost", 0.0), fano_target=loss.get("fano_target", 1.0),
             sync_bin=int(loss.get("sync_bin", 50)), loss_scale=loss.get("loss_scale", 1.0))
+        groups = loss.get("rate_groups")
+        if groups:
+            key = id(groups)
+            if getattr(self, "_rate_groups_key", None) != key:
+                sizes = [len(g[0]) for g in groups]
+                offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int32)
+                ids = np.concatenate([np.asarray(g[0], dtype=np.int32) for g in groups])
+                tgt = np.concatenate([np.asarray(g[1], dtype=np.float32) for g in groups])
+                dev = lambda a: torch.from_numpy(a).to(self.device)
+                self._rate_groups_dev = (dev(offs), dev(ids), dev(tgt), len(sizes), int(offs[-1]))
+                self._rate_groups_key = key
+            offs, ids, tgt, ng, nn = self._rate_groups_dev
+            spec.n_rate_groups, spec.n_rate_neurons = ng, nn
+            spec.rate_group_offsets = offs.data_ptr()
+            spec.rate_group_neurons = ids.data_ptr()
+            spec.rate_group_targets = tgt.data_ptr()
+            spec.rate_kappa = float(loss.get("rate_kappa", 0.002))
+            spec.rate_pre_delay = int(loss.get("rate_pre_delay", 0) or 0)
+            spec.rate_post_delay = int(loss.get("rate_post_delay", 0) or 0)
+        return spec
 
     def backward_internal(self, loss, grads_flat, losses=None):
         """BPTT with the gradients accumulated into ``grads_flat`` ([rec | lgn | bkg]) in the
@@ -429,18 +454,10 @@ class V1Column:
     def backward(self, loss=None, g_z=None, g_v=None, accumulate_into=None):
         """BPTT over the rollout saved by ``rollout(..., save_for_bwd=True)``.
 
-        ``loss``: dict with any of ``rate_target`` (tensor [N], spikes/step), ``v_lo`` (tensor
-        [N]), ``rate_cost``, ``voltage_cost``, ``sync_cost``, ``fano_target``, ``sync_bin``,
-        ``loss_scale``.  Returns ``(dW_rec, dW_lgn, dW_bkg, losses[4])`` in the synapse order of
-        the constructor's arrays.
+        ``loss``: see ``_loss_spec``.  Returns ``(dW_rec, dW_lgn, dW_bkg, losses[4])`` in the synapse
+        order of the constructor's arrays.
         """
-        loss = dict(loss or {})
-        spec = _lib.V1GLossSpec(
-            rate_target=loss["rate_target"].data_ptr() if loss.get("rate_target") is not None else None,
-            v_lo=loss["v_lo"].data_ptr() if loss.get("v_lo") is not None else None,
-            rate_cost=loss.get("rate_cost", 0.0), voltage_cost=loss.get("voltage_cost", 0.0),
-            sync_cost=loss.get("sync_cost", 0.0), fano_target=loss.get("fano_target", 1.0),
-            sync_bin=int(loss.get("sync_bin", 50)), loss_scale=loss.get("loss_scale", 1.0))
+        spec = self._loss_spec(loss)
         if accumulate_into is None:
             grads = [torch.zeros_like(w) for w in (self.recurrent_weight_values,
                                                    self.input_weight_values,
