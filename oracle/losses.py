@@ -81,3 +81,42 @@ def rate_distribution_loss(z, groups, cost, kappa=0.002, pre_delay=0, post_delay
         total = total + huber_quantile(srt - tg, tau, kappa).sum()
         count += n
     return cost * loss_scale * total / max(count, 1)
+
+
+def population_fano_loss(pop, bin_sizes, target_fanos, cost, eps=1e-7):
+    """``cost * mean_k (target_k - Fano_k)^2`` for population counts ``pop[sample, step]``
+    (``pop_fano_tf`` and the mean squared error of ``__call__``, ``loss_functions.py:964-981,
+    1031-1044``): for every bin size smaller than half the window the counts are summed in
+    non-overlapping bins (incomplete last bin dropped), Fano = biased variance / max(mean, eps)
+    per sample, averaged over the samples."""
+    w = pop.shape[1]
+    terms = []
+    for bs, tg in zip(bin_sizes, target_fanos):
+        bs = int(bs)
+        if not bs < w // 2:
+            continue
+        nb = w // bs
+        c = pop[:, :nb * bs].reshape(pop.shape[0], nb, bs).sum(dim=2)
+        mean = c.mean(dim=1)
+        var = ((c - mean[:, None]) ** 2).mean(dim=1)
+        fano = (var / torch.clamp(mean, min=eps)).mean()
+        terms.append((float(tg) - fano) ** 2)
+    if not terms:
+        return pop.sum() * 0.0
+    return cost * torch.stack(terms).mean()
+
+
+def synchronization_loss(z, samples, bin_sizes, target_fanos, cost, t_start=0, t_end=None,
+                         loss_scale=1.0, eps=1e-7):
+    """The reference's synchrony target in full (``SynchronizationLoss.__call__``,
+    ``loss_functions.py:983-1044``) for given samples.
+
+    ``samples`` = list of ``(trial, neuron_ids)``: the population spike count of the neurons in
+    trial (batch row) ``trial`` over the steps ``[t_start, t_end)`` enters ``population_fano_loss``.
+    The reference draws trial, sample size and members at random in every call; here they are an
+    input.
+    """
+    t_end = z.shape[1] if t_end is None else t_end
+    zt = z[:, t_start:t_end, :]
+    pop = torch.stack([zt[tr][:, torch.as_tensor(ids, dtype=torch.long)].sum(dim=1) for tr, ids in samples])
+    return loss_scale * population_fano_loss(pop, bin_sizes, target_fanos, cost, eps)

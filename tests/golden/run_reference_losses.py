@@ -10,7 +10,10 @@ it), and evaluates ``spike_trimming`` -> mean over batch and time ->
 ``SpikeRateDistributionTarget.__call__`` - on seeded spikes of the 600-neuron synthetic net, with
 one population per node type.  Writes ``tests/golden/reference_rate_loss.npz`` (spikes, populations,
 loss, gradient with respect to the spikes' per-neuron rates).  ``tests/test_oracle_pinning.py``
-checks ``oracle/losses.py::rate_distribution_loss`` against it.
+checks ``oracle/losses.py::rate_distribution_loss`` against it.  A second fixture,
+``reference_sync_loss.npz``, holds the population Fano factors of
+``SynchronizationLoss.pop_fano_tf`` for seeded population counts and the loss built from them, for
+``oracle/losses.py::synchronization_loss``.
 
 The stand-in's ``tf.random.shuffle`` is the identity and its ``tf.sort`` is stable, so neurons with
 equal rates keep the order of ``neuron_ids`` (the reference orders them at random).
@@ -77,5 +80,33 @@ def main():
     print(f"wrote {out}: loss {loss.item():.6e}, populations {len(groups)}, with ties {ties}")
 
 
+def sync_fixture(ref_root):
+    """Population Fano factors of the reference's ``SynchronizationLoss.pop_fano_tf`` and the mean
+    squared error of ``__call__`` (``loss_functions.py:964-981, 1031-1044``) for seeded population
+    counts; ``self`` is a stand-in object with the three attributes the method reads."""
+    lf = load_reference_losses(ref_root)
+    import tf_standin as _ts
+    tf = sys.modules["tensorflow"]
+    rng = np.random.Generator(np.random.PCG64(7))
+    n_samples, width = 6, 120
+    counts = rng.poisson(rng.uniform(0.2, 3.0, (n_samples, 1)), (n_samples, width)).astype(np.float64)
+    counts[0] = 0.0                                     # a silent sample: mean clamped at 1e-7
+    bin_sizes = (1, 2, 3, 5, 8, 13, 21, 34, 55, 89)     # the last two are not below half the window
+    targets = rng.uniform(0.8, 2.5, len(bin_sizes))
+    used = [b for b in bin_sizes if b < width // 2]
+    stub = types.SimpleNamespace(_bin_sizes_ms=tuple(used), _dtype=torch.float64,
+                                 _epsilon_tf=torch.tensor(1e-7, dtype=torch.float64))
+    x = torch.from_numpy(counts).requires_grad_(True)
+    fanos = lf.SynchronizationLoss.pop_fano_tf(stub, x)
+    mse = tf.reduce_mean(tf.square(torch.from_numpy(targets[:len(used)]) - fanos))
+    loss = 10.0 * mse
+    loss.backward()
+    out = os.path.join(HERE, "reference_sync_loss.npz")
+    np.savez_compressed(out, counts=counts, bin_sizes=np.array(bin_sizes), targets=targets, sync_cost=10.0,
+                        fanos=fanos.detach().numpy(), loss=loss.item(), grad_counts=x.grad.numpy())
+    print(f"wrote {out}: loss {loss.item():.6e}, fanos {fanos.detach().numpy().round(3)}")
+
+
 if __name__ == "__main__":
     main()
+    sync_fixture(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

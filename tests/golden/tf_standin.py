@@ -192,6 +192,25 @@ def _reduce(fn):
     return r
 
 
+class _TensorArray:
+    def __init__(self, dtype=None, size=0, **kw):
+        self.items = {}
+
+    def write(self, i, value):
+        self.items[_i(i)] = value
+        return self
+
+    def stack(self):
+        return torch.stack([self.items[k] for k in sorted(self.items)])
+
+
+def _conv1d(x, kernel, stride=1, padding="VALID"):
+    # x [batch, width, in_ch], kernel [k, in_ch, out_ch] -> [batch, new_width, out_ch]
+    assert padding == "VALID"
+    out = torch.nn.functional.conv1d(x.permute(0, 2, 1), kernel.permute(2, 1, 0), stride=_i(stride))
+    return out.permute(0, 2, 1)
+
+
 def install():
     """Register the stand-in as ``tensorflow`` in ``sys.modules`` and return it."""
     tf = types.ModuleType("tensorflow")
@@ -237,8 +256,11 @@ def install():
     tf.TensorShape = lambda dims: tuple(dims)
     tf.RaggedTensor = RaggedTensor
     tf.math = types.SimpleNamespace(unsorted_segment_sum=_unsorted_segment_sum, exp=torch.exp,
-                                    log=torch.log)
-    tf.nn = types.SimpleNamespace(relu=torch.relu, sigmoid=torch.sigmoid,
+                                    log=torch.log,
+                                    reduce_variance=lambda x, axis=None: torch.var(x, dim=axis, unbiased=False))
+    tf.TensorArray = _TensorArray
+    tf.squeeze = lambda x, axis=None: x.squeeze() if axis is None else x.squeeze(axis)
+    tf.nn = types.SimpleNamespace(relu=torch.relu, sigmoid=torch.sigmoid, conv1d=_conv1d,
                                   softplus=torch.nn.functional.softplus,
                                   softmax=lambda x, axis=-1: torch.softmax(x, dim=axis))
     tf.sparse = types.SimpleNamespace(SparseTensor=SparseTensor,

@@ -105,3 +105,15 @@ def test_oracle_rate_distribution_loss_equals_reference_loss_code():
     loss.backward()
     assert abs(loss.item() - float(f["loss"])) <= 1e-12 * abs(float(f["loss"]))
     assert rel_err(z.grad, torch.from_numpy(f["grad_z"])) <= 1e-12
+
+
+def test_oracle_population_fano_loss_equals_reference_loss_code():
+    """``oracle/losses.py::population_fano_loss`` against the Fano factors, loss and gradient that the
+    reference's ``SynchronizationLoss.pop_fano_tf`` produced for the same population counts (fp64)."""
+    from oracle import losses
+    f = np.load(os.path.join(ROOT, "tests", "golden", "reference_sync_loss.npz"))
+    pop = torch.from_numpy(f["counts"]).requires_grad_(True)
+    loss = losses.population_fano_loss(pop, f["bin_sizes"], f["targets"], float(f["sync_cost"]))
+    loss.backward()
+    assert abs(loss.item() - float(f["loss"])) <= 1e-12 * abs(float(f["loss"]))
+    assert rel_err(pop.grad, torch.from_numpy(f["grad_counts"])) <= 1e-12
