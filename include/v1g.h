@@ -89,8 +89,15 @@ typedef struct V1GState {
  *              divided by the neurons covered and multiplied by rate_cost.  Neurons with equal
  *              rates keep their listed order (the reference orders them at random).
  *   voltage  : voltage_cost * mean_{b,t,n} (relu(v-1)^2 + relu(v_lo[n]-v)^2)
- *   synchrony: sync_cost * (mean_b Fano_b - fano_target)^2, Fano_b = var/mean over bins of the
- *              population spike count in bins of sync_bin steps (loss_functions.py:964-981)
+ *   synchrony: with n_sync_samples == 0 the form of BASELINE configuration 4,
+ *                sync_cost * (mean_b Fano_b - fano_target)^2, Fano_b = var/mean over bins of the
+ *                population spike count in bins of sync_bin steps (loss_functions.py:964-981);
+ *              with n_sync_samples > 0 the reference's own target (SynchronizationLoss.__call__,
+ *              loss_functions.py:983-1044): every sample is one trial and a set of neurons, its
+ *              population count over [sync_t_start, sync_t_end) is binned with every bin size below
+ *              half the window, Fano = biased variance / max(mean, 1e-7), averaged over samples, and
+ *              the loss is sync_cost * mean_k (target_k - Fano_k)^2.  The reference draws trial,
+ *              size and members of the samples at random in every call; here they are an input.
  * All costs are multiplied by loss_scale (1/replicas, multi_training.py:427-429). */
 typedef struct V1GLossSpec {
   const float* rate_target; /* [N] device, may be NULL when rate_cost == 0 or populations are given */
@@ -110,6 +117,17 @@ typedef struct V1GLossSpec {
   const float* rate_group_targets;   /* [n_rate_neurons] "sorted_target_rates", ascending per population, spikes/step */
   float rate_kappa;
   int32_t rate_pre_delay, rate_post_delay;
+  /* samples of the synchrony target in full (see above); sample s = trial sync_sample_trial[s] and the
+   * neurons at positions [offsets[s], offsets[s+1]) */
+  int32_t n_sync_samples;
+  int32_t n_sync_members;             /* = offsets[n_sync_samples] */
+  const int32_t* sync_sample_trial;   /* [n_sync_samples] device */
+  const int32_t* sync_sample_offsets; /* [n_sync_samples + 1] device */
+  const int32_t* sync_sample_neurons; /* [n_sync_members] device */
+  int32_t n_sync_bins;
+  const int32_t* sync_bin_sizes;      /* [n_sync_bins] HOST, in steps; sizes not below half the window are ignored */
+  const float* sync_bin_targets;      /* [n_sync_bins] HOST, the measured Fano factor per bin size */
+  int32_t sync_t_start, sync_t_end;   /* window in steps; sync_t_end <= 0: end of the rollout */
 } V1GLossSpec;
 
 /* Event counters of the last rollout (for the roofline's algorithmic bytes). */

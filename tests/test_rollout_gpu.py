@@ -194,6 +194,35 @@ def test_bptt_with_rate_distribution_target(pre, post):
         assert rel_err(got, w) <= TOL_GRAD
 
 
+@pytest.mark.parametrize("t_start,t_end", [(0, 0), (6, 54)])
+def test_bptt_with_synchrony_samples_target(t_start, t_end):
+    """The reference's synchrony target (population Fano factors of sampled groups of excitatory
+    neurons over all bin sizes below half the window, ``loss_functions.py:964-1044``) on the
+    device: loss value and weight gradients against autograd through the oracle's form, which is
+    pinned to the reference's ``pop_fano_tf`` by tests/golden/reference_sync_loss.npz.  The 600-neuron
+    net has fewer excitatory neurons than the samples ask for, so some neurons sit in two samples."""
+    from oracle import losses as OL
+    cfg, dicts, orc, cell = _cells("small", **KW)
+    x, c = make_inputs(cfg)
+    samples, bins, targets = synth.make_sync_samples(cfg, dicts[0], cfg.batch, n_samples=12, seed=1)
+    cost = 0.05
+    z, v, _ = orc.rollout(torch.from_numpy(x), torch.from_numpy(c).long())
+    vlo = torch.from_numpy(-20.0 / cell.voltage_scale).float()
+    total = OL.synchronization_loss(z, samples, bins, targets, cost, t_start=t_start, t_end=t_end or None) + \
+        OL.voltage_loss(v, vlo, LOSS["voltage_cost"])
+    total.backward()
+    want = [orc.recurrent_weight_values.grad, orc.input_weight_values.grad, orc.bkg_input_weights.grad]
+    zc, _ = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), save_for_bwd=True)
+    assert torch.equal(zc.cpu().float(), z.detach())
+    grads = cell.backward(dict(sync_cost=cost, sync_samples=samples, sync_bin_sizes=bins, sync_bin_targets=targets,
+                               sync_t_start=t_start, sync_t_end=t_end, voltage_cost=LOSS["voltage_cost"],
+                               v_lo=vlo.cuda()))
+    cell.synchronize()
+    assert abs(float(grads[3][0]) - total.item()) <= 1e-4 * abs(total.item())
+    for got, w in zip(grads[:3], want):
+        assert rel_err(got, w) <= TOL_GRAD
+
+
 @pytest.mark.parametrize("options", [(), (("no_q_pack", 1),), (("rollout_chunk", 64),), (("no_meta", 1),)])
 def test_bptt_batch_of_five(options):
     """Batch 5 stores the backward Q rows as five 24-bit floats per 16-byte row (7.6e-6 relative

@@ -36,7 +36,12 @@ class V1GLossSpec(C.Structure):
                 ("n_rate_groups", C.c_int32), ("n_rate_neurons", C.c_int32),
                 ("rate_group_offsets", C.c_void_p), ("rate_group_neurons", C.c_void_p),
                 ("rate_group_targets", C.c_void_p), ("rate_kappa", C.c_float),
-                ("rate_pre_delay", C.c_int32), ("rate_post_delay", C.c_int32)]
+                ("rate_pre_delay", C.c_int32), ("rate_post_delay", C.c_int32),
+                ("n_sync_samples", C.c_int32), ("n_sync_members", C.c_int32),
+                ("sync_sample_trial", C.c_void_p), ("sync_sample_offsets", C.c_void_p),
+                ("sync_sample_neurons", C.c_void_p), ("n_sync_bins", C.c_int32),
+                ("sync_bin_sizes", C.c_void_p), ("sync_bin_targets", C.c_void_p),
+                ("sync_t_start", C.c_int32), ("sync_t_end", C.c_int32)]
 
 
 class V1GCounters(C.Structure):

@@ -109,6 +109,8 @@ struct V1GHandle {
   float* dy_ring = nullptr;
   int64_t dy_ring_cap = 0;
   float* dw_csr[V1G_NSRC] = {nullptr, nullptr, nullptr};
+  int32_t* sync_scratch = nullptr;  // membership lists, population counts and gradients of the synchrony samples
+  int64_t sync_scratch_cap = 0;
   int32_t* rate_scratch = nullptr;  // sort buffers of the rate-distribution target
   int64_t rate_scratch_cap = 0;
   float* loss_scratch = nullptr;  // rate sums [N], pop counts [B][T], bin grads, partial losses
@@ -168,6 +170,18 @@ int v1g_reserve(V1GHandle* h, T** p, int64_t* cap, int64_t need) {
   *cap = need;
   return V1G_OK;
 }
+
+// ---- synchrony target over given samples (v1g_losses.cu) ----
+struct V1GSyncTables {
+  const int32_t* first;       // [N] first membership position of a neuron, -1 = in no sample (NULL: term off)
+  const int32_t* next;        // [P] next membership position of the same neuron, -1 = end
+  const int32_t* pos_sample;  // [P] sample of a membership position
+  const int32_t* trial;       // [S] batch row of a sample
+  const float* g;             // [S][W] d loss / d population count
+  int t0, W;
+};
+int v1g_sync_samples_loss(V1GHandle* h, const V1GLossSpec* ls, int B, int T, float* loss_acc,
+                          V1GSyncTables* out, cudaStream_t st);
 
 // ---- rate-distribution target (v1g_losses.cu) ----
 int v1g_rate_distribution_loss(V1GHandle* h, const V1GLossSpec* ls, const int32_t* count, int B, int T,

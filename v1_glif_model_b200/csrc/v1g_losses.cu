@@ -125,3 +125,177 @@ int v1g_rate_distribution_loss(V1GHandle* h, const V1GLossSpec* ls, const int32_
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Synchrony target of the reference in full (SynchronizationLoss.__call__ and pop_fano_tf,
+// loss_functions.py:964-1044) for given samples.  A sample is one trial (batch row) and a set of
+// neurons; pop[s][t] is its population spike count at step t of the window [t0, t0 + W).  For every
+// bin size smaller than W/2 the counts are summed in non-overlapping bins (incomplete last bin
+// dropped), Fano = biased variance / max(mean, 1e-7) per sample, averaged over the samples; the loss
+// is sync_cost * mean_k (target_k - Fano_k)^2.  g[s][t] = d loss / d pop[s][t] is what the backward
+// rollout adds to dL/dz of the sample's members in the sample's trial.
+namespace {
+
+constexpr int SYNC_MAX_BINS = 32;
+constexpr float SYNC_EPS = 1e-7f;
+
+struct SyncBins {
+  int n;                       // bin sizes in use (already restricted to those below W/2)
+  int size[SYNC_MAX_BINS];
+  float target[SYNC_MAX_BINS];
+};
+
+// membership lists: first[n] -> position -> next[position]; pos_sample[position] = sample
+__global__ void __launch_bounds__(256) sync_members_kernel(const int32_t* __restrict__ offsets, int S,
+                                                           const int32_t* __restrict__ neurons, int P,
+                                                           int32_t* first, int32_t* __restrict__ next,
+                                                           int32_t* __restrict__ pos_sample) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= P) return;
+  int lo = 0, hi = S;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (offsets[mid] <= p) lo = mid; else hi = mid;
+  }
+  pos_sample[p] = lo;
+  next[p] = atomicExch(first + neurons[p], p);
+}
+
+// pop[s][t - t0] = spikes of the sample's neurons in its trial at step t
+__global__ void __launch_bounds__(256) sync_pop_kernel(const uint8_t* __restrict__ zr, int B, int N,
+                                                       const int32_t* __restrict__ trial,
+                                                       const int32_t* __restrict__ offsets,
+                                                       const int32_t* __restrict__ neurons, int t0, int W,
+                                                       float* __restrict__ pop) {
+  const int s = blockIdx.x;
+  const int b = trial[s], p0 = offsets[s], p1 = offsets[s + 1];
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const uint8_t* row = zr + ((int64_t)(t0 + i) * B + b) * N;
+    int c = 0;
+    for (int p = p0; p < p1; ++p) c += row[neurons[p]] & 1;
+    pop[(int64_t)s * W + i] = (float)c;
+  }
+}
+
+__device__ __forceinline__ float block_sum(float v, float* ws) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += ws[w];
+  return t;
+}
+
+// pass 0: stats[s][k] = (mean, variance) of the bin counts, fano_mean[k] += Fano / S
+// pass 1: g[s][t] = sum_k dL/dFano_k * dFano_sk / d pop[s][t]
+__global__ void __launch_bounds__(256) sync_fano_kernel(const float* __restrict__ pop, int S, int W, SyncBins bins,
+                                                        int pass, float cost, float2* __restrict__ stats,
+                                                        float* __restrict__ fano_mean, float* __restrict__ g) {
+  extern __shared__ float cnt_s[];  // bin counts of one bin size [W]
+  __shared__ float ws[8];
+  const int s = blockIdx.x;
+  const float* ps = pop + (int64_t)s * W;
+  for (int k = 0; k < bins.n; ++k) {
+    const int bs = bins.size[k], nb = W / bs;
+    __syncthreads();
+    for (int j = threadIdx.x; j < nb; j += blockDim.x) {
+      float c = 0.f;
+      for (int i = 0; i < bs; ++i) c += ps[j * bs + i];
+      cnt_s[j] = c;
+    }
+    __syncthreads();
+    if (pass == 0) {
+      float a = 0.f;
+      for (int j = threadIdx.x; j < nb; j += blockDim.x) a += cnt_s[j];
+      const float mean = block_sum(a, ws) / (float)nb;
+      float q = 0.f;
+      for (int j = threadIdx.x; j < nb; j += blockDim.x) q += (cnt_s[j] - mean) * (cnt_s[j] - mean);
+      const float var = block_sum(q, ws) / (float)nb;
+      if (threadIdx.x == 0) {
+        stats[(int64_t)s * bins.n + k] = make_float2(mean, var);
+        atomicAdd(fano_mean + k, var / fmaxf(mean, SYNC_EPS) / (float)S);
+      }
+    } else {
+      const float2 mv = stats[(int64_t)s * bins.n + k];
+      const float dldf = cost * 2.f * (fano_mean[k] - bins.target[k]) / (float)bins.n / (float)S;
+      const float m = fmaxf(mv.x, SYNC_EPS);
+      // d(var/m)/dc_j = 2 (c_j - mean) / (nb m) - [mean > eps] var / (m^2 nb)
+      const float k1 = 2.f / ((float)nb * m), k0 = mv.x > SYNC_EPS ? mv.y / (m * m * (float)nb) : 0.f;
+      for (int i = threadIdx.x; i < nb * bs; i += blockDim.x)
+        g[(int64_t)s * W + i] += dldf * (k1 * (cnt_s[i / bs] - mv.x) - k0);
+    }
+  }
+}
+
+__global__ void sync_loss_value_kernel(const float* __restrict__ fano_mean, SyncBins bins, float cost,
+                                       float* __restrict__ loss_acc) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    float a = 0.f;
+    for (int k = 0; k < bins.n; ++k) a += (bins.target[k] - fano_mean[k]) * (bins.target[k] - fano_mean[k]);
+    if (bins.n > 0) atomicAdd(loss_acc, cost * a / (float)bins.n);
+  }
+}
+
+}  // namespace
+
+// Fills h->sync_* (membership lists and g) for the backward rollout; loss_acc += loss.
+int v1g_sync_samples_loss(V1GHandle* h, const V1GLossSpec* ls, int B, int T, float* loss_acc,
+                          V1GSyncTables* out, cudaStream_t st) {
+  const int N = h->cfg.n_neurons, S = ls->n_sync_samples, P = ls->n_sync_members;
+  out->first = nullptr;
+  if (S <= 0 || P <= 0) return V1G_OK;
+  if (!ls->sync_sample_trial || !ls->sync_sample_offsets || !ls->sync_sample_neurons ||
+      (ls->n_sync_bins > 0 && (!ls->sync_bin_sizes || !ls->sync_bin_targets)))
+    return v1g_fail(h, V1G_EINVAL, "synchrony samples: null trial / offsets / neurons / bins");
+  const int t0 = std::max(ls->sync_t_start, 0), t1 = ls->sync_t_end > 0 ? std::min(ls->sync_t_end, T) : T;
+  const int W = t1 - t0;
+  if (W < 2) return v1g_fail(h, V1G_EINVAL, "synchrony window [%d, %d) is too short", t0, t1);
+  SyncBins bins;
+  bins.n = 0;
+  for (int k = 0; k < ls->n_sync_bins; ++k) {  // host arrays
+    const int bs = ls->sync_bin_sizes[k];
+    if (bs < 1) return v1g_fail(h, V1G_EINVAL, "synchrony bin size %d", bs);
+    if (!(bs < W / 2)) continue;
+    if (bins.n == SYNC_MAX_BINS) return v1g_fail(h, V1G_ERANGE, "more than %d synchrony bin sizes", SYNC_MAX_BINS);
+    bins.size[bins.n] = bs;
+    bins.target[bins.n] = ls->sync_bin_targets[k];
+    ++bins.n;
+  }
+  const float cost = ls->sync_cost * ls->loss_scale;
+  // scratch (4-byte words): first[N] | next[P] | pos_sample[P] | fano_mean[32] | stats[S*32*2] | pop[S*W] | g[S*W]
+  const int64_t words = (int64_t)N + 2 * (int64_t)P + SYNC_MAX_BINS + (int64_t)S * SYNC_MAX_BINS * 2 + 2 * (int64_t)S * W + 2;
+  int rc;
+  if ((rc = v1g_reserve(h, &h->sync_scratch, &h->sync_scratch_cap, words))) return rc;
+  int32_t* first = h->sync_scratch;
+  int32_t* next = first + N;
+  int32_t* pos_sample = next + P;
+  float* fano_mean = (float*)(pos_sample + P);
+  float2* stats = (float2*)(((uintptr_t)(fano_mean + SYNC_MAX_BINS) + 7) & ~(uintptr_t)7);
+  float* pop = (float*)(stats + (int64_t)S * SYNC_MAX_BINS);
+  float* g = pop + (int64_t)S * W;
+  V1G_CUDA(h, cudaMemsetAsync(first, 0xff, (size_t)N * sizeof(int32_t), st));  // -1: in no sample
+  V1G_CUDA(h, cudaMemsetAsync(fano_mean, 0, SYNC_MAX_BINS * sizeof(float), st));
+  V1G_CUDA(h, cudaMemsetAsync(g, 0, (size_t)S * W * sizeof(float), st));
+  sync_members_kernel<<<(P + 255) / 256, 256, 0, st>>>(ls->sync_sample_offsets, S, ls->sync_sample_neurons, P,
+                                                       first, next, pos_sample);
+  sync_pop_kernel<<<S, 256, 0, st>>>(h->tape_zr, B, N, ls->sync_sample_trial, ls->sync_sample_offsets,
+                                     ls->sync_sample_neurons, t0, W, pop);
+  const size_t smem = (size_t)W * sizeof(float);
+  if (smem > 200 * 1024) return v1g_fail(h, V1G_ERANGE, "synchrony window of %d steps is too long", W);
+  if (smem > 48 * 1024)
+    V1G_CUDA(h, cudaFuncSetAttribute(sync_fano_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  sync_fano_kernel<<<S, 256, smem, st>>>(pop, S, W, bins, 0, cost, stats, fano_mean, g);
+  sync_fano_kernel<<<S, 256, smem, st>>>(pop, S, W, bins, 1, cost, stats, fano_mean, g);
+  sync_loss_value_kernel<<<1, 32, 0, st>>>(fano_mean, bins, cost, loss_acc);
+  v1g_count_launches(5);
+  V1G_CUDA(h, cudaGetLastError());
+  out->first = first;
+  out->next = next;
+  out->pos_sample = pos_sample;
+  out->trial = ls->sync_sample_trial;
+  out->g = g;
+  out->t0 = t0;
+  out->W = W;
+  return V1G_OK;
+}

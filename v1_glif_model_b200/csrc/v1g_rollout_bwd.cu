@@ -58,6 +58,7 @@ struct BwdArgs {
   // loss
   const float* rate_coef;  // [N] dL/dz contribution of the rate term, or NULL
   int rate_t0, rate_t1;    // steps whose spikes enter the rate term
+  V1GSyncTables sync;      // synchrony target over given samples (first == NULL: off)
   const float* sgrad;      // [B][nbins] dL/d(bin count), or NULL
   int sync_bin, nbins;
   float volt_coef;  // voltage_cost * loss_scale / (B*T*N); gradient is 2*volt_coef*(...)
@@ -424,6 +425,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       const float k_decay = a.decay[n], k_cf = a.cf[n], k_ad0 = a.asc_decay[2 * n], k_ad1 = a.asc_decay[2 * n + 1];
       const float rc = (a.rate_coef && t >= a.rate_t0 && t < a.rate_t1) ? a.rate_coef[n] : 0.f;
       const float vlo = a.v_lo ? a.v_lo[n] : 0.f;
+      const int sync_p0 = (a.sync.first && t >= a.sync.t0 && t < a.sync.t0 + a.sync.W) ? a.sync.first[n] : -1;
       float dyv[BP_][R_];  // dy(t-2) of every batch row of this neuron
 #pragma unroll
       for (int b = 0; b < BP_; ++b) {
@@ -436,6 +438,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           const bool free_ = !(zr & 2u);
           const int64_t oi = ((int64_t)b * T + t) * N + n;
           float gz = rc + (bin >= 0 ? a.sgrad[b * a.nbins + bin] : 0.f) + (a.g_z ? a.g_z[oi] : 0.f);
+          for (int sp = sync_p0; sp >= 0; sp = a.sync.next[sp]) {  // samples of the synchrony target with this neuron
+            const int smp = a.sync.pos_sample[sp];
+            if (a.sync.trial[smp] == b) gz += a.sync.g[(int64_t)smp * a.sync.W + (t - a.sync.t0)];
+          }
           gz += a.rec_factor * gzC[si];
           float gv = G_v[si] + (a.g_v ? a.g_v[oi] : 0.f);
           if (a.volt_coef != 0.f) {
@@ -1062,7 +1068,8 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   const int64_t q_elems = (int64_t)K * Np * C * QW;
   if (q_elems >= 0x7fffffffLL) return v1g_fail(h, V1G_ERANGE, "backward Q ring of %lld elements exceeds 32-bit indexing", (long long)q_elems);
   if ((rc = v1g_reserve(h, &h->dy_ring, &h->dy_ring_cap, q_elems))) return rc;
-  const int nbins = (ls.sync_cost != 0.f && ls.sync_bin > 0) ? T / ls.sync_bin : 0;
+  const bool sync_samples = ls.sync_cost != 0.f && ls.n_sync_samples > 0;
+  const int nbins = (ls.sync_cost != 0.f && !sync_samples && ls.sync_bin > 0) ? T / ls.sync_bin : 0;
   // loss scratch layout (floats): acc[4] | rate_coef[N] | sgrad[B*nbins] | spike_count[N] (int) | popcount[T*B] (int)
   const int64_t ls_elems = 4 + (int64_t)N + (int64_t)B * std::max(nbins, 1) + N + (int64_t)T * B;
   if ((rc = v1g_reserve(h, &h->loss_scratch, &h->loss_scratch_cap, ls_elems))) return rc;
@@ -1102,7 +1109,13 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
     V1G_CUDA(h, cudaGetLastError());
   }
 
+  V1GSyncTables sync_tables;
+  sync_tables.first = nullptr;
+  if (sync_samples)
+    if ((rc = v1g_sync_samples_loss(h, &ls, B, T, acc + 3, &sync_tables, st))) return rc;
+
   BwdArgs a;
+  a.sync = sync_tables;
   a.N = N; a.D = D; a.K = K; a.B = B; a.T = T; a.Np = Np;
   a.chunk = plan.chunk; a.chunkP = plan.chunkP; a.S = S; a.C = C; a.n_bkg = c.n_bkg;
   a.state_in_smem = state_in_smem;

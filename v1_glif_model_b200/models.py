@@ -259,7 +259,10 @@ class V1Column:
         ``v_lo`` (tensor [N]), ``rate_cost``, ``voltage_cost``, ``sync_cost``, ``fano_target``,
         ``sync_bin``, ``loss_scale`` and, for the reference's rate-distribution target
         (``loss_functions.py:782-889``), ``rate_groups`` = list of ``(neuron_ids, sorted_targets)``
-        with ``rate_kappa``, ``rate_pre_delay``, ``rate_post_delay``."""
+        with ``rate_kappa``, ``rate_pre_delay``, ``rate_post_delay``; and, for the reference's
+        synchrony target (``loss_functions.py:983-1044``), ``sync_samples`` = list of
+        ``(trial, neuron_ids)`` with ``sync_bin_sizes`` (steps), ``sync_bin_targets`` (measured Fano
+        factors), ``sync_t_start``, ``sync_t_end``."""
         loss = dict(loss or {})
         spec = _lib.V1GLossSpec(
             rate_target=loss["rate_target"].data_ptr() if loss.get("rate_target") is not None else None,
@@ -286,6 +289,29 @@ class V1Column:
             spec.rate_kappa = float(loss.get("rate_kappa", 0.002))
             spec.rate_pre_delay = int(loss.get("rate_pre_delay", 0) or 0)
             spec.rate_post_delay = int(loss.get("rate_post_delay", 0) or 0)
+        samples = loss.get("sync_samples")
+        if samples:
+            key = id(samples)
+            if getattr(self, "_sync_samples_key", None) != key:
+                sizes = [len(smp[1]) for smp in samples]
+                offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int32)
+                trial = np.asarray([smp[0] for smp in samples], dtype=np.int32)
+                ids = np.concatenate([np.asarray(smp[1], dtype=np.int32) for smp in samples])
+                dev = lambda a: torch.from_numpy(a).to(self.device)
+                self._sync_samples_dev = (dev(trial), dev(offs), dev(ids), len(sizes), int(offs[-1]))
+                self._sync_samples_key = key
+            trial, offs, ids, ns, nm = self._sync_samples_dev
+            self._sync_bins_host = (np.ascontiguousarray(loss["sync_bin_sizes"], dtype=np.int32),
+                                    np.ascontiguousarray(loss["sync_bin_targets"], dtype=np.float32))
+            spec.n_sync_samples, spec.n_sync_members = ns, nm
+            spec.sync_sample_trial = trial.data_ptr()
+            spec.sync_sample_offsets = offs.data_ptr()
+            spec.sync_sample_neurons = ids.data_ptr()
+            spec.n_sync_bins = len(self._sync_bins_host[0])
+            spec.sync_bin_sizes = self._sync_bins_host[0].ctypes.data
+            spec.sync_bin_targets = self._sync_bins_host[1].ctypes.data
+            spec.sync_t_start = int(loss.get("sync_t_start", 0) or 0)
+            spec.sync_t_end = int(loss.get("sync_t_end", 0) or 0)
         return spec
 
     def backward_internal(self, loss, grads_flat, losses=None):

@@ -230,3 +230,29 @@ def make_rate_groups(cfg: SynthConfig | str, network, seed: int = 0):
         sample = np.sort(np.interp(rng.uniform(0.0, 1.0, ids.size), pct, recorded))
         groups.append((ids, sample.astype(np.float32)))
     return groups
+
+
+def make_sync_samples(cfg: SynthConfig | str, network, batch: int, n_samples: int = 12, seed: int = 0):
+    """Samples and targets for the synchrony loss in the form ``SynchronizationLoss.__call__`` builds
+    them (``loss_functions.py:997-1024``): ``n_samples`` draws of a trial (batch row) and of
+    ``clip(int(N(70, 30)), 15, n_exc)`` excitatory neurons taken without replacement from a shuffled
+    list (reshuffled when it runs out), the reference's log-spaced bin sizes
+    (``np.logspace(-3, 0, 20)`` s, ``:945-950``) and a seeded stand-in for the measured mean Fano
+    factor per bin size (1 + 0.6 log10(bin/ms)); none of the recorded data is used.
+    Returns ``(samples, bin_sizes_steps, target_fanos)``.
+    """
+    if isinstance(cfg, str):
+        cfg = CONFIGS[cfg]
+    rng = np.random.Generator(np.random.PCG64(seed + 49979687))
+    exc = np.nonzero(np.asarray(network["is_exc"]))[0].astype(np.int32)
+    pool = rng.permutation(exc)
+    samples, at = [], 0
+    for _ in range(n_samples):
+        size = int(np.clip(int(rng.normal(70.0, 30.0)), 15, exc.size))
+        if at + size > pool.size:
+            pool, at = rng.permutation(pool), 0
+        samples.append((int(rng.integers(0, batch)), np.sort(pool[at:at + size])))
+        at += size
+    bins_ms = np.unique(np.maximum(1, np.round(np.logspace(-3, 0, 20) * 1000.0).astype(np.int64)))
+    targets = (1.0 + 0.6 * np.log10(bins_ms)).astype(np.float32)
+    return samples, bins_ms.astype(np.int32), targets
