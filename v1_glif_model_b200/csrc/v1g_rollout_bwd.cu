@@ -420,12 +420,24 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     // ---------------- dense adjoint of step t, publish Q(t-2), background weight gradient ----------------
     const int bin = (a.sgrad && a.sync_bin > 0 && t / a.sync_bin < a.nbins) ? t / a.sync_bin : -1;
     float* Qw = a.Q + (int64_t)((t + K - 2) % K) * Np * C * QW;
+    const bool sync_on = a.sync.first != nullptr && t >= a.sync.t0 && t < a.sync.t0 + a.sync.W;
     for (int k = tid; k < cn; k += NT) {
       const int n = n0 + k;
       const float k_decay = a.decay[n], k_cf = a.cf[n], k_ad0 = a.asc_decay[2 * n], k_ad1 = a.asc_decay[2 * n + 1];
       const float rc = (a.rate_coef && t >= a.rate_t0 && t < a.rate_t1) ? a.rate_coef[n] : 0.f;
       const float vlo = a.v_lo ? a.v_lo[n] : 0.f;
-      const int sync_p0 = (a.sync.first && t >= a.sync.t0 && t < a.sync.t0 + a.sync.W) ? a.sync.first[n] : -1;
+      float sadd[BP_];  // synchrony target over given samples: dL/dz[b, t, n]
+#pragma unroll
+      for (int b = 0; b < BP_; ++b) sadd[b] = 0.f;
+      if (sync_on) {
+        for (int sp = a.sync.first[n]; sp >= 0; sp = a.sync.next[sp]) {
+          const int smp = a.sync.pos_sample[sp];
+          const int tb = a.sync.trial[smp];
+          const float gs = a.sync.g[(int64_t)smp * a.sync.W + (t - a.sync.t0)];
+#pragma unroll
+          for (int b = 0; b < BP_; ++b) sadd[b] += (b == tb) ? gs : 0.f;
+        }
+      }
       float dyv[BP_][R_];  // dy(t-2) of every batch row of this neuron
 #pragma unroll
       for (int b = 0; b < BP_; ++b) {
@@ -438,10 +450,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           const bool free_ = !(zr & 2u);
           const int64_t oi = ((int64_t)b * T + t) * N + n;
           float gz = rc + (bin >= 0 ? a.sgrad[b * a.nbins + bin] : 0.f) + (a.g_z ? a.g_z[oi] : 0.f);
-          for (int sp = sync_p0; sp >= 0; sp = a.sync.next[sp]) {  // samples of the synchrony target with this neuron
-            const int smp = a.sync.pos_sample[sp];
-            if (a.sync.trial[smp] == b) gz += a.sync.g[(int64_t)smp * a.sync.W + (t - a.sync.t0)];
-          }
+          gz += sadd[b];
           gz += a.rec_factor * gzC[si];
           float gv = G_v[si] + (a.g_v ? a.g_v[oi] : 0.f);
           if (a.volt_coef != 0.f) {
