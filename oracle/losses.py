@@ -120,3 +120,41 @@ def synchronization_loss(z, samples, bin_sizes, target_fanos, cost, t_start=0, t
     zt = z[:, t_start:t_end, :]
     pop = torch.stack([zt[tr][:, torch.as_tensor(ids, dtype=torch.long)].sum(dim=1) for tr, ids in samples])
     return loss_scale * population_fano_loss(pop, bin_sizes, target_fanos, cost, eps)
+
+
+def orientation_selectivity_loss(z, angle, tuning_angle, type_ids, osi_targets, dsi_targets, type_counts,
+                                 cost, pre_delay=0, post_delay=0, normalizer=None, loss_scale=1.0,
+                                 min_rate=0.0005):
+    """The reference's population OSI/DSI target (``OrientationSelectivityLoss`` with
+    ``method="crowd_osi"``: ``__call__``, ``crowd_osi_loss`` and ``_compute_osi_dsi_core``,
+    ``loss_functions.py:1340-1440``).
+
+    ``rates[b, n]`` = mean of the spikes over the steps ``[pre_delay, T - post_delay)``, optionally
+    divided by ``max(normalizer[n], min_rate)``; ``delta[b, n] = (angle[b] - tuning_angle[n]) pi/180``.
+    Per trial and cell type: ``den = max(mean_n rates, min_rate)``, ``osi = mean_n(rates cos 2 delta) /
+    den``, ``dsi = mean_n(rates cos delta) / den`` (means over the neurons whose ``type_ids`` equal
+    the type); both are averaged over the trials and the loss is
+    ``cost * sum_type count_type ((osi - osi_target)^2 + (dsi - dsi_target)^2) / sum_type count_type``.
+    """
+    t = z.shape[1]
+    zt = z[:, pre_delay:t - post_delay if post_delay else t, :]
+    rates = zt.mean(dim=1)
+    dt = rates.dtype
+    if normalizer is not None:
+        rates = rates / torch.clamp(torch.as_tensor(normalizer, dtype=dt), min=min_rate)
+    delta = (torch.as_tensor(angle, dtype=dt)[:, None] - torch.as_tensor(tuning_angle, dtype=dt)[None, :]) \
+        * (torch.pi / 180.0)
+    ids = torch.as_tensor(type_ids, dtype=torch.long)
+    n_types = len(osi_targets)
+    onehot = torch.nn.functional.one_hot(ids, n_types).to(dt)            # [N, types]
+    n_per = torch.clamp(onehot.sum(dim=0), min=1.0)
+
+    def seg_mean(x):
+        return (x @ onehot) / n_per                                      # [B, types]
+
+    den = torch.clamp(seg_mean(rates), min=min_rate)
+    osi = (seg_mean(rates * torch.cos(2.0 * delta)) / den).mean(dim=0)
+    dsi = (seg_mean(rates * torch.cos(delta)) / den).mean(dim=0)
+    cnt = torch.as_tensor(type_counts, dtype=dt)
+    per_type = (osi - torch.as_tensor(osi_targets, dtype=dt)) ** 2 + (dsi - torch.as_tensor(dsi_targets, dtype=dt)) ** 2
+    return cost * loss_scale * (per_type * cnt).sum() / cnt.sum()

@@ -13,7 +13,9 @@ loss, gradient with respect to the spikes' per-neuron rates).  ``tests/test_orac
 checks ``oracle/losses.py::rate_distribution_loss`` against it.  A second fixture,
 ``reference_sync_loss.npz``, holds the population Fano factors of
 ``SynchronizationLoss.pop_fano_tf`` for seeded population counts and the loss built from them, for
-``oracle/losses.py::synchronization_loss``.
+``oracle/losses.py::synchronization_loss``; a third, ``reference_osi_loss.npz``, the population
+OSI/DSI target (``OrientationSelectivityLoss`` with ``method="crowd_osi"``) with and without the
+rate normalizer, for ``oracle/losses.py::orientation_selectivity_loss``.
 
 The stand-in's ``tf.random.shuffle`` is the identity and its ``tf.sort`` is stable, so neurons with
 equal rates keep the order of ``neuron_ids`` (the reference orders them at random).
@@ -107,6 +109,52 @@ def sync_fixture(ref_root):
     print(f"wrote {out}: loss {loss.item():.6e}, fanos {fanos.detach().numpy().round(3)}")
 
 
+def osi_fixture(ref_root):
+    """The population OSI/DSI target of the reference (``OrientationSelectivityLoss.__call__`` with
+    ``method="crowd_osi"``, ``loss_functions.py:1340-1440``) on seeded spikes; the object is created
+    without its constructor (which reads recorded data) and given the attributes the method reads."""
+    lf = load_reference_losses(ref_root)
+    rng = np.random.Generator(np.random.PCG64(11))
+    b, t, n, n_types = 3, 50, 400, 4
+    tuning = rng.uniform(0.0, 360.0, n)
+    type_ids = rng.integers(0, n_types, n)
+    angle = np.array([0.0, 45.0, 270.0])
+    # orientation-tuned spike probabilities so that OSI and DSI are away from zero
+    d = np.deg2rad(angle[:, None] - tuning[None, :])
+    p = 0.02 * (1.0 + 0.6 * np.cos(2 * d) + 0.3 * np.cos(d)) * rng.lognormal(0.0, 0.5, n)[None, :]
+    p[:, type_ids == 3] *= 0.002                       # a nearly silent type: denominator clamped
+    z = (rng.random((b, t, n)) < p[:, None, :]).astype(np.float64)
+    normalizer = rng.lognormal(np.log(0.01), 0.7, n)
+    normalizer[::17] = 0.0                             # below the floor of 0.0005
+    osi_t, dsi_t = rng.uniform(0.2, 0.6, n_types), rng.uniform(0.05, 0.3, n_types)
+    counts = np.bincount(type_ids, minlength=n_types).astype(np.float64)
+    out = {}
+    for tag, norm in (("plain", None), ("normalized", normalizer)):
+        obj = object.__new__(lf.OrientationSelectivityLoss)
+        obj._pre_delay, obj._post_delay, obj._dtype, obj._method = 4, 6, torch.float64, "crowd_osi"
+        obj._core_mask, obj._osi_cost = None, 20.0
+        obj._tuning_angles = torch.from_numpy(tuning)
+        obj._tf_pi = torch.tensor(np.pi, dtype=torch.float64)
+        obj._min_rates_threshold = torch.tensor(0.0005, dtype=torch.float64)
+        obj.node_type_ids = torch.from_numpy(type_ids.astype(np.int64))
+        obj._n_node_types = n_types
+        obj.osi_target_values, obj.dsi_target_values = torch.from_numpy(osi_t), torch.from_numpy(dsi_t)
+        obj.cell_type_count = torch.from_numpy(counts)
+        zt = torch.from_numpy(z).requires_grad_(True)
+        loss = obj(zt, torch.from_numpy(angle), True,
+                   normalizer=None if norm is None else torch.from_numpy(norm))
+        loss.backward()
+        out["loss_" + tag], out["grad_z_" + tag] = loss.item(), zt.grad.numpy()
+        print(f"osi/dsi {tag}: loss {loss.item():.6e}")
+    path = os.path.join(HERE, "reference_osi_loss.npz")
+    np.savez_compressed(path, z=z.astype(np.uint8), angle=angle, tuning=tuning, type_ids=type_ids.astype(np.int32),
+                        osi_targets=osi_t, dsi_targets=dsi_t, type_counts=counts, normalizer=normalizer,
+                        osi_cost=20.0, pre_delay=4, post_delay=6, **out)
+    print(f"wrote {path}")
+
+
 if __name__ == "__main__":
+    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     main()
-    sync_fixture(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    sync_fixture(root)
+    osi_fixture(root)

@@ -107,6 +107,13 @@ def _unsorted_segment_sum(data, segment_ids, num_segments):
     return torch.zeros(shape, dtype=data.dtype).index_add(0, _t(segment_ids).long(), data)
 
 
+def _unsorted_segment_mean(data, segment_ids, num_segments):
+    ids = _t(segment_ids).long()
+    tot = torch.zeros((_i(num_segments),), dtype=data.dtype).index_add(0, ids, data)
+    cnt = torch.zeros((_i(num_segments),), dtype=data.dtype).index_add(0, ids, torch.ones_like(data))
+    return tot / torch.clamp(cnt, min=1.0)
+
+
 def _shape(x, out_type=None):
     return torch.tensor(list(x.shape), dtype=out_type or torch.int32)
 
@@ -257,7 +264,9 @@ def install():
     tf.RaggedTensor = RaggedTensor
     tf.math = types.SimpleNamespace(unsorted_segment_sum=_unsorted_segment_sum, exp=torch.exp,
                                     log=torch.log,
-                                    reduce_variance=lambda x, axis=None: torch.var(x, dim=axis, unbiased=False))
+                                    reduce_variance=lambda x, axis=None: torch.var(x, dim=axis, unbiased=False),
+                                    cos=torch.cos, square=torch.square,
+                                    unsorted_segment_mean=_unsorted_segment_mean)
     tf.TensorArray = _TensorArray
     tf.squeeze = lambda x, axis=None: x.squeeze() if axis is None else x.squeeze(axis)
     tf.nn = types.SimpleNamespace(relu=torch.relu, sigmoid=torch.sigmoid, conv1d=_conv1d,

@@ -117,3 +117,20 @@ def test_oracle_population_fano_loss_equals_reference_loss_code():
     loss.backward()
     assert abs(loss.item() - float(f["loss"])) <= 1e-12 * abs(float(f["loss"]))
     assert rel_err(pop.grad, torch.from_numpy(f["grad_counts"])) <= 1e-12
+
+
+@pytest.mark.parametrize("tag", ["plain", "normalized"])
+def test_oracle_orientation_selectivity_loss_equals_reference_loss_code(tag):
+    """``oracle/losses.py::orientation_selectivity_loss`` against the value and gradient of the
+    reference's ``OrientationSelectivityLoss.__call__`` (crowd OSI/DSI) for the same spikes (fp64)."""
+    from oracle import losses
+    f = np.load(os.path.join(ROOT, "tests", "golden", "reference_osi_loss.npz"))
+    z = torch.from_numpy(f["z"].astype(np.float64)).requires_grad_(True)
+    loss = losses.orientation_selectivity_loss(
+        z, f["angle"], f["tuning"], f["type_ids"], f["osi_targets"], f["dsi_targets"], f["type_counts"],
+        float(f["osi_cost"]), pre_delay=int(f["pre_delay"]), post_delay=int(f["post_delay"]),
+        normalizer=f["normalizer"] if tag == "normalized" else None)
+    loss.backward()
+    want = float(f["loss_" + tag])
+    assert abs(loss.item() - want) <= 1e-12 * abs(want)
+    assert rel_err(z.grad, torch.from_numpy(f["grad_z_" + tag])) <= 1e-11
