@@ -98,6 +98,13 @@ typedef struct V1GState {
  *              half the window, Fano = biased variance / max(mean, 1e-7), averaged over samples, and
  *              the loss is sync_cost * mean_k (target_k - Fano_k)^2.  The reference draws trial,
  *              size and members of the samples at random in every call; here they are an input.
+ *   OSI/DSI  : the reference's population orientation / direction selectivity target
+ *              (OrientationSelectivityLoss with method "crowd_osi", loss_functions.py:1340-1440):
+ *              rates per trial over [osi_pre_delay, T - osi_post_delay), optionally divided by a
+ *              normaliser; per trial and cell type osi = mean(rates cos 2d) / max(mean rates, 0.0005),
+ *              dsi with cos d, d = angle[b] - tuning_angle[n]; averaged over trials;
+ *              osi_cost * sum_type count ((osi - target)^2 + (dsi - target)^2) / sum_type count.
+ *              Its value is added to the synchrony slot of the returned losses.
  * All costs are multiplied by loss_scale (1/replicas, multi_training.py:427-429). */
 typedef struct V1GLossSpec {
   const float* rate_target; /* [N] device, may be NULL when rate_cost == 0 or populations are given */
@@ -128,6 +135,17 @@ typedef struct V1GLossSpec {
   const int32_t* sync_bin_sizes;      /* [n_sync_bins] HOST, in steps; sizes not below half the window are ignored */
   const float* sync_bin_targets;      /* [n_sync_bins] HOST, the measured Fano factor per bin size */
   int32_t sync_t_start, sync_t_end;   /* window in steps; sync_t_end <= 0: end of the rollout */
+  /* population OSI/DSI target (see above), off when osi_cost == 0 or n_osi_types == 0 */
+  float osi_cost;
+  int32_t n_osi_types;
+  const float* osi_angle;          /* [B] device, stimulus direction of each trial in degrees */
+  const float* osi_tuning_angle;   /* [N] device, network['tuning_angle'] in degrees */
+  const int32_t* osi_type_ids;     /* [N] device, cell type of every neuron ("node_type_ids") */
+  const float* osi_normalizer;     /* [N] device or NULL, rate normaliser (floored at 0.0005) */
+  const float* osi_targets;        /* [n_osi_types] HOST, measured OSI per cell type */
+  const float* dsi_targets;        /* [n_osi_types] HOST */
+  const float* osi_type_counts;    /* [n_osi_types] HOST, the weights "cell_type_count" */
+  int32_t osi_pre_delay, osi_post_delay;
 } V1GLossSpec;
 
 /* Event counters of the last rollout (for the roofline's algorithmic bytes). */

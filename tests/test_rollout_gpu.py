@@ -223,6 +223,44 @@ def test_bptt_with_synchrony_samples_target(t_start, t_end):
         assert rel_err(got, w) <= TOL_GRAD
 
 
+@pytest.mark.parametrize("with_normalizer", [False, True])
+def test_bptt_with_osi_dsi_target(with_normalizer):
+    """The reference's population OSI/DSI target (``OrientationSelectivityLoss``, crowd method,
+    ``loss_functions.py:1340-1440``) on the device: loss value and weight gradients against autograd
+    through the oracle's form, which is pinned to the reference's code by
+    tests/golden/reference_osi_loss.npz."""
+    from oracle import losses as OL
+    cfg, dicts, orc, cell = _cells("small", **KW)
+    x, c = make_inputs(cfg)
+    rng = np.random.Generator(np.random.PCG64(5))
+    n = cfg.n_neurons
+    type_ids = np.asarray(dicts[0]["node_type_ids"], dtype=np.int32)
+    n_types = int(type_ids.max()) + 1
+    tuning = rng.uniform(0.0, 360.0, n).astype(np.float32)
+    angle = rng.uniform(0.0, 360.0, cfg.batch).astype(np.float32)
+    osi_t, dsi_t = rng.uniform(0.2, 0.6, n_types).astype(np.float32), rng.uniform(0.05, 0.3, n_types).astype(np.float32)
+    counts = np.bincount(type_ids, minlength=n_types).astype(np.float32)
+    norm = rng.lognormal(np.log(0.02), 0.6, n).astype(np.float32) if with_normalizer else None
+    cost, pre, post = 5.0, 4, 6
+    z, v, _ = orc.rollout(torch.from_numpy(x), torch.from_numpy(c).long())
+    vlo = torch.from_numpy(-20.0 / cell.voltage_scale).float()
+    total = OL.orientation_selectivity_loss(z, angle, tuning, type_ids, osi_t, dsi_t, counts, cost, pre_delay=pre,
+                                            post_delay=post, normalizer=norm) + \
+        OL.voltage_loss(v, vlo, LOSS["voltage_cost"])
+    total.backward()
+    want = [orc.recurrent_weight_values.grad, orc.input_weight_values.grad, orc.bkg_input_weights.grad]
+    zc, _ = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), save_for_bwd=True)
+    assert torch.equal(zc.cpu().float(), z.detach())
+    grads = cell.backward(dict(osi_cost=cost, osi_angle=angle, osi_tuning_angle=tuning, osi_type_ids=type_ids,
+                               osi_targets=osi_t, dsi_targets=dsi_t, osi_type_counts=counts, osi_normalizer=norm,
+                               osi_pre_delay=pre, osi_post_delay=post, voltage_cost=LOSS["voltage_cost"],
+                               v_lo=vlo.cuda()))
+    cell.synchronize()
+    assert abs(float(grads[3][0]) - total.item()) <= 1e-4 * abs(total.item())
+    for got, w in zip(grads[:3], want):
+        assert rel_err(got, w) <= TOL_GRAD
+
+
 @pytest.mark.parametrize("options", [(), (("no_q_pack", 1),), (("rollout_chunk", 64),), (("no_meta", 1),)])
 def test_bptt_batch_of_five(options):
     """Batch 5 stores the backward Q rows as five 24-bit floats per 16-byte row (7.6e-6 relative

@@ -41,7 +41,12 @@ class V1GLossSpec(C.Structure):
                 ("sync_sample_trial", C.c_void_p), ("sync_sample_offsets", C.c_void_p),
                 ("sync_sample_neurons", C.c_void_p), ("n_sync_bins", C.c_int32),
                 ("sync_bin_sizes", C.c_void_p), ("sync_bin_targets", C.c_void_p),
-                ("sync_t_start", C.c_int32), ("sync_t_end", C.c_int32)]
+                ("sync_t_start", C.c_int32), ("sync_t_end", C.c_int32),
+                ("osi_cost", C.c_float), ("n_osi_types", C.c_int32), ("osi_angle", C.c_void_p),
+                ("osi_tuning_angle", C.c_void_p), ("osi_type_ids", C.c_void_p),
+                ("osi_normalizer", C.c_void_p), ("osi_targets", C.c_void_p),
+                ("dsi_targets", C.c_void_p), ("osi_type_counts", C.c_void_p),
+                ("osi_pre_delay", C.c_int32), ("osi_post_delay", C.c_int32)]
 
 
 class V1GCounters(C.Structure):

@@ -136,6 +136,7 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   cudaFree(h->tape_stats);
   cudaFree(h->rate_scratch);
   cudaFree(h->sync_scratch);
+  cudaFree(h->osi_scratch);
   cudaFree(h->lgn_offsets);
   cudaFree(h->ring);
   cudaFree(h->state_ws);

@@ -109,6 +109,8 @@ struct V1GHandle {
   float* dy_ring = nullptr;
   int64_t dy_ring_cap = 0;
   float* dw_csr[V1G_NSRC] = {nullptr, nullptr, nullptr};
+  float* osi_scratch = nullptr;  // spike counts, segment sums and the [B][N] gradient table of the OSI/DSI target
+  int64_t osi_scratch_cap = 0;
   int32_t* sync_scratch = nullptr;  // membership lists, population counts and gradients of the synchrony samples
   int64_t sync_scratch_cap = 0;
   int32_t* rate_scratch = nullptr;  // sort buffers of the rate-distribution target
@@ -182,6 +184,10 @@ struct V1GSyncTables {
 };
 int v1g_sync_samples_loss(V1GHandle* h, const V1GLossSpec* ls, int B, int T, float* loss_acc,
                           V1GSyncTables* out, cudaStream_t st);
+
+// ---- population OSI/DSI target (v1g_losses.cu) ----
+int v1g_osi_dsi_loss(V1GHandle* h, const V1GLossSpec* ls, int B, int T, float* loss_acc, const float** coef_out,
+                     int* t0_out, int* t1_out, cudaStream_t st);
 
 // ---- rate-distribution target (v1g_losses.cu) ----
 int v1g_rate_distribution_loss(V1GHandle* h, const V1GLossSpec* ls, const int32_t* count, int B, int T,

@@ -299,3 +299,161 @@ int v1g_sync_samples_loss(V1GHandle* h, const V1GLossSpec* ls, int B, int T, flo
   out->W = W;
   return V1G_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Population OSI/DSI target of the reference (OrientationSelectivityLoss with method "crowd_osi":
+// __call__, crowd_osi_loss, _compute_osi_dsi_core; loss_functions.py:1340-1440).
+// rates[b, n] = mean of the spikes over the steps [t0, t1), optionally divided by
+// max(normalizer[n], 0.0005); delta = (angle[b] - tuning[n]) pi / 180.  Per trial and cell type:
+// den = max(mean_n rates, 0.0005), osi = mean_n(rates cos 2 delta) / den, dsi = mean_n(rates cos delta) /
+// den; both averaged over the trials; loss = cost * sum_type count ((osi - osi_t)^2 + (dsi - dsi_t)^2) /
+// sum_type count.  The gradient with respect to z[b, t, n] is one coefficient per (b, n) for all steps
+// of the window.
+namespace {
+
+constexpr int OSI_MAX_TYPES = 64;
+constexpr float OSI_MIN_RATE = 0.0005f;
+
+__global__ void __launch_bounds__(256) osi_count_kernel(const uint8_t* __restrict__ zr, int B, int N, int t0,
+                                                        int t1, int32_t* __restrict__ cnt /*[B][N]*/) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (n >= N) return;
+  int c = 0;
+  for (int t = t0; t < t1; ++t) c += zr[((int64_t)t * B + b) * N + n] & 1;
+  cnt[(int64_t)b * N + n] = c;
+}
+
+__device__ __forceinline__ float osi_rate(int c, float inv_w, const float* normalizer, int n) {
+  float r = (float)c * inv_w;
+  if (normalizer) r = r / fmaxf(normalizer[n], OSI_MIN_RATE);
+  return r;
+}
+
+// seg[b][ty] = (sum rates, sum rates cos 2 delta, sum rates cos delta); seg_n[ty] = neurons of the type
+__global__ void __launch_bounds__(256) osi_segment_kernel(const int32_t* __restrict__ cnt, int B, int N,
+                                                          float inv_w, const float* __restrict__ normalizer,
+                                                          const float* __restrict__ angle,
+                                                          const float* __restrict__ tuning,
+                                                          const int32_t* __restrict__ type_ids, int n_types,
+                                                          float* __restrict__ seg, float* __restrict__ seg_n) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (n >= N) return;
+  const int ty = type_ids[n];
+  if (b == 0) atomicAdd(seg_n + ty, 1.f);
+  const int c = cnt[(int64_t)b * N + n];
+  if (c == 0) return;
+  const float r = osi_rate(c, inv_w, normalizer, n);
+  const float d = (angle[b] - tuning[n]) * (3.14159265358979323846f / 180.f);
+  float* o = seg + ((int64_t)b * n_types + ty) * 3;
+  atomicAdd(o, r);
+  atomicAdd(o + 1, r * cosf(2.f * d));
+  atomicAdd(o + 2, r * cosf(d));
+}
+
+struct OsiTargets {
+  int n;
+  float osi[OSI_MAX_TYPES], dsi[OSI_MAX_TYPES], count[OSI_MAX_TYPES];
+};
+
+// one block: loss value and, per (b, type), the three coefficients of d loss / d rates[b, n]:
+//   d = ca * cos 2 delta + cb * cos delta + cc
+__global__ void osi_type_kernel(const float* __restrict__ seg, const float* __restrict__ seg_n, int B,
+                                OsiTargets tg, float cost, float* __restrict__ coef3, float* __restrict__ loss_acc) {
+  __shared__ float osi_s[OSI_MAX_TYPES], dsi_s[OSI_MAX_TYPES];
+  const int ty = threadIdx.x;
+  float csum = 0.f;
+  for (int k = 0; k < tg.n; ++k) csum += tg.count[k];
+  if (ty < tg.n) {
+    const float nn = fmaxf(seg_n[ty], 1.f);
+    float so = 0.f, sd = 0.f;
+    for (int b = 0; b < B; ++b) {
+      const float* o = seg + ((int64_t)b * tg.n + ty) * 3;
+      const float den = fmaxf(o[0] / nn, OSI_MIN_RATE);
+      so += (o[1] / nn) / den;
+      sd += (o[2] / nn) / den;
+    }
+    osi_s[ty] = so / (float)B;
+    dsi_s[ty] = sd / (float)B;
+    const float dl_osi = cost * tg.count[ty] * 2.f * (osi_s[ty] - tg.osi[ty]) / csum / (float)B;
+    const float dl_dsi = cost * tg.count[ty] * 2.f * (dsi_s[ty] - tg.dsi[ty]) / csum / (float)B;
+    for (int b = 0; b < B; ++b) {
+      const float* o = seg + ((int64_t)b * tg.n + ty) * 3;
+      const float mean = o[0] / nn, den = fmaxf(mean, OSI_MIN_RATE);
+      float* c3 = coef3 + ((int64_t)b * tg.n + ty) * 3;
+      c3[0] = dl_osi / (nn * den);
+      c3[1] = dl_dsi / (nn * den);
+      c3[2] = mean > OSI_MIN_RATE ? -(dl_osi * (o[1] / nn) + dl_dsi * (o[2] / nn)) / (den * den * nn) : 0.f;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f;
+    for (int k = 0; k < tg.n; ++k)
+      a += tg.count[k] * ((osi_s[k] - tg.osi[k]) * (osi_s[k] - tg.osi[k]) + (dsi_s[k] - tg.dsi[k]) * (dsi_s[k] - tg.dsi[k]));
+    atomicAdd(loss_acc, cost * a / csum);
+  }
+}
+
+// coef[b][n] = d loss / d z[b, t, n] for t in the window
+__global__ void __launch_bounds__(256) osi_coef_kernel(int B, int N, float inv_w, const float* __restrict__ normalizer,
+                                                       const float* __restrict__ angle, const float* __restrict__ tuning,
+                                                       const int32_t* __restrict__ type_ids, int n_types,
+                                                       const float* __restrict__ coef3, float* __restrict__ coef) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (n >= N) return;
+  const float* c3 = coef3 + ((int64_t)b * n_types + type_ids[n]) * 3;
+  const float d = (angle[b] - tuning[n]) * (3.14159265358979323846f / 180.f);
+  float g = c3[0] * cosf(2.f * d) + c3[1] * cosf(d) + c3[2];
+  if (normalizer) g = g / fmaxf(normalizer[n], OSI_MIN_RATE);
+  coef[(int64_t)b * N + n] = g * inv_w;
+}
+
+}  // namespace
+
+// *coef_out = [B][N] table of d loss / d z[b, t, n] for t in [*t0_out, *t1_out) (NULL: term off); loss_acc += loss.
+int v1g_osi_dsi_loss(V1GHandle* h, const V1GLossSpec* ls, int B, int T, float* loss_acc, const float** coef_out,
+                     int* t0_out, int* t1_out, cudaStream_t st) {
+  *coef_out = nullptr;
+  const int N = h->cfg.n_neurons, n_types = ls->n_osi_types;
+  if (ls->osi_cost == 0.f || n_types <= 0) return V1G_OK;
+  if (n_types > OSI_MAX_TYPES) return v1g_fail(h, V1G_ERANGE, "more than %d OSI/DSI cell types", OSI_MAX_TYPES);
+  if (!ls->osi_angle || !ls->osi_tuning_angle || !ls->osi_type_ids || !ls->osi_targets || !ls->dsi_targets ||
+      !ls->osi_type_counts)
+    return v1g_fail(h, V1G_EINVAL, "OSI/DSI target: null angle / tuning / types / targets");
+  const int t0 = std::max(ls->osi_pre_delay, 0), t1 = T - std::max(ls->osi_post_delay, 0);
+  if (t1 <= t0) return v1g_fail(h, V1G_EINVAL, "OSI/DSI window [%d, %d) is empty", t0, t1);
+  OsiTargets tg;
+  tg.n = n_types;
+  for (int k = 0; k < n_types; ++k) {  // host arrays
+    tg.osi[k] = ls->osi_targets[k];
+    tg.dsi[k] = ls->dsi_targets[k];
+    tg.count[k] = ls->osi_type_counts[k];
+  }
+  // scratch (4-byte words): cnt[B*N] | coef[B*N] | seg[B*types*3] | coef3[B*types*3] | seg_n[types]
+  const int64_t bn = (int64_t)B * N, bt3 = (int64_t)B * n_types * 3;
+  int rc;
+  if ((rc = v1g_reserve(h, &h->osi_scratch, &h->osi_scratch_cap, 2 * bn + 2 * bt3 + n_types))) return rc;
+  int32_t* cnt = (int32_t*)h->osi_scratch;
+  float* coef = h->osi_scratch + bn;
+  float* seg = coef + bn;
+  float* coef3 = seg + bt3;
+  float* seg_n = coef3 + bt3;
+  V1G_CUDA(h, cudaMemsetAsync(seg, 0, (size_t)(2 * bt3 + n_types) * sizeof(float), st));
+  const dim3 grid((N + 255) / 256, B);
+  const float inv_w = 1.f / (float)(t1 - t0);
+  osi_count_kernel<<<grid, 256, 0, st>>>(h->tape_zr, B, N, t0, t1, cnt);
+  osi_segment_kernel<<<grid, 256, 0, st>>>(cnt, B, N, inv_w, ls->osi_normalizer, ls->osi_angle, ls->osi_tuning_angle,
+                                           ls->osi_type_ids, n_types, seg, seg_n);
+  osi_type_kernel<<<1, OSI_MAX_TYPES, 0, st>>>(seg, seg_n, B, tg, ls->osi_cost * ls->loss_scale, coef3, loss_acc);
+  osi_coef_kernel<<<grid, 256, 0, st>>>(B, N, inv_w, ls->osi_normalizer, ls->osi_angle, ls->osi_tuning_angle,
+                                        ls->osi_type_ids, n_types, coef3, coef);
+  v1g_count_launches(4);
+  V1G_CUDA(h, cudaGetLastError());
+  *coef_out = coef;
+  *t0_out = t0;
+  *t1_out = t1;
+  return V1G_OK;
+}

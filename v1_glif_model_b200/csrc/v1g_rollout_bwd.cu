@@ -59,6 +59,8 @@ struct BwdArgs {
   const float* rate_coef;  // [N] dL/dz contribution of the rate term, or NULL
   int rate_t0, rate_t1;    // steps whose spikes enter the rate term
   V1GSyncTables sync;      // synchrony target over given samples (first == NULL: off)
+  const float* osi_coef;   // [B][N] dL/dz of the OSI/DSI target inside [osi_t0, osi_t1), or NULL
+  int osi_t0, osi_t1;
   const float* sgrad;      // [B][nbins] dL/d(bin count), or NULL
   int sync_bin, nbins;
   float volt_coef;  // voltage_cost * loss_scale / (B*T*N); gradient is 2*volt_coef*(...)
@@ -421,12 +423,13 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     const int bin = (a.sgrad && a.sync_bin > 0 && t / a.sync_bin < a.nbins) ? t / a.sync_bin : -1;
     float* Qw = a.Q + (int64_t)((t + K - 2) % K) * Np * C * QW;
     const bool sync_on = a.sync.first != nullptr && t >= a.sync.t0 && t < a.sync.t0 + a.sync.W;
+    const bool osi_on = a.osi_coef != nullptr && t >= a.osi_t0 && t < a.osi_t1;
     for (int k = tid; k < cn; k += NT) {
       const int n = n0 + k;
       const float k_decay = a.decay[n], k_cf = a.cf[n], k_ad0 = a.asc_decay[2 * n], k_ad1 = a.asc_decay[2 * n + 1];
       const float rc = (a.rate_coef && t >= a.rate_t0 && t < a.rate_t1) ? a.rate_coef[n] : 0.f;
       const float vlo = a.v_lo ? a.v_lo[n] : 0.f;
-      float sadd[BP_];  // synchrony target over given samples: dL/dz[b, t, n]
+      float sadd[BP_];  // synchrony target over given samples and OSI/DSI target: dL/dz[b, t, n]
 #pragma unroll
       for (int b = 0; b < BP_; ++b) sadd[b] = 0.f;
       if (sync_on) {
@@ -437,6 +440,11 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
 #pragma unroll
           for (int b = 0; b < BP_; ++b) sadd[b] += (b == tb) ? gs : 0.f;
         }
+      }
+      if (osi_on) {
+#pragma unroll
+        for (int b = 0; b < BP_; ++b)
+          if (b < B) sadd[b] += a.osi_coef[(int64_t)b * N + n];
       }
       float dyv[BP_][R_];  // dy(t-2) of every batch row of this neuron
 #pragma unroll
@@ -1123,8 +1131,13 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   if (sync_samples)
     if ((rc = v1g_sync_samples_loss(h, &ls, B, T, acc + 3, &sync_tables, st))) return rc;
 
+  const float* osi_coef = nullptr;
+  int osi_t0 = 0, osi_t1 = 0;
+  if ((rc = v1g_osi_dsi_loss(h, &ls, B, T, acc + 3, &osi_coef, &osi_t0, &osi_t1, st))) return rc;
+
   BwdArgs a;
   a.sync = sync_tables;
+  a.osi_coef = osi_coef; a.osi_t0 = osi_t0; a.osi_t1 = osi_t1;
   a.N = N; a.D = D; a.K = K; a.B = B; a.T = T; a.Np = Np;
   a.chunk = plan.chunk; a.chunkP = plan.chunkP; a.S = S; a.C = C; a.n_bkg = c.n_bkg;
   a.state_in_smem = state_in_smem;

@@ -262,7 +262,11 @@ class V1Column:
         with ``rate_kappa``, ``rate_pre_delay``, ``rate_post_delay``; and, for the reference's
         synchrony target (``loss_functions.py:983-1044``), ``sync_samples`` = list of
         ``(trial, neuron_ids)`` with ``sync_bin_sizes`` (steps), ``sync_bin_targets`` (measured Fano
-        factors), ``sync_t_start``, ``sync_t_end``."""
+        factors), ``sync_t_start``, ``sync_t_end``; and, for its population OSI/DSI target
+        (``loss_functions.py:1340-1440``), ``osi_cost``, ``osi_angle`` [B] (degrees),
+        ``osi_tuning_angle`` [N], ``osi_type_ids`` [N], ``osi_targets`` / ``dsi_targets`` /
+        ``osi_type_counts`` [types], optional ``osi_normalizer`` [N], ``osi_pre_delay``,
+        ``osi_post_delay``."""
         loss = dict(loss or {})
         spec = _lib.V1GLossSpec(
             rate_target=loss["rate_target"].data_ptr() if loss.get("rate_target") is not None else None,
@@ -312,6 +316,27 @@ class V1Column:
             spec.sync_bin_targets = self._sync_bins_host[1].ctypes.data
             spec.sync_t_start = int(loss.get("sync_t_start", 0) or 0)
             spec.sync_t_end = int(loss.get("sync_t_end", 0) or 0)
+        if loss.get("osi_cost"):
+            dev_f = lambda a: torch.as_tensor(np.asarray(a, dtype=np.float32)).to(self.device)
+            key = (id(loss["osi_tuning_angle"]), id(loss["osi_type_ids"]), id(loss.get("osi_normalizer")))
+            if getattr(self, "_osi_key", None) != key:
+                self._osi_dev = (dev_f(loss["osi_tuning_angle"]),
+                                 torch.as_tensor(np.asarray(loss["osi_type_ids"], dtype=np.int32)).to(self.device),
+                                 dev_f(loss["osi_normalizer"]) if loss.get("osi_normalizer") is not None else None)
+                self._osi_key = key
+            tuning, types, norm = self._osi_dev
+            self._osi_angle_dev = dev_f(loss["osi_angle"])
+            self._osi_host = tuple(np.ascontiguousarray(loss[k], dtype=np.float32)
+                                   for k in ("osi_targets", "dsi_targets", "osi_type_counts"))
+            spec.osi_cost = float(loss["osi_cost"])
+            spec.n_osi_types = len(self._osi_host[0])
+            spec.osi_angle = self._osi_angle_dev.data_ptr()
+            spec.osi_tuning_angle = tuning.data_ptr()
+            spec.osi_type_ids = types.data_ptr()
+            spec.osi_normalizer = norm.data_ptr() if norm is not None else None
+            spec.osi_targets, spec.dsi_targets, spec.osi_type_counts = (a.ctypes.data for a in self._osi_host)
+            spec.osi_pre_delay = int(loss.get("osi_pre_delay", 0) or 0)
+            spec.osi_post_delay = int(loss.get("osi_post_delay", 0) or 0)
         return spec
 
     def backward_internal(self, loss, grads_flat, losses=None):
