@@ -88,7 +88,10 @@ typedef struct V1GState {
  *              quantile-Huber penalty (kappa = rate_kappa, 0 -> 0.002), summed over populations,
  *              divided by the neurons covered and multiplied by rate_cost.  Neurons with equal
  *              rates keep their listed order (the reference orders them at random).
- *   voltage  : voltage_cost * mean_{b,t,n} (relu(v-1)^2 + relu(v_lo[n]-v)^2)
+ *   voltage  : voltage_cost * mean_{b,t,n} (relu(v-1)^2 + relu(v_lo[n]-v)^2); with v_lo == NULL
+ *              (lower bound 0) this is the reference's "range" penalty relu(|v-.5|-.5)^2, with
+ *              voltage_mode == 1 its "threshold" penalty (v-1)^2 (VoltageRegularization,
+ *              loss_functions.py:1047-1119)
  *   synchrony: with n_sync_samples == 0 the form of BASELINE configuration 4,
  *                sync_cost * (mean_b Fano_b - fano_target)^2, Fano_b = var/mean over bins of the
  *                population spike count in bins of sync_bin steps (loss_functions.py:964-981);
@@ -146,6 +149,7 @@ typedef struct V1GLossSpec {
   const float* dsi_targets;        /* [n_osi_types] HOST */
   const float* osi_type_counts;    /* [n_osi_types] HOST, the weights "cell_type_count" */
   int32_t osi_pre_delay, osi_post_delay;
+  int32_t voltage_mode; /* 0: range (above), 1: threshold, voltage_cost * mean (v - 1)^2 */
 } V1GLossSpec;
 
 /* Event counters of the last rollout (for the roofline's algorithmic bytes). */

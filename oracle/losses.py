@@ -18,9 +18,14 @@ def rate_loss(z, target, cost, loss_scale=1.0):
     return cost * loss_scale * torch.mean((m - target) ** 2)
 
 
-def voltage_loss(v, v_lo, cost, loss_scale=1.0):
-    """``cost * mean(relu(v - 1)^2 + relu(v_lo - v)^2)`` in scaled voltage units."""
-    pen = torch.relu(v - 1.0) ** 2 + torch.relu(v_lo - v) ** 2
+def voltage_loss(v, v_lo, cost, loss_scale=1.0, mode="range"):
+    """``cost * mean(relu(v - 1)^2 + relu(v_lo - v)^2)`` in scaled voltage units; with ``v_lo = 0``
+    this is the reference's "range" penalty ``relu(|v - .5| - .5)^2`` and ``mode="threshold"`` is its
+    ``(v - 1)^2`` (``VoltageRegularization``, ``loss_functions.py:1087-1119``)."""
+    if mode == "threshold":
+        pen = (v - 1.0) ** 2
+    else:
+        pen = torch.relu(v - 1.0) ** 2 + torch.relu(v_lo - v) ** 2
     return cost * loss_scale * pen.mean()
 
 

@@ -223,6 +223,28 @@ def test_bptt_with_synchrony_samples_target(t_start, t_end):
         assert rel_err(got, w) <= TOL_GRAD
 
 
+@pytest.mark.parametrize("mode", ["range", "threshold"])
+def test_bptt_with_reference_voltage_penalties(mode):
+    """The two penalties of the reference's ``VoltageRegularization`` (``loss_functions.py:1087-1119``):
+    "range" = relu(|v - .5| - .5)^2 (lower bound 0, no ``v_lo``) and "threshold" = (v - 1)^2."""
+    cfg, dicts, orc, cell = _cells("small", **KW)
+    x, c = make_inputs(cfg)
+    z, v, _ = orc.rollout(torch.from_numpy(x), torch.from_numpy(c).long())
+    cost = 1e-2
+    if mode == "range":
+        total = cost * torch.relu((v - 0.5).abs() - 0.5).pow(2).mean()
+    else:
+        total = cost * (v - 1.0).pow(2).mean()
+    total.backward()
+    want = [orc.recurrent_weight_values.grad, orc.input_weight_values.grad, orc.bkg_input_weights.grad]
+    cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), save_for_bwd=True)
+    grads = cell.backward(dict(voltage_cost=cost, voltage_mode=mode))
+    cell.synchronize()
+    assert abs(float(grads[3][0]) - total.item()) <= 1e-4 * abs(total.item())
+    for got, w in zip(grads[:3], want):
+        assert rel_err(got, w) <= TOL_GRAD
+
+
 @pytest.mark.parametrize("with_normalizer", [False, True])
 def test_bptt_with_osi_dsi_target(with_normalizer):
     """The reference's population OSI/DSI target (``OrientationSelectivityLoss``, crowd method,

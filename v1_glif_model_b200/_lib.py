@@ -46,7 +46,8 @@ class V1GLossSpec(C.Structure):
                 ("osi_tuning_angle", C.c_void_p), ("osi_type_ids", C.c_void_p),
                 ("osi_normalizer", C.c_void_p), ("osi_targets", C.c_void_p),
                 ("dsi_targets", C.c_void_p), ("osi_type_counts", C.c_void_p),
-                ("osi_pre_delay", C.c_int32), ("osi_post_delay", C.c_int32)]
+                ("osi_pre_delay", C.c_int32), ("osi_post_delay", C.c_int32),
+                ("voltage_mode", C.c_int32)]
 
 
 class V1GCounters(C.Structure):

@@ -64,6 +64,7 @@ struct BwdArgs {
   const float* sgrad;      // [B][nbins] dL/d(bin count), or NULL
   int sync_bin, nbins;
   float volt_coef;  // voltage_cost * loss_scale / (B*T*N); gradient is 2*volt_coef*(...)
+  int volt_threshold_mode;
   const float* v_lo;
   const float *g_z, *g_v;  // explicit [B,T,N] gradients, nullable
   // outputs (accumulated)
@@ -462,7 +463,9 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           gz += a.rec_factor * gzC[si];
           float gv = G_v[si] + (a.g_v ? a.g_v[oi] : 0.f);
           if (a.volt_coef != 0.f) {
-            const float hi = fmaxf(v - 1.f, 0.f), lo = fmaxf(vlo - v, 0.f);
+            // range mode: outside [vlo, 1]; threshold mode: distance from the threshold
+            const float hi = a.volt_threshold_mode ? v - 1.f : fmaxf(v - 1.f, 0.f);
+            const float lo = a.volt_threshold_mode ? 0.f : fmaxf(vlo - v, 0.f);
             gv += 2.f * a.volt_coef * (hi - lo);
             volt_loss += hi * hi + lo * lo;
           }
@@ -1172,6 +1175,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   a.sgrad = want_sync ? sgrad : nullptr;
   a.sync_bin = ls.sync_bin; a.nbins = nbins;
   a.volt_coef = ls.voltage_cost * ls.loss_scale / ((float)B * (float)T * (float)N);
+  a.volt_threshold_mode = ls.voltage_mode == 1 ? 1 : 0;
   a.v_lo = ls.v_lo;
   a.g_z = g_z; a.g_v = g_v;
   a.dw_rec = dw_int[V1G_SRC_REC]; a.dw_lgn = dw_int[V1G_SRC_LGN]; a.dw_bkg = dw_int[V1G_SRC_BKG];

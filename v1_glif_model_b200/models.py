@@ -257,7 +257,7 @@ class V1Column:
     def _loss_spec(self, loss):
         """``V1GLossSpec`` from a dict with any of ``rate_target`` (tensor [N], spikes/step),
         ``v_lo`` (tensor [N]), ``rate_cost``, ``voltage_cost``, ``sync_cost``, ``fano_target``,
-        ``sync_bin``, ``loss_scale`` and, for the reference's rate-distribution target
+        ``sync_bin``, ``loss_scale``, ``voltage_mode`` ("range" or "threshold") and, for the reference's rate-distribution target
         (``loss_functions.py:782-889``), ``rate_groups`` = list of ``(neuron_ids, sorted_targets)``
         with ``rate_kappa``, ``rate_pre_delay``, ``rate_post_delay``; and, for the reference's
         synchrony target (``loss_functions.py:983-1044``), ``sync_samples`` = list of
@@ -274,6 +274,7 @@ class V1Column:
             rate_cost=loss.get("rate_cost", 0.0), voltage_cost=loss.get("voltage_cost", 0.0),
             sync_cost=loss.get("sync_cost", 0.0), fano_target=loss.get("fano_target", 1.0),
             sync_bin=int(loss.get("sync_bin", 50)), loss_scale=loss.get("loss_scale", 1.0))
+        spec.voltage_mode = 1 if loss.get("voltage_mode") == "threshold" else 0
         groups = loss.get("rate_groups")
         if groups:
             key = id(groups)
