@@ -4,7 +4,7 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 A "step" is one data-parallel training step of the 66,634-neuron synthetic column
-(BASELINE configuration 4): forward rollout of T=500 ms at batch 5 per GPU, BPTT with the rate +
+(benchmark configuration 4): forward rollout of T=500 ms at batch 5 per GPU, BPTT with the rate +
 voltage + synchrony losses, one NCCL all-reduce of the flat fp32 weight-gradient buffer, an
 Exp-Adam update of the recurrent and LGN weights.  ``value`` is simulated neuron-steps/s of that
 whole step over all ranks with the inputs already on the device; ``e2e`` repeats it with the

@@ -78,7 +78,7 @@ typedef struct V1GState {
 } V1GState;
 
 /* In-kernel loss specification of the training rollout.
- *   rate     : with n_rate_groups == 0 the form of BASELINE configurations 2 and 4,
+ *   rate     : with n_rate_groups == 0 the simplified form of the benchmark configurations,
  *                rate_cost * mean_n (mean_{b,t} z[b,t,n] - target[n])^2, target in spikes/step;
  *              with n_rate_groups > 0 the reference's own firing-rate target
  *              (SpikeRateDistributionTarget.__call__, loss_functions.py:873-889, with
@@ -92,7 +92,7 @@ typedef struct V1GState {
  *              (lower bound 0) this is the reference's "range" penalty relu(|v-.5|-.5)^2, with
  *              voltage_mode == 1 its "threshold" penalty (v-1)^2 (VoltageRegularization,
  *              loss_functions.py:1047-1119)
- *   synchrony: with n_sync_samples == 0 the form of BASELINE configuration 4,
+ *   synchrony: with n_sync_samples == 0 the simplified form of the benchmark configuration,
  *                sync_cost * (mean_b Fano_b - fano_target)^2, Fano_b = var/mean over bins of the
  *                population spike count in bins of sync_bin steps (loss_functions.py:964-981);
  *              with n_sync_samples > 0 the reference's own target (SynchronizationLoss.__call__,

@@ -53,7 +53,7 @@ def load_reference_losses(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("V1_GLIF_REFERENCE", "V1_GLIF_model")
     lf = load_reference_losses(ref_root)
     cfg = synth.CONFIGS["small"]
     net, _, _ = synth.make_network(cfg, 3)
@@ -154,7 +154,7 @@ def osi_fixture(ref_root):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("V1_GLIF_REFERENCE", "V1_GLIF_model")
     main()
     sync_fixture(root)
     osi_fixture(root)

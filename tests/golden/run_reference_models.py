@@ -101,7 +101,7 @@ def run_case(models, name, config, seed, hard_reset, batch=None, seq_len=None, s
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("V1_GLIF_REFERENCE", "V1_GLIF_model")
     models = load_reference_models(ref_root)
     for name, spec in CASES.items():
         run_case(models, name, **spec)
