@@ -144,7 +144,6 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   cudaFree(h->dev_status);
   cudaFree(h->counters);
   cudaFree(h->tape_v);
-  cudaFree(h->tape_zr);
   cudaFree(h->tape_hist0);
   cudaFree(h->dy_ring);
   cudaFree(h->loss_scratch);

@@ -93,7 +93,6 @@ struct V1GHandle {
   unsigned long long* counters = nullptr;  // V1GCounters on the device
   // saved forward for BPTT
   float* tape_v = nullptr;    // [T][B][N]
-  uint8_t* tape_zr = nullptr;  // [T][B][N] bit0 spike, bit1 refractory
   int64_t tape_cap = 0;
   uint8_t* tape_hist0 = nullptr;  // [B][N] spike-history bits of the initial z_buf of the saved rollout
   int64_t tape_hist0_cap = 0;

@@ -19,8 +19,10 @@
 
 namespace {
 
+// The saved rollout is one word per (step, batch row, neuron): the voltage with its two lowest mantissa
+// bits replaced by (spiked, refractory).
 // count[n] = spikes of neuron n over all batch rows and the steps [t0, t1) of the saved rollout
-__global__ void __launch_bounds__(256) window_count_kernel(const uint8_t* __restrict__ zr, int B, int N,
+__global__ void __launch_bounds__(256) window_count_kernel(const uint32_t* __restrict__ zr, int B, int N,
                                                            int t0, int t1, int32_t* __restrict__ count) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= N) return;
@@ -105,7 +107,7 @@ int v1g_rate_distribution_loss(V1GHandle* h, const V1GLossSpec* ls, const int32_
   unsigned long long* keys_out = keys_in + M;
   void* cub_tmp = keys_out + M;
   if (!count || t0 != 0 || t1 != T) {
-    window_count_kernel<<<(N + 255) / 256, 256, 0, st>>>(h->tape_zr, B, N, t0, t1, cnt);
+    window_count_kernel<<<(N + 255) / 256, 256, 0, st>>>((const uint32_t*)h->tape_v, B, N, t0, t1, cnt);
     v1g_count_launches(1);
     count = cnt;
   }
@@ -162,7 +164,7 @@ __global__ void __launch_bounds__(256) sync_members_kernel(const int32_t* __rest
 }
 
 // pop[s][t - t0] = spikes of the sample's neurons in its trial at step t
-__global__ void __launch_bounds__(256) sync_pop_kernel(const uint8_t* __restrict__ zr, int B, int N,
+__global__ void __launch_bounds__(256) sync_pop_kernel(const uint32_t* __restrict__ zr, int B, int N,
                                                        const int32_t* __restrict__ trial,
                                                        const int32_t* __restrict__ offsets,
                                                        const int32_t* __restrict__ neurons, int t0, int W,
@@ -170,7 +172,7 @@ __global__ void __launch_bounds__(256) sync_pop_kernel(const uint8_t* __restrict
   const int s = blockIdx.x;
   const int b = trial[s], p0 = offsets[s], p1 = offsets[s + 1];
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const uint8_t* row = zr + ((int64_t)(t0 + i) * B + b) * N;
+    const uint32_t* row = zr + ((int64_t)(t0 + i) * B + b) * N;
     int c = 0;
     for (int p = p0; p < p1; ++p) c += row[neurons[p]] & 1;
     pop[(int64_t)s * W + i] = (float)c;
@@ -279,7 +281,7 @@ int v1g_sync_samples_loss(V1GHandle* h, const V1GLossSpec* ls, int B, int T, flo
   V1G_CUDA(h, cudaMemsetAsync(g, 0, (size_t)S * W * sizeof(float), st));
   sync_members_kernel<<<(P + 255) / 256, 256, 0, st>>>(ls->sync_sample_offsets, S, ls->sync_sample_neurons, P,
                                                        first, next, pos_sample);
-  sync_pop_kernel<<<S, 256, 0, st>>>(h->tape_zr, B, N, ls->sync_sample_trial, ls->sync_sample_offsets,
+  sync_pop_kernel<<<S, 256, 0, st>>>((const uint32_t*)h->tape_v, B, N, ls->sync_sample_trial, ls->sync_sample_offsets,
                                      ls->sync_sample_neurons, t0, W, pop);
   const size_t smem = (size_t)W * sizeof(float);
   if (smem > 200 * 1024) return v1g_fail(h, V1G_ERANGE, "synchrony window of %d steps is too long", W);
@@ -314,7 +316,7 @@ namespace {
 constexpr int OSI_MAX_TYPES = 64;
 constexpr float OSI_MIN_RATE = 0.0005f;
 
-__global__ void __launch_bounds__(256) osi_count_kernel(const uint8_t* __restrict__ zr, int B, int N, int t0,
+__global__ void __launch_bounds__(256) osi_count_kernel(const uint32_t* __restrict__ zr, int B, int N, int t0,
                                                         int t1, int32_t* __restrict__ cnt /*[B][N]*/) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   const int b = blockIdx.y;
@@ -444,7 +446,7 @@ int v1g_osi_dsi_loss(V1GHandle* h, const V1GLossSpec* ls, int B, int T, float* l
   V1G_CUDA(h, cudaMemsetAsync(seg, 0, (size_t)(2 * bt3 + n_types) * sizeof(float), st));
   const dim3 grid((N + 255) / 256, B);
   const float inv_w = 1.f / (float)(t1 - t0);
-  osi_count_kernel<<<grid, 256, 0, st>>>(h->tape_zr, B, N, t0, t1, cnt);
+  osi_count_kernel<<<grid, 256, 0, st>>>((const uint32_t*)h->tape_v, B, N, t0, t1, cnt);
   osi_segment_kernel<<<grid, 256, 0, st>>>(cnt, B, N, inv_w, ls->osi_normalizer, ls->osi_angle, ls->osi_tuning_angle,
                                            ls->osi_type_ids, n_types, seg, seg_n);
   osi_type_kernel<<<1, OSI_MAX_TYPES, 0, st>>>(seg, seg_n, B, tg, ls->osi_cost * ls->loss_scale, coef3, loss_acc);

@@ -49,7 +49,6 @@ struct BwdArgs {
   int gauss, hard_reset, csr_evict_first;
   // saved forward
   const float* tape_v;
-  const uint8_t* tape_zr;
   const uint8_t* hist0;  // initial spike-history bits [B][N], or NULL for a zero initial state
   const int32_t* lgn_off;
   const uint4* lgn_ent4;  // {batch row << 24 | unit, first synapse, end, 0} per event
@@ -321,8 +320,9 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         zz[b] = 2u;
         if (b < B && act) {
           const int64_t ti = ((int64_t)ts * B + b) * N + n;
-          vv[b] = __ldcs(a.tape_v + ti);
-          zz[b] = __ldcs(a.tape_zr + ti);
+          const float w = __ldcs(a.tape_v + ti);  // voltage, low two mantissa bits = (spiked, refractory)
+          vv[b] = __uint_as_float(__float_as_uint(w) & ~3u);
+          zz[b] = __float_as_uint(w) & 3u;
         }
       }
       unsigned zm = 0, need = 0;
@@ -1165,7 +1165,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   a.gauss = (c.flags & V1G_FLAG_PSEUDO_GAUSS) ? 1 : 0;
   a.hard_reset = (c.flags & V1G_FLAG_HARD_RESET) ? 1 : 0;
   a.csr_evict_first = h->opt_csr_evict_first;
-  a.tape_v = h->tape_v; a.tape_zr = h->tape_zr;
+  a.tape_v = h->tape_v;
   a.hist0 = h->tape_has_hist0 ? h->tape_hist0 : nullptr;
   a.lgn_off = h->lgn_offsets; a.lgn_ent4 = h->lgn_ent4; a.lgn_nseg = h->lgn_nseg;
   a.bkg_counts = h->tape_counts;

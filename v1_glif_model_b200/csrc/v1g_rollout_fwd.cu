@@ -322,8 +322,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
       if (a.v_out) __stcs(a.v_out + ((int64_t)b * a.T + t) * N + n, nv);
       if (a.tape_v) {
         const int64_t ti = ((int64_t)t * B + b) * N + n;
-        __stcs(a.tape_v + ti, nv);
-        __stcs(a.tape_zr + ti, (uint8_t)((z ? 1 : 0) | (nr > 0 ? 2 : 0)));
+        // the voltage with its two lowest mantissa bits replaced by (spiked, refractory)
+        __stcs(a.tape_v + ti, __uint_as_float((__float_as_uint(nv) & ~3u) | (z ? 1u : 0u) | (nr > 0 ? 2u : 0u)));
       }
       if (z) spk_list[atomicAdd(nspk_p, 1)] = ((uint32_t)b << 24) | (uint32_t)k;
 #pragma unroll
@@ -588,12 +588,9 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
     const int64_t need = (int64_t)T * B * N;
     if (need > h->tape_cap || !h->tape_v) {
       if (h->tape_v) cudaFree(h->tape_v);
-      if (h->tape_zr) cudaFree(h->tape_zr);
       h->tape_v = nullptr;
-      h->tape_zr = nullptr;
       h->tape_cap = 0;
       V1G_CUDA(h, cudaMalloc((void**)&h->tape_v, (size_t)need * sizeof(float)));
-      V1G_CUDA(h, cudaMalloc((void**)&h->tape_zr, (size_t)need));
       h->tape_cap = need;
     }
   }
@@ -641,7 +638,6 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
   a.state_ws = h->state_ws;
   a.z_out = z_out; a.v_out = v_out;
   a.tape_v = save_for_bwd ? h->tape_v : nullptr;
-  a.tape_zr = save_for_bwd ? h->tape_zr : nullptr;
   a.ring = h->ring; a.barrier = h->barrier; a.status = h->dev_status; a.counters = h->counters;
   a.spin_limit = h->opt_spin_limit;
   a.phase_ns = nullptr;

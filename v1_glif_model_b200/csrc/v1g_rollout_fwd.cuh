@@ -40,7 +40,6 @@ struct FwdArgs {
   uint8_t* z_out;
   float* v_out;
   float* tape_v;
-  uint8_t* tape_zr;
   // plumbing
   float* ring;
   unsigned long long* barrier;

@@ -251,8 +251,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
         if (a.v_out) __stcs(a.v_out + oi, nv);
         if (a.tape_v) {
           const int64_t ti = ((int64_t)t * B_ + b) * N + n;
-          __stcs(a.tape_v + ti, nv);
-          __stcs(a.tape_zr + ti, (uint8_t)((z ? 1 : 0) | (nr > 0 ? 2 : 0)));
+          // the voltage with its two lowest mantissa bits replaced by (spiked, refractory)
+          __stcs(a.tape_v + ti, __uint_as_float((__float_as_uint(nv) & ~3u) | (z ? 1u : 0u) | (nr > 0 ? 2u : 0u)));
         }
         if (z) spk_list[atomicAdd(nspk_p, 1)] = ((uint32_t)b << 24) | (uint32_t)tid;
       }
