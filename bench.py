@@ -191,7 +191,7 @@ def workload_config(cfg, n_gpus, t_len):
             "n_neurons": cfg.n_neurons, "batch_per_gpu": cfg.batch, "global_batch": cfg.batch * n_gpus,
             "seq_len": t_len, "n_receptors": cfg.n_receptors, "max_delay": cfg.max_delay,
             "parallelism": f"dp{n_gpus}",
-            "l2": "inputs larger than L2 (saved rollout %.2f GB per step)" % (5e-9 * cfg.batch * cfg.n_neurons * t_len)}
+            "l2": "inputs larger than L2 (saved rollout %.2f GB per step)" % (4e-9 * cfg.batch * cfg.n_neurons * t_len)}
 
 
 # --------------------------------------------------------------------------------------
