@@ -223,6 +223,26 @@ def test_bptt_with_synchrony_samples_target(t_start, t_end):
         assert rel_err(got, w) <= TOL_GRAD
 
 
+@pytest.mark.parametrize("batch", [1, 4, 6, 8])
+def test_rollout_and_bptt_at_every_batch_width(batch):
+    """Batch 1..4 uses 16-byte fp32 rows in the backward ring, 6..8 32-byte rows, 7 and 8 the general
+    forward kernel; spikes must be exact and gradients inside the bar at each width, and a second
+    backward pass over the same saved rollout must give the same recurrent gradient."""
+    cfg, dicts, orc, cell = _cells("small", **KW)
+    x, c = make_inputs(cfg, batch=batch, seq_len=30)
+    zo, lo, go = _oracle_grads(orc, cfg, x, c, cell.voltage_scale, torch.float32)
+    z, _ = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), save_for_bwd=True)
+    assert torch.equal(z.cpu().float(), zo)
+    tgt = torch.from_numpy(synth.make_rate_targets(cfg)).cuda() / 1000.0
+    vlo = torch.from_numpy((-20.0 / cell.voltage_scale).astype(np.float32)).cuda()
+    grads = cell.backward(dict(LOSS, rate_target=tgt, v_lo=vlo))
+    again = cell.backward(dict(LOSS, rate_target=tgt, v_lo=vlo))
+    cell.synchronize()
+    for got, want in zip(grads[:3], go):
+        assert rel_err(got, want) <= TOL_GRAD
+    assert torch.equal(grads[0], again[0])     # recurrent gradient: no atomics, same order
+
+
 @pytest.mark.parametrize("mode", ["range", "threshold"])
 def test_bptt_with_reference_voltage_penalties(mode):
     """The two penalties of the reference's ``VoltageRegularization`` (``loss_functions.py:1087-1119``):
