@@ -266,7 +266,11 @@ int v1g_step_bwd(V1GHandle* h, int32_t batch, const V1GState* g_out, const float
 /* T steps from `state` (updated in place; NULL pointers inside mean zero state and nothing is
  * written back).  x[B,T,n_lgn] uint8 LGN spikes, bkg_counts[B,T,n_bkg] int32 Poisson counts.
  * z_out[B,T,N] uint8 and v_out[B,T,N] float32 are optional.  save_for_bwd != 0 keeps v and the
- * spike/refractory bits of every step inside the handle for v1g_rollout_bwd. */
+ * spike/refractory bits of every step, and a copy of bkg_counts, inside the handle for
+ * v1g_rollout_bwd; x and bkg_counts may be reused once the call has returned.
+ * The call is NOT asynchronous to the host: it waits on `stream` once (cudaStreamSynchronize) to
+ * learn the number of LGN events before it sizes their list, so it cannot be captured in a CUDA
+ * graph, and everything queued on `stream` before it has finished when it returns. */
 int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x,
                     const int32_t* bkg_counts, V1GState* state, uint8_t* z_out, float* v_out,
                     int32_t save_for_bwd, void* stream);

@@ -1,7 +1,7 @@
 """Golden vectors from the reference's OWN cell (run from the repo root, in a container that has
 the reference tree):
 
-    python tests/golden/run_reference_models.py /path/to/V1_GLIF_model
+    python tests/golden/run_reference_models.py /path/to/V1_GLIF_model [fixture names]
 
 Imports ``v1_model_utils/models.py`` unmodified from the reference tree over ``tf_standin`` (a
 torch-backed stand-in for the TensorFlow calls it makes), builds its ``V1Column`` from the seeded
@@ -36,7 +36,10 @@ CASES = {"reference_tiny": dict(config="tiny", seed=0, hard_reset=False),
          # a busier net (hundreds of spikes, refractory periods, all delays in use); the output
          # cotangents are regenerated from g_seed by the test instead of being stored
          "reference_small": dict(config="small", seed=2, hard_reset=False, batch=2, seq_len=40,
-                                 store_cotangents=False)}
+                                 store_cotangents=False),
+         # the Gaussian pseudo-derivative (spike_gauss / gauss_pseudo, models.py:17-21, 36-50, 1106-1107)
+         "reference_small_gauss": dict(config="small", seed=5, hard_reset=False, batch=2, seq_len=30,
+                                       store_cotangents=False, pseudo_gauss=True, gauss_std=0.3)}
 
 
 def load_reference_models(ref_root):
@@ -52,7 +55,8 @@ def load_reference_models(ref_root):
     return mod
 
 
-def run_case(models, name, config, seed, hard_reset, batch=None, seq_len=None, store_cotangents=True):
+def run_case(models, name, config, seed, hard_reset, batch=None, seq_len=None, store_cotangents=True,
+             pseudo_gauss=False, gauss_std=0.5):
     import dataclasses
     cfg = synth.CONFIGS[config]
     cfg = dataclasses.replace(cfg, batch=batch or cfg.batch, seq_len=seq_len or cfg.seq_len)
@@ -69,7 +73,8 @@ def run_case(models, name, config, seed, hard_reset, batch=None, seq_len=None, s
         net = dict(net, data_dir=os.path.join(tmp, "net"))
         os.chdir(tmp)
         try:
-            cell = models.V1Column(net, lgn, bkg, hard_reset=hard_reset, **KW)
+            cell = models.V1Column(net, lgn, bkg, hard_reset=hard_reset, pseudo_gauss=pseudo_gauss,
+                                   gauss_std=gauss_std, **KW)
         finally:
             os.chdir(cwd)
     state = cell.zero_state(cfg.batch)
@@ -87,7 +92,8 @@ def run_case(models, name, config, seed, hard_reset, batch=None, seq_len=None, s
     ((z * g_z).sum() + (v * g_v).sum()).backward()
     out = os.path.join(HERE, name + ".npz")
     np.savez_compressed(
-        out, config=config, seed=seed, hard_reset=hard_reset, x=x, bkg_counts=counts,
+        out, config=config, seed=seed, hard_reset=hard_reset, pseudo_gauss=pseudo_gauss, gauss_std=gauss_std,
+        x=x, bkg_counts=counts,
         g_seed=99 + seed, **(dict(g_z=g_z.numpy(), g_v=g_v.numpy()) if store_cotangents else {}), z=z.detach().numpy().astype(np.uint8),
         v=v.detach().numpy(), z_buf=state[0].detach().numpy(), r=state[2].numpy(),
         asc=state[3].detach().numpy(), psc_rise=state[4].detach().numpy(),
@@ -103,8 +109,10 @@ def run_case(models, name, config, seed, hard_reset, batch=None, seq_len=None, s
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("V1_GLIF_REFERENCE", "V1_GLIF_model")
     models = load_reference_models(ref_root)
+    only = sys.argv[2:]
     for name, spec in CASES.items():
-        run_case(models, name, **spec)
+        if not only or name in only:
+            run_case(models, name, **spec)
 
 
 if __name__ == "__main__":

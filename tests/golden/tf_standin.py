@@ -86,7 +86,51 @@ def _variable(value, trainable=True, dtype=None, name=None, constraint=None, **k
     t.trainable = bool(trainable)
     t.constraint = constraint
     t.read_value = lambda: t
+
+    def _assign(value):
+        t.data.copy_(_t(value).detach().to(t.dtype))
+        return t
+
+    def _assign_add(value):
+        t.data.add_(_t(value).detach().to(t.dtype))
+        return t
+    t.assign = _assign
+    t.assign_add = _assign_add
     return t
+
+
+class _Optimizer:
+    """The part of ``tf.keras.optimizers.Optimizer`` that the reference's ``ExponentiatedAdam``
+    relies on: slot variables, the iteration counter and the variable -> slot index table."""
+
+    def __init__(self, name=None, **kw):
+        self.name = name
+        self.iterations = torch.zeros((), dtype=torch.int64)
+        self._index_dict = {}
+
+    def _build_learning_rate(self, learning_rate):
+        return learning_rate
+
+    @property
+    def learning_rate(self):
+        lr = self._learning_rate
+        return lr(self.iterations) if callable(lr) else lr
+
+    def _var_key(self, variable):
+        return id(variable)
+
+    def build(self, var_list):
+        for i, var in enumerate(var_list):
+            self._index_dict[self._var_key(var)] = i
+
+    def add_variable_from_reference(self, model_variable, variable_name, **kw):
+        return _variable(torch.zeros_like(model_variable.detach()), trainable=False)
+
+    def _serialize_hyperparameter(self, h):
+        return h
+
+    def get_config(self):
+        return {"name": self.name}
 
 
 def _gather(params, indices, axis=0, **kw):
@@ -255,6 +299,10 @@ def install():
     tf.exp = torch.exp
     tf.square = torch.square
     tf.sign = torch.sign
+    tf.sqrt = torch.sqrt
+    tf.pow = torch.pow
+    tf.cos = torch.cos
+    tf.IndexedSlices = type("IndexedSlices", (), {})
     tf.reduce_sum = _reduce(torch.sum)
     tf.reduce_mean = _reduce(torch.mean)
     tf.clip_by_value = lambda x, lo, hi: torch.clamp(x, _t(lo).item(), _t(hi).item())
@@ -290,6 +338,9 @@ def install():
     keras.layers = layers
     keras.constraints = types.SimpleNamespace(Constraint=_Constraint)
     keras.regularizers = types.SimpleNamespace(Regularizer=object)
+    keras.optimizers = types.SimpleNamespace(
+        Optimizer=_Optimizer, schedules=types.SimpleNamespace(LearningRateSchedule=object))
+    keras.utils = types.SimpleNamespace(register_keras_serializable=lambda **kw: (lambda cls: cls))
     tf.keras = keras
     sys.modules["tensorflow"] = tf
     sys.modules["tensorflow.keras"] = keras

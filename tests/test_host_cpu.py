@@ -133,3 +133,27 @@ def test_expadam_oracle_properties():
     assert torch.all(w1[:5] == 0)                            # zeros stay zero
     up = (g < 0) & (w > 0)
     assert torch.all(w1[up] > w[up])                         # negative gradient grows |w|
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-13), (torch.float32, 2e-6)])
+def test_oracle_scatter_transpose_equals_sparse_matmul(dtype, tol):
+    """The oracle's optional scatter form of the spike-gradient product (used by the full-length
+    parity runs at the benchmark shapes) gives the gradients of the reference-shaped form, which
+    builds one sparse tensor per receptor channel and step (``models.py:187-202``)."""
+    from util import make_case, make_inputs, rel_err
+    kw = dict(dampening_factor=0.5, pseudo_width=0.5, recurrent_dampening_factor=0.3,
+              voltage_gradient_dampening=0.4, dtype=dtype)
+    grads = []
+    for scatter in (False, True):
+        cfg, dicts, orc = make_case("small", scatter_transpose=scatter, **kw)
+        x, c = make_inputs(cfg, seq_len=25)
+        z, v, _ = orc.rollout(torch.from_numpy(x), torch.from_numpy(c).long())
+        g = torch.Generator().manual_seed(3)
+        g_z = torch.randn(z.shape, generator=g, dtype=torch.float64).to(dtype) * 1e-2
+        g_v = torch.randn(v.shape, generator=g, dtype=torch.float64).to(dtype) * 1e-3
+        ((z * g_z).sum() + (v * g_v).sum()).backward()
+        grads.append([w.grad.clone() for w in (orc.recurrent_weight_values, orc.input_weight_values,
+                                               orc.bkg_input_weights)])
+    for a, b in zip(*grads):
+        assert float(b.abs().max()) > 0
+        assert rel_err(a, b) <= tol

@@ -14,7 +14,7 @@ import torch
 from util import TOL_GRAD, TOL_STATE, make_case, rel_err
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-CASES = ["reference_tiny", "reference_tiny_hard_reset", "reference_small"]
+CASES = ["reference_tiny", "reference_tiny_hard_reset", "reference_small", "reference_small_gauss"]
 
 
 def _load(name):
@@ -23,6 +23,8 @@ def _load(name):
               recurrent_dampening_factor=float(g["kw_recurrent_dampening_factor"]),
               voltage_gradient_dampening=float(g["kw_voltage_gradient_dampening"]),
               hard_reset=bool(g["hard_reset"]))
+    if "pseudo_gauss" in g.files and bool(g["pseudo_gauss"]):
+        kw.update(pseudo_gauss=True, gauss_std=float(g["gauss_std"]))
     return g, kw
 
 
@@ -134,3 +136,46 @@ def test_oracle_orientation_selectivity_loss_equals_reference_loss_code(tag):
     want = float(f["loss_" + tag])
     assert abs(loss.item() - want) <= 1e-12 * abs(want)
     assert rel_err(z.grad, torch.from_numpy(f["grad_z_" + tag])) <= 1e-11
+
+
+def _expadam_fixture():
+    return np.load(os.path.join(ROOT, "tests", "golden", "reference_expadam.npz"))
+
+
+def test_oracle_expadam_equals_reference_optimizer_code():
+    """``oracle/expadam.py`` against weights and moments that the reference's
+    ``ExponentiatedAdam.update_step`` (dense branch) followed by its ``SignedConstraint`` produced over
+    four steps in float32 (tests/golden/run_reference_optimizer.py)."""
+    from oracle.expadam import expadam_step
+    f = _expadam_fixture()
+    w, pos = torch.from_numpy(f["w0"]), torch.from_numpy(f["positive"])
+    m, v = torch.zeros_like(w), torch.zeros_like(w)
+    for k in range(f["grads"].shape[0]):
+        w, m, v = expadam_step(w, torch.from_numpy(f["grads"][k]), m, v, pos, float(f["lr"]),
+                               float(f["beta_1"]), float(f["beta_2"]), float(f["epsilon"]), k + 1)
+        assert rel_err(m, f["m"][k]) <= 1e-7 and rel_err(v, f["v"][k]) <= 1e-7
+        assert rel_err(w, f["w"][k]) <= 1e-7
+        assert np.array_equal(w.numpy() == 0, f["w"][k] == 0)       # zeros stay zeros, nothing else becomes one
+
+
+@pytest.mark.gpu
+def test_cuda_expadam_equals_reference_optimizer_code():
+    """The Exp-Adam kernel against the same reference-generated fixture, through the C ABI."""
+    import ctypes as C
+    from v1_glif_model_b200 import _lib
+    f = _expadam_fixture()
+    lib = _lib.load()
+    w = torch.from_numpy(f["w0"]).cuda()
+    pos = torch.from_numpy(f["positive"].astype(np.uint8)).cuda()
+    m, v = torch.zeros_like(w), torch.zeros_like(w)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for k in range(f["grads"].shape[0]):
+        g = torch.from_numpy(f["grads"][k]).cuda()
+        rc = lib.v1g_expadam_update(w.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), pos.data_ptr(),
+                                    w.numel(), float(f["lr"]), float(f["beta_1"]), float(f["beta_2"]),
+                                    float(f["epsilon"]), k + 1, 1.0, stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert rel_err(m, f["m"][k]) <= 1e-6 and rel_err(v, f["v"][k]) <= 1e-6
+        assert rel_err(w, f["w"][k]) <= 1e-6
+        assert np.array_equal(w.cpu().numpy() == 0, f["w"][k] == 0)

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from util import TOL_GRAD, TOL_STATE, make_case, make_inputs, rel_err
+from util import TOL_GRAD, TOL_STATE, first_spike_divergence, make_case, make_inputs, rel_err
 from v1_glif_model_b200 import synth
 
 pytestmark = pytest.mark.gpu
@@ -33,10 +33,13 @@ def _compare_rollout(cfg, orc, cell, x, c):
     state = cell.zero_state(x.shape[0])
     z, v = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), state=state)
     cell.synchronize()
-    # spikes are compared exactly; a borderline threshold crossing that flips under a different
-    # summation order of the currents would show here as a first divergence step
-    diff = (z.cpu().float() != zo).nonzero()
-    assert diff.numel() == 0, f"first spike divergence at (b,t,n)={diff[0].tolist()}"
+    # spikes are compared exactly; a divergence is accepted only as a proven threshold tie (the
+    # oracle's voltage within a few float steps of 1 at the first differing entries), in which case
+    # everything before that step is compared and the rest is not comparable
+    t_tie = first_spike_divergence(z, zo, vo)
+    if t_tie is not None:
+        assert t_tie >= 1 and rel_err(v[:, :t_tie], vo[:, :t_tie]) <= TOL_STATE
+        pytest.skip(f"threshold tie at step {t_tie}: compared up to it")
     assert rel_err(v, vo) <= TOL_STATE
     for got, want in zip(state[:6], so[:6]):
         assert rel_err(got.float(), want.float()) <= TOL_STATE
@@ -221,6 +224,22 @@ def test_bptt_with_synchrony_samples_target(t_start, t_end):
     assert abs(float(grads[3][0]) - total.item()) <= 1e-4 * abs(total.item())
     for got, w in zip(grads[:3], want):
         assert rel_err(got, w) <= TOL_GRAD
+
+
+def test_synchrony_samples_are_taken_from_every_call():
+    """The reference redraws the synchrony samples in every call; two calls with freshly built lists
+    (which CPython may well give the same address) must each use their own list."""
+    cfg, dicts, orc, cell = _cells("small", **KW)
+    x, c = make_inputs(cfg)
+    cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), save_for_bwd=True)
+    losses = []
+    for seed in (1, 2, 1):
+        samples, bins, targets = synth.make_sync_samples(cfg, dicts[0], cfg.batch, n_samples=12, seed=seed)
+        spec = dict(sync_cost=0.05, sync_samples=list(samples), sync_bin_sizes=bins, sync_bin_targets=targets)
+        losses.append(float(cell.backward(spec)[3][0]))
+        del samples, spec
+    cell.synchronize()
+    assert losses[0] != losses[1] and losses[0] == losses[2]
 
 
 @pytest.mark.parametrize("batch", [1, 4, 6, 8])

@@ -145,6 +145,7 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   cudaFree(h->counters);
   cudaFree(h->tape_v);
   cudaFree(h->tape_hist0);
+  cudaFree(h->tape_counts_buf);
   cudaFree(h->dy_ring);
   cudaFree(h->loss_scratch);
   cudaFree(h->stage_x);

@@ -103,7 +103,9 @@ struct V1GHandle {
   // (all batch rows and steps) followed by [T*B] population spikes per (step, batch row)
   int32_t* tape_stats = nullptr;
   int64_t tape_stats_cap = 0;
-  const int32_t* tape_counts = nullptr;  // caller's bkg counts of the saved rollout
+  const int32_t* tape_counts = nullptr;  // background counts of the saved rollout (= tape_counts_buf)
+  int32_t* tape_counts_buf = nullptr;    // handle-owned copy [B][T][n_bkg]
+  int64_t tape_counts_cap = 0;
   // backward scratch
   float* dy_ring = nullptr;
   int64_t dy_ring_cap = 0;

@@ -670,10 +670,16 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
   }
   if (rc) return rc;
   if (save_for_bwd) {
+    // the backward pass needs the counts again; keep a copy so that the caller's buffer may be
+    // reused as soon as this call has been queued
+    const int64_t nc = (int64_t)B * T * c.n_bkg;
+    if ((rc = v1g_reserve(h, &h->tape_counts_buf, &h->tape_counts_cap, nc))) return rc;
+    V1G_CUDA(h, cudaMemcpyAsync(h->tape_counts_buf, bkg_counts, (size_t)nc * sizeof(int32_t),
+                                cudaMemcpyDeviceToDevice, st));
     h->tape_valid = true;
     h->tape_B = B;
     h->tape_T = T;
-    h->tape_counts = bkg_counts;
+    h->tape_counts = h->tape_counts_buf;
   }
   return V1G_OK;
 }

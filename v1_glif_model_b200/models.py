@@ -23,6 +23,7 @@ There is no CPU path: without a CUDA device or without the built library every e
 from __future__ import annotations
 
 import ctypes as C
+import zlib
 
 import numpy as np
 import torch
@@ -276,14 +277,16 @@ class V1Column:
             sync_bin=int(loss.get("sync_bin", 50)), loss_scale=loss.get("loss_scale", 1.0))
         spec.voltage_mode = 1 if loss.get("voltage_mode") == "threshold" else 0
         groups = loss.get("rate_groups")
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
         if groups:
-            key = id(groups)
+            # constant over a training run, so the device copy is cached; the key is the CONTENT
+            # (an object's id can be reused by a new list once the old one is freed)
+            sizes = [len(g[0]) for g in groups]
+            offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int32)
+            ids = np.concatenate([np.asarray(g[0], dtype=np.int32) for g in groups])
+            tgt = np.concatenate([np.asarray(g[1], dtype=np.float32) for g in groups])
+            key = (tuple(sizes), zlib.crc32(ids.tobytes()), zlib.crc32(tgt.tobytes()))
             if getattr(self, "_rate_groups_key", None) != key:
-                sizes = [len(g[0]) for g in groups]
-                offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int32)
-                ids = np.concatenate([np.asarray(g[0], dtype=np.int32) for g in groups])
-                tgt = np.concatenate([np.asarray(g[1], dtype=np.float32) for g in groups])
-                dev = lambda a: torch.from_numpy(a).to(self.device)
                 self._rate_groups_dev = (dev(offs), dev(ids), dev(tgt), len(sizes), int(offs[-1]))
                 self._rate_groups_key = key
             offs, ids, tgt, ng, nn = self._rate_groups_dev
@@ -296,15 +299,13 @@ class V1Column:
             spec.rate_post_delay = int(loss.get("rate_post_delay", 0) or 0)
         samples = loss.get("sync_samples")
         if samples:
-            key = id(samples)
-            if getattr(self, "_sync_samples_key", None) != key:
-                sizes = [len(smp[1]) for smp in samples]
-                offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int32)
-                trial = np.asarray([smp[0] for smp in samples], dtype=np.int32)
-                ids = np.concatenate([np.asarray(smp[1], dtype=np.int32) for smp in samples])
-                dev = lambda a: torch.from_numpy(a).to(self.device)
-                self._sync_samples_dev = (dev(trial), dev(offs), dev(ids), len(sizes), int(offs[-1]))
-                self._sync_samples_key = key
+            # the reference redraws the samples in every call (loss_functions.py:997-1024), so they are
+            # uploaded on every call (a few KB); the tensors are kept alive until the next call
+            sizes = [len(smp[1]) for smp in samples]
+            offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int32)
+            trial = np.asarray([smp[0] for smp in samples], dtype=np.int32)
+            ids = np.concatenate([np.asarray(smp[1], dtype=np.int32) for smp in samples])
+            self._sync_samples_dev = (dev(trial), dev(offs), dev(ids), len(sizes), int(offs[-1]))
             trial, offs, ids, ns, nm = self._sync_samples_dev
             self._sync_bins_host = (np.ascontiguousarray(loss["sync_bin_sizes"], dtype=np.int32),
                                     np.ascontiguousarray(loss["sync_bin_targets"], dtype=np.float32))
@@ -319,11 +320,14 @@ class V1Column:
             spec.sync_t_end = int(loss.get("sync_t_end", 0) or 0)
         if loss.get("osi_cost"):
             dev_f = lambda a: torch.as_tensor(np.asarray(a, dtype=np.float32)).to(self.device)
-            key = (id(loss["osi_tuning_angle"]), id(loss["osi_type_ids"]), id(loss.get("osi_normalizer")))
+            tuning_h = np.ascontiguousarray(loss["osi_tuning_angle"], dtype=np.float32)
+            types_h = np.ascontiguousarray(loss["osi_type_ids"], dtype=np.int32)
+            norm_h = (np.ascontiguousarray(loss["osi_normalizer"], dtype=np.float32)
+                      if loss.get("osi_normalizer") is not None else None)
+            key = (zlib.crc32(tuning_h.tobytes()), zlib.crc32(types_h.tobytes()),
+                   zlib.crc32(norm_h.tobytes()) if norm_h is not None else None)
             if getattr(self, "_osi_key", None) != key:
-                self._osi_dev = (dev_f(loss["osi_tuning_angle"]),
-                                 torch.as_tensor(np.asarray(loss["osi_type_ids"], dtype=np.int32)).to(self.device),
-                                 dev_f(loss["osi_normalizer"]) if loss.get("osi_normalizer") is not None else None)
+                self._osi_dev = (dev(tuning_h), dev(types_h), dev(norm_h) if norm_h is not None else None)
                 self._osi_key = key
             tuning, types, norm = self._osi_dev
             self._osi_angle_dev = dev_f(loss["osi_angle"])

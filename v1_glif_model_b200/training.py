@@ -119,6 +119,9 @@ class Trainer:
         if self.order == "internal":
             cell = self.cell
             losses = cell.backward_internal(self.loss, self.grads.flat, self._losses)
+            # a rollout kernel whose bounded grid-barrier wait gave up leaves garbage behind: raise
+            # here (V1GError, code ETIMEOUT) before the gradients reach the other replicas or the weights
+            cell.synchronize()
             self.grads.all_reduce(self.group)
             self.iterations += 1
             cell._check(cell._lib.v1g_expadam_update_internal(
@@ -127,6 +130,7 @@ class Trainer:
                 C.c_void_p(torch.cuda.current_stream().cuda_stream)))
             return losses
         _, _, _, losses = self.cell.backward(self.loss, accumulate_into=self.grads.views)
+        self.cell.synchronize()                  # as above: no update from an aborted rollout
         self.grads.all_reduce(self.group)
         self.opt.apply_gradients([self.grads.views[i] for i in self._sel])
         self.cell.refresh_weights()
