@@ -65,6 +65,7 @@ typedef struct V1GConfig {
   float gauss_std;
   float pseudo_width; /* support half-width of the triangular pseudo-derivative; reference = 1 */
   float lr_scale;     /* models.py:1097 */
+  float bkg_firing_rate; /* Hz; Poisson rate per step = bkg_firing_rate * 0.001 (models.py:741) */
 } V1GConfig;
 
 /* Cell state, reference layouts and dtypes (models.py:1030-1056).  r is int8. */
@@ -75,6 +76,7 @@ typedef struct V1GState {
   float* asc;      /* [B, N*2] */
   float* psc_rise; /* [B, N*R] */
   float* psc;      /* [B, N*R] */
+  int32_t* noise_step; /* [B] step counter of the background sampler (models.py:1042, 1133), may be NULL */
 } V1GState;
 
 /* In-kernel loss specification of the training rollout.
@@ -208,6 +210,29 @@ int v1g_set_neuron_params(V1GHandle* h, const float* decay, const float* current
  * (models.py:663-682, 966-976). */
 int v1g_set_weights(V1GHandle* h, int source, const float* w, void* stream);
 
+/* ---- stochastic inputs on the device -------------------------------------------------------
+ * The reference draws the background counts inside the cell with tf.random.stateless_poisson keyed
+ * by [noise_seed + replica_id * 1000003, noise_step[0]] (models.py:865-887) and the LGN spikes in its
+ * data pipeline as uniform < 1 - exp(-rate / 1000) (stim_dataset.py:182-193).  These entry points do
+ * the same with a Philox-4x32-10 generator evaluated as a function of (seed, replica, step, trial,
+ * node): equal arguments give equal draws in every call, chunking and replay.  TensorFlow's own
+ * random streams are not reproduced. */
+
+/* noise_seed of the cell (models.py:506; advanced once per rollout by the training loop,
+ * tf_utils.py:235-237) and the replica id that offsets it (models.py:869-877). */
+int v1g_set_noise_seed(V1GHandle* h, int64_t noise_seed, int32_t replica_id);
+
+/* counts_out[B, T, n_bkg] int32 ~ Poisson(bkg_firing_rate * 0.001 * dt) for the steps
+ * first_step .. first_step + T - 1 (the values of noise_step[0]).  Rates above 8 per step:
+ * V1G_ERANGE. */
+int v1g_sample_bkg_counts(V1GHandle* h, int32_t batch, int32_t n_steps, int32_t first_step,
+                          int32_t* counts_out, void* stream);
+
+/* x_out[B, T, n_lgn] uint8 = uniform < 1 - exp(-rates / 1000); rates[T, n_lgn] in Hz, one table for
+ * all trials (rates_batch_stride = 0) or one per trial (stride in elements between trials). */
+int v1g_sample_lgn_spikes(V1GHandle* h, int32_t batch, int32_t n_steps, const float* rates,
+                          int64_t rates_batch_stride, int64_t seed, uint8_t* x_out, void* stream);
+
 /* ---- operator level (one TensorFlow-level callable each) ---------------------------------- */
 
 /* tf.where(x > 0) (models.py:128, 826, 890): row-major coordinates of the positive entries of
@@ -264,7 +289,10 @@ int v1g_step_bwd(V1GHandle* h, int32_t batch, const V1GState* g_out, const float
 /* ---- fused rollout (the Keras RNN loop over V1Column.call, models.py:1317-1322) ----------- */
 
 /* T steps from `state` (updated in place; NULL pointers inside mean zero state and nothing is
- * written back).  x[B,T,n_lgn] uint8 LGN spikes, bkg_counts[B,T,n_bkg] int32 Poisson counts.
+ * written back).  x[B,T,n_lgn] uint8 LGN spikes, bkg_counts[B,T,n_bkg] int32 Poisson counts; with
+ * bkg_counts == NULL the counts are drawn on the device as v1g_sample_bkg_counts draws them, for the
+ * steps state->noise_step[0] .. (0 when there is no state or no counter), and state->noise_step is
+ * advanced by T (models.py:1133).
  * z_out[B,T,N] uint8 and v_out[B,T,N] float32 are optional.  save_for_bwd != 0 keeps v and the
  * spike/refractory bits of every step, and a copy of bkg_counts, inside the handle for
  * v1g_rollout_bwd; x and bkg_counts may be reused once the call has returned.
@@ -274,6 +302,14 @@ int v1g_step_bwd(V1GHandle* h, int32_t batch, const V1GState* g_out, const float
 int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x,
                     const int32_t* bkg_counts, V1GState* state, uint8_t* z_out, float* v_out,
                     int32_t save_for_bwd, void* stream);
+
+/* v1g_rollout_fwd with the LGN spikes drawn on the device from firing rates (as
+ * v1g_sample_lgn_spikes draws them with `lgn_seed`) directly into the rollout's event list, without
+ * materialising x.  rates[T, n_lgn] or [B, T, n_lgn] (rates_batch_stride as above). */
+int v1g_rollout_fwd_rates(V1GHandle* h, int32_t batch, int32_t n_steps, const float* rates,
+                          int64_t rates_batch_stride, int64_t lgn_seed, const int32_t* bkg_counts,
+                          V1GState* state, uint8_t* z_out, float* v_out, int32_t save_for_bwd,
+                          void* stream);
 
 /* Same through HOST buffers: copies x and bkg_counts to the device, runs the rollout from the
  * zero state, copies z_out (uint8, nullable) and v_out (nullable) back.  The end-to-end form a
@@ -344,7 +380,8 @@ int v1g_selftest_bounded_wait(V1GHandle* h, long long polls, void* stream);
  * kernel even where the register-resident one applies), "spin_limit" (iterations a grid-barrier
  * wait may spin before giving up), "no_meta" (1 = the rollout kernels read the plain post / sid /
  * weight arrays instead of the packed 8-byte synapse records), "no_q_pack" (1 = fp32 rows in the
- * backward ring for a batch of 5 instead of 24-bit floats), "phase_timers" (1 = per-block phase
+ * backward ring for a batch of 5 instead of 24-bit floats), "pair_rows" (1 = two steps per 32-byte
+ * row in the backward ring, halving the L2 requests of delays >= 2; measured slower, off by default), "phase_timers" (1 = per-block phase
  * times, read with v1g_get_phase_times), "l2_window", "csr_evict_first" (cache-policy
  * experiments).  No counterpart in the reference. */
 int v1g_set_option(V1GHandle* h, const char* name, long long value);

@@ -104,6 +104,11 @@ def test_batch_5_full_length_reverse_sweep_with_packed_and_fp32_rows():
     t_tie = _check_forward(z, v, zo, vo)
     if t_tie is not None:
         pytest.skip(f"threshold tie at step {t_tie}")
+    cell.set_option("pair_rows", 1)               # two steps per 32-byte ring row (24-bit values)
+    _, _, paired = _gpu_run(cell, cfg, x, c, LOSS_C2)
+    for name, gp, want in zip(NAMES, paired[:3], go):
+        assert_grad_close(gp, want, f"B=5 T=500 {name}, paired 24-bit rows")
+    cell.set_option("pair_rows", 0)
     cell.set_option("no_q_pack", 1)
     _, _, plain = _gpu_run(cell, cfg, x, c, LOSS_C2)
     report = {}

@@ -35,7 +35,8 @@ def nets(draw):
         clip=draw(st.booleans()), lgn_widens=draw(st.booleans()),
         t_ref=draw(st.sampled_from(["one_step", "mixed", "long"])),
         mute=draw(st.booleans()), burst=draw(st.booleans()), hard_reset=draw(st.booleans()),
-        dense_basis=draw(st.booleans()), n_lgn=draw(st.integers(1, 20)), n_bkg=draw(st.integers(1, 8)))
+        dense_basis=draw(st.booleans()), n_lgn=draw(st.integers(1, 20)), n_bkg=draw(st.integers(1, 8)),
+        pair_rows=draw(st.booleans()))
 
 
 def _build(p):
@@ -89,6 +90,7 @@ def test_random_small_nets_forward_and_backward(p):
         return
     orc = OracleV1Column(*dicts, **kw)
     cell = V1Column(*dicts, **kw)
+    cell.set_option("pair_rows", int(p["pair_rows"]))     # both layouts of the backward ring
     assert cell.max_delay == orc.max_delay
     # forward
     z, v, so = orc.rollout(torch.from_numpy(x), torch.from_numpy(c).long())

@@ -153,6 +153,10 @@ def _oracle_grads(orc, cfg, x, c, vscale, dtype, g_z=None, g_v=None, loss=LOSS):
     ("small", (), dict(n_receptors=4)),
     ("small", (), dict(pseudo_gauss=True, gauss_std=0.3)),
     ("small", (), dict(hard_reset=True)),
+    ("tiny", (("pair_rows", 1),), {}),                     # two steps per 32-byte row in the backward ring
+    ("small", (("pair_rows", 1),), {}),
+    ("small", (("pair_rows", 1), ("rollout_chunk", 32)), dict(hard_reset=True)),
+    ("small", (("pair_rows", 1),), dict(n_receptors=4)),
 ])
 def test_bptt_gradients_match_oracle_autograd(name, options, kw):
     kw = dict(KW, **kw)
@@ -322,7 +326,8 @@ def test_bptt_with_osi_dsi_target(with_normalizer):
         assert rel_err(got, w) <= TOL_GRAD
 
 
-@pytest.mark.parametrize("options", [(), (("no_q_pack", 1),), (("rollout_chunk", 64),), (("no_meta", 1),)])
+@pytest.mark.parametrize("options", [(), (("no_q_pack", 1),), (("rollout_chunk", 64),), (("no_meta", 1),),
+                                     (("pair_rows", 1),), (("pair_rows", 1), ("rollout_chunk", 64))])
 def test_bptt_batch_of_five(options):
     """Batch 5 stores the backward Q rows as five 24-bit floats per 16-byte row (7.6e-6 relative
     rounding); the gradients must stay inside the 1e-4 bar, as they do with fp32 rows."""

@@ -21,12 +21,13 @@ class V1GConfig(C.Structure):
                 ("max_delay", C.c_int32), ("n_lgn", C.c_int32), ("n_bkg", C.c_int32),
                 ("flags", C.c_int32), ("dt", C.c_float), ("dampening_factor", C.c_float),
                 ("recurrent_dampening", C.c_float), ("voltage_gradient_dampening", C.c_float),
-                ("gauss_std", C.c_float), ("pseudo_width", C.c_float), ("lr_scale", C.c_float)]
+                ("gauss_std", C.c_float), ("pseudo_width", C.c_float), ("lr_scale", C.c_float),
+                ("bkg_firing_rate", C.c_float)]
 
 
 class V1GState(C.Structure):
     _fields_ = [("z_buf", C.c_void_p), ("v", C.c_void_p), ("r", C.c_void_p), ("asc", C.c_void_p),
-                ("psc_rise", C.c_void_p), ("psc", C.c_void_p)]
+                ("psc_rise", C.c_void_p), ("psc", C.c_void_p), ("noise_step", C.c_void_p)]
 
 
 class V1GLossSpec(C.Structure):
@@ -68,6 +69,11 @@ SIGNATURES = {
     "v1g_get_pre_ind_table": (C.c_int, [_P, C.c_int, _P, _P]),
     "v1g_set_neuron_params": (C.c_int, [_P] * 9),
     "v1g_set_weights": (C.c_int, [_P, C.c_int, _P, _P]),
+    "v1g_set_noise_seed": (C.c_int, [_P, C.c_int64, C.c_int32]),
+    "v1g_sample_bkg_counts": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
+    "v1g_sample_lgn_spikes": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P, _P]),
+    "v1g_rollout_fwd_rates": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P,
+                                        C.POINTER(V1GState), _P, _P, C.c_int32, _P]),
     "v1g_compact_spikes": (C.c_int, [_P, _P, C.c_int32, C.c_int64, _P, C.c_int64, _P, _P]),
     "v1g_compact_spikes_noalloc": (C.c_int, [_P, C.c_int32, C.c_int64, _P, C.c_int64, _P, _P]),
     "v1g_syn_currents_fwd": (C.c_int, [_P, C.c_int, _P, C.c_int32, _P, _P]),

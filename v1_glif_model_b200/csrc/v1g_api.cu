@@ -526,6 +526,8 @@ extern "C" int v1g_set_option(V1GHandle* h, const char* name, long long value) {
     h->opt_no_meta = value != 0;
   } else if (!strcmp(name, "no_q_pack")) {
     h->opt_no_q_pack = value != 0;
+  } else if (!strcmp(name, "pair_rows")) {
+    h->opt_pair_rows = value != 0;
   } else if (!strcmp(name, "l2_window")) {
     h->opt_l2_window = value != 0;
   } else if (!strcmp(name, "csr_evict_first")) {

@@ -4,12 +4,29 @@
 // (3) per-segment ordered fill with warp ballots + prefix sums.  The output order is exactly
 // row-major (row, col), or (t, b, col) for the time-major LGN list of the fused rollout, and is
 // bit-for-bit reproducible (no atomics decide a position).
-#include "v1g_internal.h"
+#include "v1g_rng.cuh"
 
 namespace {
 
+// where the flags come from: an array (positive entries), or LGN firing rates from which the spike
+// of (trial, step, unit) is drawn on the fly - the draw is a pure function of its coordinates, so
+// the counting and the filling pass see the same flags
 template <typename T>
-__device__ __forceinline__ bool is_pos(T v) { return v > (T)0; }
+struct ArraySource {
+  const T* x;
+  int64_t n_cols;
+  __device__ __forceinline__ bool operator()(int row, int64_t c) const { return x[(int64_t)row * n_cols + c] > (T)0; }
+};
+struct RateSource {
+  V1GRateSource s;
+  int64_t n_cols;
+  int T;  // rows are (trial, step) = (row / T, row % T)
+  __device__ __forceinline__ bool operator()(int row, int64_t c) const {
+    const int b = row / T, t = row - b * T;
+    const float rate = s.rates[(int64_t)b * s.batch_stride + (int64_t)t * n_cols + c];
+    return v1g_lgn_spike(rate, b, t, (int)c, s.key0, s.key1);
+  }
+};
 
 // segment id in OUTPUT order for memory row `row`
 __device__ __forceinline__ int64_t out_segment(int row, int seg, int nseg, int n_rows, int tmT) {
@@ -21,17 +38,16 @@ __device__ __forceinline__ int64_t out_segment(int row, int seg, int nseg, int n
   return (int64_t)row * nseg + seg;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256) count_kernel(const T* __restrict__ x, int n_rows,
+template <typename SRC>
+__global__ void __launch_bounds__(256) count_kernel(const SRC src, int n_rows,
                                                     int64_t n_cols, int nseg, int tmT,
                                                     int32_t* __restrict__ counts) {
   const int64_t blk = blockIdx.x;
   const int row = (int)(blk / nseg), seg = (int)(blk - (int64_t)row * nseg);
   const int64_t c0 = (int64_t)seg * V1G_SEG;
   const int64_t c1 = min(c0 + (int64_t)V1G_SEG, n_cols);
-  const T* xr = x + (int64_t)row * n_cols;
   int cnt = 0;
-  for (int64_t c = c0 + threadIdx.x; c < c1; c += blockDim.x) cnt += is_pos(xr[c]) ? 1 : 0;
+  for (int64_t c = c0 + threadIdx.x; c < c1; c += blockDim.x) cnt += src(row, c) ? 1 : 0;
   __shared__ int wsum[8];
   for (int o = 16; o > 0; o >>= 1) cnt += __shfl_down_sync(0xffffffffu, cnt, o);
   if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = cnt;
@@ -82,8 +98,8 @@ __global__ void __launch_bounds__(1024) scan_kernel(int32_t* __restrict__ counts
   }
 }
 
-template <typename T, int KIND>
-__global__ void __launch_bounds__(256) fill_kernel(const T* __restrict__ x, int n_rows,
+template <typename SRC, int KIND>
+__global__ void __launch_bounds__(256) fill_kernel(const SRC src, int n_rows,
                                                    int64_t n_cols, int nseg, int tmT,
                                                    const int32_t* __restrict__ offsets,
                                                    void* __restrict__ out, int64_t cap) {
@@ -91,14 +107,13 @@ __global__ void __launch_bounds__(256) fill_kernel(const T* __restrict__ x, int 
   const int row = (int)(blk / nseg), seg = (int)(blk - (int64_t)row * nseg);
   const int64_t c0 = (int64_t)seg * V1G_SEG;
   const int64_t c1 = min(c0 + (int64_t)V1G_SEG, n_cols);
-  const T* xr = x + (int64_t)row * n_cols;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   __shared__ int wcnt[8];
   int64_t base = offsets[out_segment(row, seg, nseg, n_rows, tmT)];
   const int b = (tmT > 0) ? row / tmT : row;
   for (int64_t cb = c0; cb < c1; cb += blockDim.x) {
     const int64_t c = cb + threadIdx.x;
-    const bool f = (c < c1) && is_pos(xr[c]);
+    const bool f = (c < c1) && src(row, c);
     const unsigned bal = __ballot_sync(0xffffffffu, f);
     if (lane == 0) wcnt[warp] = __popc(bal);
     __syncthreads();
@@ -136,11 +151,14 @@ int v1g_compact_count_scan(V1GHandle* h, int kind, const void* x, int n_rows, in
   if (n_segments_out) *n_segments_out = m;
   if (m > 0) {
     if (kind == V1G_COMPACT_F32_COORDS)
-      count_kernel<float><<<(unsigned)m, 256, 0, st>>>((const float*)x, n_rows, n_cols, nseg,
-                                                       time_major_T, offsets);
+      count_kernel<<<(unsigned)m, 256, 0, st>>>(ArraySource<float>{(const float*)x, n_cols}, n_rows, n_cols, nseg,
+                                                time_major_T, offsets);
+    else if (kind == V1G_COMPACT_U8_PACKED)
+      count_kernel<<<(unsigned)m, 256, 0, st>>>(ArraySource<uint8_t>{(const uint8_t*)x, n_cols}, n_rows, n_cols,
+                                                nseg, time_major_T, offsets);
     else
-      count_kernel<uint8_t><<<(unsigned)m, 256, 0, st>>>((const uint8_t*)x, n_rows, n_cols, nseg,
-                                                         time_major_T, offsets);
+      count_kernel<<<(unsigned)m, 256, 0, st>>>(RateSource{*(const V1GRateSource*)x, n_cols, time_major_T}, n_rows,
+                                                n_cols, nseg, time_major_T, offsets);
   }
   scan_kernel<<<1, 1024, 0, st>>>(offsets, m, h->d_count);
   v1g_count_launches(m > 0 ? 2 : 1);
@@ -155,11 +173,15 @@ int v1g_compact_fill(V1GHandle* h, int kind, const void* x, int n_rows, int64_t 
   const int64_t m = (int64_t)n_rows * nseg;
   if (m == 0) return V1G_OK;
   if (kind == V1G_COMPACT_F32_COORDS)
-    fill_kernel<float, V1G_COMPACT_F32_COORDS><<<(unsigned)m, 256, 0, st>>>(
-        (const float*)x, n_rows, n_cols, nseg, time_major_T, offsets, out, cap);
+    fill_kernel<ArraySource<float>, V1G_COMPACT_F32_COORDS><<<(unsigned)m, 256, 0, st>>>(
+        ArraySource<float>{(const float*)x, n_cols}, n_rows, n_cols, nseg, time_major_T, offsets, out, cap);
+  else if (kind == V1G_COMPACT_U8_PACKED)
+    fill_kernel<ArraySource<uint8_t>, V1G_COMPACT_U8_PACKED><<<(unsigned)m, 256, 0, st>>>(
+        ArraySource<uint8_t>{(const uint8_t*)x, n_cols}, n_rows, n_cols, nseg, time_major_T, offsets, out, cap);
   else
-    fill_kernel<uint8_t, V1G_COMPACT_U8_PACKED><<<(unsigned)m, 256, 0, st>>>(
-        (const uint8_t*)x, n_rows, n_cols, nseg, time_major_T, offsets, out, cap);
+    fill_kernel<RateSource, V1G_COMPACT_U8_PACKED><<<(unsigned)m, 256, 0, st>>>(
+        RateSource{*(const V1GRateSource*)x, n_cols, time_major_T}, n_rows, n_cols, nseg, time_major_T, offsets,
+        out, cap);
   v1g_count_launches(1);
   V1G_CUDA(h, cudaGetLastError());
   return V1G_OK;
@@ -243,11 +265,11 @@ extern "C" int v1g_compact_spikes_noalloc(const float* x, int32_t n_rows, int64_
   // every counter the later passes read is written by the count pass of this same call, so the
   // values left by the previous call never need clearing
   if (m > 0)
-    count_kernel<float><<<(unsigned)m, 256, 0, st>>>(x, n_rows, n_cols, nseg_i, 0, counters);
+    count_kernel<<<(unsigned)m, 256, 0, st>>>(ArraySource<float>{x, n_cols}, n_rows, n_cols, nseg_i, 0, counters);
   scan_kernel<<<1, 1024, 0, st>>>(counters, m, count);
   if (m > 0)
-    fill_kernel<float, V1G_COMPACT_F32_COORDS><<<(unsigned)m, 256, 0, st>>>(
-        x, n_rows, n_cols, nseg_i, 0, counters, coords, cap);
+    fill_kernel<ArraySource<float>, V1G_COMPACT_F32_COORDS><<<(unsigned)m, 256, 0, st>>>(
+        ArraySource<float>{x, n_cols}, n_rows, n_cols, nseg_i, 0, counters, coords, cap);
   v1g_count_launches(m > 0 ? 3 : 1);
   if (cudaGetLastError() != cudaSuccess) {
     v1g_set_global_error("v1g_compact_spikes_noalloc: kernel launch failed");

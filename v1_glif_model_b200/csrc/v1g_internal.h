@@ -61,6 +61,9 @@ struct V1GHandle {
   mutable std::string err;
   V1GSource src[V1G_NSRC];
   bool params_set = false;
+  // keys of the device-side background sampler (models.py:506, 869-877)
+  int64_t noise_seed = 0;
+  int32_t noise_replica = 0;
   // per-neuron constants (device)
   float *decay = nullptr, *cf = nullptr, *asc_decay = nullptr, *asc_amps = nullptr;
   int32_t* tref = nullptr;
@@ -131,6 +134,7 @@ struct V1GHandle {
   int opt_force_smem_kernel = 0;  // never pick the register-resident forward kernel
   int opt_no_meta = 0;            // backward gather reads post / sid / w arrays instead of the packed records
   int opt_no_q_pack = 0;          // keep the backward Q rows in fp32 even for a batch of 5
+  int opt_pair_rows = 0;          // two steps per 32-byte row in the backward ring where the layout allows it
   int opt_l2_window = 0;          // pin the backward Q ring in L2 with an access-policy window
   int opt_csr_evict_first = 1;    // read the backward synapse stream with evict-first loads
   int opt_phase_timers = 0;   // record per-block phase times of the rollout kernels
@@ -198,7 +202,13 @@ int v1g_rate_distribution_loss(V1GHandle* h, const V1GLossSpec* ls, const int32_
 // Input viewed as [n_rows][n_cols]; positives are listed in output order.  time_major_T > 0:
 // rows are (b, t) = (row / T, row % T) and the output is ordered (t, b, col); otherwise (row, col).
 // offsets[] gets the exclusive scan per (ordered) segment, offsets[n_segments] the total.
-enum V1GCompactKind { V1G_COMPACT_F32_COORDS = 0, V1G_COMPACT_U8_PACKED = 1 };
+enum V1GCompactKind { V1G_COMPACT_F32_COORDS = 0, V1G_COMPACT_U8_PACKED = 1, V1G_COMPACT_LGN_RATES = 2 };
+// input of kind V1G_COMPACT_LGN_RATES: spikes are drawn on the fly from firing rates
+struct V1GRateSource {
+  const float* rates;    // [T, n_cols] or [B, T, n_cols]
+  int64_t batch_stride;  // elements between the tables of consecutive trials, 0 = one table
+  unsigned key0, key1;
+};
 #define V1G_SEG 4096
 int v1g_compact_count_scan(V1GHandle* h, int kind, const void* x, int n_rows, int64_t n_cols,
                            int time_major_T, int32_t* offsets, int64_t* n_segments_out,

@@ -18,13 +18,30 @@
 // reads dy(t+1 .. t+D) of arbitrary neurons, i.e. values published at steps >= t+3: like the
 // forward sweep, blocks synchronise through a lagged per-phase counter and rarely wait.
 //
-// What is published is Q, a ring over K = D+6 steps with a 16- or 32-byte row per (neuron, channel):
+// What is published is Q, a ring over K = D+3 steps with a 16- or 32-byte row per (neuron, channel):
 //   projected mode (S <= 8 synapse types): Q[slot][n][s][b] = sum_r basis[s, r] * dy[b, n, r]; a
 //       synapse then needs ONE sector, Q[slot][post][sid][0..B)
 //   raw mode: Q[slot][n][r][b] = dy[b, n, r]; the consumer contracts with basis[sid, :] (R sectors)
 // The gather walks every neuron's CSR row (all synapses, every step: the pseudo-derivative is
 // non-zero for non-spiking neurons), one warp per row, except rows whose B batch entries are all
 // refractory / outside the pseudo-derivative's support and did not spike (exactly zero result).
+//
+// Paired mode (option "pair_rows"; 16-byte rows, projected, packed synapse records, at most one neuron
+// per thread): the ring is laid out in PAIRS of steps, {Q(tau), Q(tau-1)} for even tau in one 32-byte
+// row (one sector), and a synapse of delay d >= 2 reads one pair to serve the steps s and s-1 at once:
+// Q(s+d) and Q(s-1+d), which costs the L2 one request instead of two.  The
+// iteration whose dense part handles step t serves the steps (t-1, t-2) for the delays d >= 2 with
+// t-1+d even - the other delay parity has its turn in the next iteration - and step t-1 alone for
+// the synapses of delay 1, whose Q(t-1) for step t-2 is not complete yet (it is published by the
+// slowest block during this very iteration; waiting for it would need a hard grid barrier).
+// Everything read was published at least two iterations earlier, as in the unpaired loop, so the
+// lagged counters are unchanged.  Requests per reverse step: 0.2 + 0.8 / 2 of the unpaired count for
+// uniform delays 1..5.  Measured on B200 (66,634 neurons, batch 5, T=150, one launch each): L2 read
+// requests 645 M -> 409 M and the L1-to-L2 request port 52 % -> 25 % busy, but 4.33 G instead of
+// 2.20 G warp instructions (slot-to-synapse mapping, two accumulator sets) at 57 % issue utilisation:
+// 6.6 ms against 4.5 ms.  The unpaired loop is therefore the default; it is bound by the latency of
+// its dependent chains (20 % of stalls wait for L2, 30 % for shared memory and shuffles), not by
+// the request count.
 #include <algorithm>
 #include <type_traits>
 
@@ -34,6 +51,7 @@ namespace {
 
 struct BwdArgs {
   int N, D, K, B, T, Np, chunk, chunkP, S, C, n_bkg, state_in_smem, bkg_in_smem, bkg_cap;
+  int KP;  // paired mode: ring slots, each holding the steps (2p, 2p-1)
   const int32_t *rec_rowptr, *rec_post;
   const float* rec_w;
   const uint8_t* rec_sid;
@@ -87,6 +105,9 @@ struct BwdArgs {
 #endif
 #ifndef V1G_BWD_STAGES
 #define V1G_BWD_STAGES 2  // Q-row buffers of the gather pipeline (registers: 20 per stage)
+#endif
+#ifndef V1G_BWD_PAIR_GROUPS
+#define V1G_BWD_PAIR_GROUPS 4  // 32-lane groups of a pass of the paired gather
 #endif
 constexpr int NT = V1G_BWD_NT;
 constexpr int NW = NT / 32;
@@ -156,9 +177,64 @@ __device__ __forceinline__ void load_row(const float* p, float (&q)[BP_]) {
   unpack_row<BP_, PACK>(raw, q);
 }
 
-template <int R_, int BP_, bool PROJ, int DT, bool PACK>
+// the NB batch values of one 16-byte row: five 24-bit floats (PACK) or four fp32 words
+template <int NB, bool PACK>
+__device__ __forceinline__ void unpack_half(const float4 a, float (&q)[NB]) {
+  if (PACK) {
+    const unsigned w0 = __float_as_uint(a.x), w1 = __float_as_uint(a.y), w2 = __float_as_uint(a.z),
+                   w3 = __float_as_uint(a.w);
+    q[0] = __uint_as_float(w0 << 8);
+    q[1 % NB] = __uint_as_float(__funnelshift_l(w0, w1, 16) & 0xffffff00u);
+    q[2 % NB] = __uint_as_float(__funnelshift_l(w1, w2, 24) & 0xffffff00u);
+    q[3 % NB] = __uint_as_float(w2 & 0xffffff00u);
+    q[4 % NB] = __uint_as_float(w3 << 8);
+  } else {
+    q[0] = a.x; q[1 % NB] = a.y; q[2 % NB] = a.z; q[3 % NB] = a.w;
+  }
+}
+
+// Sum eight per-lane values over the warp with 9 shuffles (each exchange halves what a lane
+// carries); lane l returns the total of value ((l >> 2) & 1) | ((l >> 3) & 1) << 1 | ((l >> 4) & 1) << 2.
+__device__ __forceinline__ float warp_reduce8(const float (&v)[8], int lane) {
+  float a4[4], a2[2], a1;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const bool hi = lane & 16;
+    const float recv = __shfl_xor_sync(0xffffffffu, hi ? v[i] : v[i + 4], 16);
+    a4[i] = (hi ? v[i + 4] : v[i]) + recv;
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const bool hi = lane & 8;
+    const float recv = __shfl_xor_sync(0xffffffffu, hi ? a4[i] : a4[i + 2], 8);
+    a2[i] = (hi ? a4[i + 2] : a4[i]) + recv;
+  }
+  {
+    const bool hi = lane & 4;
+    const float recv = __shfl_xor_sync(0xffffffffu, hi ? a2[0] : a2[1], 4);
+    a1 = (hi ? a2[1] : a2[0]) + recv;
+  }
+  a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+  a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+  return a1;
+}
+
+// Sum two per-lane values over the warp with 5 shuffles; lanes 0..15 return the total of v0,
+// lanes 16..31 that of v1.
+__device__ __forceinline__ float warp_reduce2(float v0, float v1, int lane) {
+  const bool hi = lane & 16;
+  float x = (hi ? v1 : v0) + __shfl_xor_sync(0xffffffffu, hi ? v0 : v1, 16);
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+template <int R_, int BP_, bool PROJ, int DT, bool PACK, bool PAIR>
 __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
-  constexpr int QW = PACK ? 4 : BP_;  // 32-bit words per Q row
+  constexpr int QW = PACK ? 4 : BP_;       // 32-bit words per Q row
+  constexpr int RS = PAIR ? 2 * QW : QW;   // words between the rows of consecutive (neuron, channel) entries
+  constexpr int NBX = PACK ? 5 : BP_;      // batch rows the tape and dense loops cover (packed rows: exactly 5)
+  static_assert(!PAIR || (PROJ && QW == 4), "paired rows need the projected 16-byte form");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int B = a.B, K = a.K, N = a.N, Np = a.Np, chunkP = a.chunkP, T = a.T, C = a.C;
@@ -167,6 +243,11 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   const int n0 = blockIdx.x * a.chunk;
   const int cn = min(a.chunk, N - n0);
   const int nb = B * a.n_bkg;
+  // first word of the rows of a step: row (n, c) of that step is at qbase(step) + (n * C + c) * RS
+  auto qbase = [&](int step) -> int64_t {
+    if (PAIR) return ((int64_t)(((step + 1) >> 1) % a.KP) * Np * C * 2 + (step & 1)) * QW;
+    return (int64_t)(step % K) * Np * C * QW;
+  };
 
   const bool fast_rows = PROJ && a.rec_syn8 != nullptr;  // packed-record gather
   unsigned char* sp_ = smem_raw;
@@ -179,18 +260,21 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   float* basis_s = (float*)take(sizeof(float) * a.S * R_);
   // per-step planes [parity of the step][b][k]
   float* gz_s = (float*)take(sizeof(float) * 2 * plane);   // gathered spike gradient
-  float* tv_s = (float*)take(sizeof(float) * 2 * plane);   // v(t)
-  uint8_t* tz_s = (uint8_t*)take(2 * plane);               // spike / refractory bits
-  uint8_t* zmask_s = (uint8_t*)take(chunkP);           // batch rows that spiked at this step
+  float* tv_s = (float*)take(sizeof(float) * 2 * plane);   // v(t) (paired mode: the saved word, flags in its low bits)
+  uint8_t* tz_s = (uint8_t*)take(PAIR ? 0 : 2 * plane);    // spike / refractory bits
+  uint8_t* zmask_s = (uint8_t*)take(PAIR ? 2 * chunkP : chunkP);  // batch rows that spiked at this step (paired mode: walk | mask << 1, by step parity)
   float* s_cnt = (float*)take(sizeof(float) * nb);  // background counts of step t-2, as floats
   int* s_misc = (int*)take(sizeof(int) * 8);  // [1] abort flag, [2+p] rows queued, [4+p] next queue slot (p = parity of the iteration)
   int* slot_s = (int*)take(sizeof(int) * 8);  // first Q row of step t+1+d, d = 0..7
-  uint16_t* rowq_s = (uint16_t*)take(sizeof(uint16_t) * chunkP);  // rows to walk this step
-  int4* rowd_s = (int4*)take(sizeof(int4) * chunkP);  // the same rows as {first synapse, end, row | spike mask << 16, 0}
-  // row pointers of the slice: on chip for the gather that reads them per row pass, from global
-  // memory (two loads per neuron and step) for the packed-record gather
-  int32_t* rp_s = (int32_t*)take(fast_rows ? 0 : sizeof(int32_t) * ((size_t)chunkP * D + 1));
-  const int32_t* rpx = fast_rows ? a.rec_rowptr + (int64_t)n0 * D : rp_s;
+  uint16_t* rowq_s = (uint16_t*)take(PAIR ? 0 : sizeof(uint16_t) * chunkP);  // rows to walk this step
+  int4* rowd_s = (int4*)take(PAIR ? 0 : sizeof(int4) * chunkP);  // the same rows as {first synapse, end, row | spike mask << 16, 0}
+  // paired mode: rows to walk as row | single << 16 | spike mask(t-1) << 17 | spike mask(t-2) << 22
+  uint32_t* rowc_s = (uint32_t*)take(PAIR ? sizeof(uint32_t) * chunkP : 0);
+  // row pointers of the slice: on chip for the gathers that read them per row, from global
+  // memory (two loads per neuron and step) for the unpaired packed-record gather
+  const bool rp_on_chip = PAIR || !fast_rows;
+  int32_t* rp_s = (int32_t*)take(rp_on_chip ? sizeof(int32_t) * ((size_t)chunkP * D + 1) : 0);
+  const int32_t* rpx = rp_on_chip ? rp_s : a.rec_rowptr + (int64_t)n0 * D;
   int* bkptr_s = (int*)take(sizeof(int) * (chunkP + 1));  // background in-synapse ranges, slice-relative
   // background in-synapses of the slice and their weight-gradient accumulators; on chip when they
   // fit, otherwise the global tables are used directly
@@ -214,8 +298,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   float* G_pr = G_p + plane * R_;  // [r][b][k]
 
   for (int i = tid; i < a.S * R_; i += NT) basis_s[i] = a.basis[i];
-  if (!fast_rows)
+  if (rp_on_chip)
     for (int i = tid; i <= cn * D; i += NT) rp_s[i] = a.rec_rowptr[(int64_t)n0 * D + i];
+  if (PAIR)
+    for (int i = tid; i < 2 * chunkP; i += NT) zmask_s[i] = 0;
   const int bk_base = a.bkg_inptr[n0];
   const int bk_m = a.bkg_inptr[n0 + cn] - bk_base;
   for (int k = tid; k <= cn; k += NT) bkptr_s[k] = a.bkg_inptr[n0 + k] - bk_base;
@@ -253,7 +339,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   auto lgn_dw = [&](int tt) {
     const int seg_per_t = B * a.lgn_nseg;
     const int e0 = a.lgn_off[(int64_t)tt * seg_per_t], e1 = a.lgn_off[(int64_t)(tt + 1) * seg_per_t];
-    const float* Qs = a.Q + (int64_t)(tt % K) * Np * C * QW;
+    const float* Qs = a.Q + qbase(tt);
     constexpr int UL = 4;
     for (int e = e0 + gw; e < e1; e += gnw) {
       const uint4 ent = a.lgn_ent4[e];
@@ -271,7 +357,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         if (PROJ) {
           float qv[UL][BP_];
 #pragma unroll
-          for (int q = 0; q < UL; ++q) load_row<BP_, PACK>(Qs + ((int64_t)post[q] * C + sid[q]) * QW, qv[q]);
+          for (int q = 0; q < UL; ++q) load_row<BP_, PACK>(Qs + ((int64_t)post[q] * C + sid[q]) * RS, qv[q]);
 #pragma unroll
           for (int q = 0; q < UL; ++q) {
             val[q] = 0.f;
@@ -285,7 +371,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
 #pragma unroll
             for (int r = 0; r < R_; ++r) {
               float qr[BP_];
-              load_row<BP_, PACK>(Qs + ((int64_t)post[q] * C + r) * QW, qr);
+              load_row<BP_, PACK>(Qs + ((int64_t)post[q] * C + r) * RS, qr);
               float qb = 0.f;
 #pragma unroll
               for (int bb = 0; bb < BP_; ++bb) qb = (bb == b) ? qr[bb] : qb;
@@ -312,10 +398,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       const bool act = k < cn;
       const int n = n0 + (act ? k : 0);
       // all tape loads of the neuron are issued before any of them is used
-      float vv[BP_];
-      unsigned zz[BP_];
+      float vv[NBX];
+      unsigned zz[NBX];
 #pragma unroll
-      for (int b = 0; b < BP_; ++b) {
+      for (int b = 0; b < NBX; ++b) {
         vv[b] = 0.f;
         zz[b] = 2u;
         if (b < B && act) {
@@ -327,7 +413,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       }
       unsigned zm = 0, need = 0;
 #pragma unroll
-      for (int b = 0; b < BP_; ++b) {
+      for (int b = 0; b < NBX; ++b) {
         if (b < B && act) {
           tvp[b * chunkP + k] = vv[b];
           tzp[b * chunkP + k] = (uint8_t)zz[b];
@@ -363,6 +449,26 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     }
   };
 
+  // Paired mode: the saved words of step ts for this thread's neuron into `pl` (the thread is the
+  // only reader and writer of its entries); returns walk | spike mask << 1.
+  auto load_tape_own = [&](int ts, float* pl) -> unsigned {
+    if (tid >= cn || ts < 0) return 0u;
+    unsigned ww[NBX];
+#pragma unroll
+    for (int b = 0; b < NBX; ++b)
+      ww[b] = b < B ? __float_as_uint(__ldcs(a.tape_v + ((int64_t)ts * B + b) * N + n0 + tid)) : 2u;
+    unsigned zm = 0, need = 0;
+#pragma unroll
+    for (int b = 0; b < NBX; ++b) {
+      if (b < B) {
+        pl[b * chunkP + tid] = __uint_as_float(ww[b]);
+        zm |= (ww[b] & 1u) << b;
+        if (!(ww[b] & 2u) && pseudo_h(__uint_as_float(ww[b] & ~3u) - 1.f, a) != 0.f) need = 1;
+      }
+    }
+    return ((need | zm) ? 1u : 0u) | (zm << 1);
+  };
+
   // The loop runs one iteration per step t, newest first.  An iteration loads the tape of step t-1,
   // then every warp does its share of the dense adjoint of step t and goes straight on to the gather
   // of step t-1 (spike gradients of step t-1, needed by the next iteration): the two have no
@@ -372,7 +478,17 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   // Gather(t-1) reads Q(t .. t-1+D); Q(t) was published by the dense part of step t+2, so every block
   // must have finished iteration it-2 (phase it-1).  A block is then at most one iteration ahead of
   // the slowest one and writes Q(t-3) at the earliest: D+3 ring slots suffice.
-  if (T >= 1) {
+  if (PAIR) {
+    // prologue: the saved words of the last two steps (and the row flags of step T-2); the spike
+    // gradient that later steps send to them is zero
+    if (T >= 1) {
+      load_tape_own(T - 1, tv_s + ((T - 1) & 1) * plane);
+      const unsigned f = load_tape_own(T - 2, tv_s + ((T - 2) & 1) * plane);
+      if (tid < cn) zmask_s[((T - 2) & 1) * chunkP + tid] = (uint8_t)f;
+    }
+    for (int i = tid; i < 2 * (int)plane; i += NT) gz_s[i] = 0.f;
+    __syncthreads();
+  } else if (T >= 1) {
     // prologue: tape of the last step; its spike gradient from later steps is zero
     load_step(T - 1, tv_s + ((T - 1) & 1) * plane, tz_s + ((T - 1) & 1) * plane, gz_s + ((T - 1) & 1) * plane, false);
     __syncthreads();
@@ -393,7 +509,11 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       s_misc[2 + ((it + 1) & 1)] = 0;  // the counters of the next iteration
       s_misc[4 + ((it + 1) & 1)] = 0;
     }
-    if (tid < 8) slot_s[tid] = ((tg + 1 + tid) % K) * Np * C;
+    if (PAIR) {
+      // first 32-byte row of the pair that a synapse of delay tid+1 reads in this iteration: delay 1
+      // the pair holding Q(t), the delays of this iteration's parity the pair {Q(t-1+d), Q(t-2+d)}
+      if (tid < 8) slot_s[tid] = (((tid == 0 ? t + 1 : t + tid + 1) >> 1) % a.KP) * Np * C;
+    } else if (tid < 8) slot_s[tid] = ((tg + 1 + tid) % K) * Np * C;
     // Lagged barrier, by a thread of the last warp (which owns no neuron when the slice has fewer
     // neurons than the block has threads) while the others load the tape: this block has finished
     // iteration it-1; every block must have finished iteration it-2 before the gather below.
@@ -407,6 +527,46 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
 
     // ---------------- phase A: tape of step t-1, row flags, counts of step t-2 ----------------
     q_cnt_cur = q_cnt;
+    float gzr[NBX];    // paired mode: gathered spike gradient and saved word of step t for the dense part
+    unsigned twr[NBX];
+    if (PAIR) {
+      // Planes are shared by the steps t and t-2; every entry belongs to one thread, which takes its
+      // values of step t into registers before it overwrites them with those of step t-2.
+#pragma unroll
+      for (int b = 0; b < NBX; ++b) {
+        const bool own = b < B && tid < cn;
+        gzr[b] = own ? gzC[b * chunkP + tid] : 0.f;
+        twr[b] = own ? __float_as_uint(tvC[b * chunkP + tid]) : 2u;
+      }
+      const unsigned f2 = load_tape_own(t - 2, tvC);
+      unsigned f1 = 0;
+      if (tid < cn) {
+        if (tg >= 0) f1 = zmask_s[((t & 1) ^ 1) * chunkP + tid];
+        zmask_s[(t & 1) * chunkP + tid] = (uint8_t)f2;
+      }
+      // the row is walked for the delays >= 2 when either step needs it, for delay 1 when step t-1 does
+      const bool walk = ((f1 | f2) & 1u) != 0;
+      if (tid < cn && !walk)
+        for (int b = 0; b < B; ++b) gzC[b * chunkP + tid] = 0.f;  // spike gradient of step t-2 so far
+      const unsigned wm = __ballot_sync(0xffffffffu, walk);
+      if (wm) {
+        int base = 0;
+        if (lane == 0) base = atomicAdd(q_cnt_cur, __popc(wm));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (walk) {
+          const unsigned zm1 = f1 >> 1, zm2 = f2 >> 1;
+          rowc_s[base + __popc(wm & ((1u << lane) - 1u))] =
+              (unsigned)tid | ((f1 & 1u) << 16) | (zm1 << 17) | (zm2 << 22);
+          const int32_t* rp = rp_s + tid * D;
+          const int len = (f1 & 1u) ? rp[1] - rp[0] : 0;
+          int lenc = 0;
+          for (int d = 1 + ((t - 1) & 1); d < D; d += 2) lenc += rp[d + 1] - rp[d];
+          c_rows += 1ull + (unsigned long long)((D - ((t - 1) & 1)) / 2);
+          c_events += (unsigned long long)(len + lenc);
+          c_dw += (unsigned long long)(len + lenc) * __popc(zm1) + (unsigned long long)lenc * __popc(zm2);
+        }
+      }
+    } else
     if (tg >= 0) load_step(tg, tv_s + ((t & 1) ^ 1) * plane, tz_s + ((t & 1) ^ 1) * plane, gzB, true);
     if (t >= 2)
       for (int i = tid; i < nb; i += NT) {
@@ -422,7 +582,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
 
     // ---------------- dense adjoint of step t, publish Q(t-2), background weight gradient ----------------
     const int bin = (a.sgrad && a.sync_bin > 0 && t / a.sync_bin < a.nbins) ? t / a.sync_bin : -1;
-    float* Qw = a.Q + (int64_t)((t + K - 2) % K) * Np * C * QW;
+    float* Qw = a.Q + (t >= 2 ? qbase(t - 2) : 0);
     const bool sync_on = a.sync.first != nullptr && t >= a.sync.t0 && t < a.sync.t0 + a.sync.W;
     const bool osi_on = a.osi_coef != nullptr && t >= a.osi_t0 && t < a.osi_t1;
     for (int k = tid; k < cn; k += NT) {
@@ -430,37 +590,37 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       const float k_decay = a.decay[n], k_cf = a.cf[n], k_ad0 = a.asc_decay[2 * n], k_ad1 = a.asc_decay[2 * n + 1];
       const float rc = (a.rate_coef && t >= a.rate_t0 && t < a.rate_t1) ? a.rate_coef[n] : 0.f;
       const float vlo = a.v_lo ? a.v_lo[n] : 0.f;
-      float sadd[BP_];  // synchrony target over given samples and OSI/DSI target: dL/dz[b, t, n]
+      float sadd[NBX];  // synchrony target over given samples and OSI/DSI target: dL/dz[b, t, n]
 #pragma unroll
-      for (int b = 0; b < BP_; ++b) sadd[b] = 0.f;
+      for (int b = 0; b < NBX; ++b) sadd[b] = 0.f;
       if (sync_on) {
         for (int sp = a.sync.first[n]; sp >= 0; sp = a.sync.next[sp]) {
           const int smp = a.sync.pos_sample[sp];
           const int tb = a.sync.trial[smp];
           const float gs = a.sync.g[(int64_t)smp * a.sync.W + (t - a.sync.t0)];
 #pragma unroll
-          for (int b = 0; b < BP_; ++b) sadd[b] += (b == tb) ? gs : 0.f;
+          for (int b = 0; b < NBX; ++b) sadd[b] += (b == tb) ? gs : 0.f;
         }
       }
       if (osi_on) {
 #pragma unroll
-        for (int b = 0; b < BP_; ++b)
+        for (int b = 0; b < NBX; ++b)
           if (b < B) sadd[b] += a.osi_coef[(int64_t)b * N + n];
       }
-      float dyv[BP_][R_];  // dy(t-2) of every batch row of this neuron
+      float dyv[NBX][R_];  // dy(t-2) of every batch row of this neuron
 #pragma unroll
-      for (int b = 0; b < BP_; ++b) {
+      for (int b = 0; b < NBX; ++b) {
 #pragma unroll
         for (int r = 0; r < R_; ++r) dyv[b][r] = 0.f;
         if (b < B) {
           const int si = b * chunkP + k;
-          const float v = tvC[si];
-          const unsigned zr = tzC[si];
+          const float v = PAIR ? __uint_as_float(twr[b] & ~3u) : tvC[si];
+          const unsigned zr = PAIR ? (twr[b] & 3u) : (unsigned)tzC[si];
           const bool free_ = !(zr & 2u);
           const int64_t oi = ((int64_t)b * T + t) * N + n;
           float gz = rc + (bin >= 0 ? a.sgrad[b * a.nbins + bin] : 0.f) + (a.g_z ? a.g_z[oi] : 0.f);
           gz += sadd[b];
-          gz += a.rec_factor * gzC[si];
+          gz += a.rec_factor * (PAIR ? gzr[b] : gzC[si]);
           float gv = G_v[si] + (a.g_v ? a.g_v[oi] : 0.f);
           if (a.volt_coef != 0.f) {
             // range mode: outside [vlo, 1]; threshold mode: distance from the threshold
@@ -490,11 +650,11 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       }
       if (t >= 2) {
         // one 16/32-byte row per channel, all batch rows of the neuron at once
-        float4* qd = (float4*)(Qw + (int64_t)n * C * QW);
+        float4* qd = (float4*)(Qw + (int64_t)n * C * RS);
         for (int c = 0; c < C; ++c) {
-          float row[BP_];
+          float row[NBX];
 #pragma unroll
-          for (int b = 0; b < BP_; ++b) {
+          for (int b = 0; b < NBX; ++b) {
             if (PROJ) {
               float s2 = 0.f;
 #pragma unroll
@@ -510,12 +670,12 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           if (PACK) {
             float r8[8];
 #pragma unroll
-            for (int b = 0; b < 8; ++b) r8[b] = b < BP_ ? row[b % BP_] : 0.f;
-            __stcg(qd + c, pack_row5(r8));
+            for (int b = 0; b < 8; ++b) r8[b] = b < NBX ? row[b % NBX] : 0.f;
+            __stcg(qd + c * (RS / 4), pack_row5(r8));
           } else {
-            __stcg(qd + c * (BP_ / 4), make_float4(row[0], row[1], row[2], row[3]));
+            __stcg(qd + c * (RS / 4), make_float4(row[0], row[1], row[2], row[3]));
             if (BP_ == 8)
-              __stcg(qd + c * 2 + 1, make_float4(row[4 % BP_], row[5 % BP_], row[6 % BP_], row[7 % BP_]));
+              __stcg(qd + c * (RS / 4) + 1, make_float4(row[4 % NBX], row[5 % NBX], row[6 % NBX], row[7 % NBX]));
           }
         }
         // background weight gradient of step t-2 for the synapses this thread owns (branch-free:
@@ -528,7 +688,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           for (int r = 0; r < R_; ++r) bsr[r] = bs[r];
           float accw = 0.f;
 #pragma unroll
-          for (int b = 0; b < BP_; ++b) {
+          for (int b = 0; b < NBX; ++b) {
             if (b < B) {
               float s2 = 0.f;
 #pragma unroll
@@ -607,7 +767,177 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       if (lane == 0) q = atomicAdd(q_pop, 1);
       return __shfl_sync(0xffffffffu, q, 0);
     };
-    if (fast_rows) {
+    if (PAIR) {
+      // Paired gather.  A queued row contributes, in this iteration, its delay-1 bucket (step t-1 only,
+      // if that step needs the row) and the buckets of delay d >= 2 with t-1+d even (steps t-1 and t-2).
+      // The L1-to-L2 port counts one request per distinct 128-byte line of a load instruction, whatever
+      // the lanes' access width (a 256-bit load per lane costs two), so a synapse of delay >= 2 takes TWO
+      // ADJACENT LANES: the even one loads the first 16-byte half of the pair row (Q(t-1+d), for step
+      // t-1), the odd one the second half (Q(t-2+d), for step t-2) - one line, one request, two steps.
+      // A delay-1 synapse takes one lane.  These lane slots form one virtual row (delay-1 bucket padded
+      // to an even length, then two slots per synapse of the other buckets); a pass is UF*32 consecutive
+      // slots.  The software pipeline is the one of the unpaired path: records of the pass after next
+      // and Q halves of the next pass in flight while the current one is accumulated.
+      constexpr int NB = PACK ? 5 : BP_;                      // batch values a row carries
+      constexpr int UF = V1G_BWD_PAIR_GROUPS, NS = 2;
+      constexpr int NSEG = 1 + (DT > 0 ? DT / 2 : V1G_MAX_DELAY / 2);  // delay-1 bucket + buckets of one parity
+      const int cpar = (t - 1) & 1;                           // first bucket of this iteration's parity is 1 + cpar
+      const unsigned half1 = (t & 1) ? 4u : 0u;               // words from the pair row to Q(t): second half when t is odd
+      float* const gz1 = gzB;                                 // spike gradient of step t-1: add
+      float* const gz2 = gzC;                                 // spike gradient of step t-2: first contribution
+      // sl[0] / sl[m]: SLOTS of the segment (delay-1 bucket rounded up to even; two per synapse else)
+      struct VRow { int ss[NSEG], sl[NSEG], n1, L, pos; unsigned code; int fl; };  // fl: 1 first pass, 2 last pass, 4 valid
+      struct CPass { unsigned code; int fl; };
+      VRow pr;
+      pr.n1 = 0; pr.L = 0; pr.pos = 0; pr.code = 0; pr.fl = 0;
+#pragma unroll
+      for (int m = 0; m < NSEG; ++m) pr.ss[m] = pr.sl[m] = 0;
+      CPass ps_[NS];
+      uint2 rec[UF];
+      int jR[UF];            // slot of the pass in `rec`: synapse * 4 + kind (1 delay 1, 2 first half, 3 second half), 0 = none
+      float4 qS[NS][UF];
+      float wS[NS][UF];
+      int jS[NS][UF];
+      float acc1[NB], acc2[NB];
+#pragma unroll
+      for (int i = 0; i < NS; ++i) ps_[i] = CPass{0u, 0};
+#pragma unroll
+      for (int b = 0; b < NB; ++b) acc1[b] = acc2[b] = 0.f;
+      auto issue_rec = [&]() {  // advance pr to the following pass and request its records
+        if (pr.fl && pr.pos + 32 * UF < pr.L) {
+          pr.pos += 32 * UF;
+          pr.fl = 4;
+        } else {
+          const int q = pop_row();
+          if (q < nq) {
+            const unsigned code = rowc_s[q];
+            const int32_t* rp = rp_s + (int)(code & 0xffffu) * D;
+            pr.code = code;
+            pr.ss[0] = rp[0];
+            pr.n1 = (code & 0x10000u) ? rp[1] - rp[0] : 0;
+            pr.sl[0] = (pr.n1 + 1) & ~1;
+            pr.L = pr.sl[0];
+#pragma unroll
+            for (int m = 1; m < NSEG; ++m) {
+              const int d = 2 * m - 1 + cpar;      // bucket index = delay - 1
+              const bool has = d < D;
+              pr.ss[m] = has ? rp[has ? d : 0] : 0;
+              pr.sl[m] = has ? 2 * (rp[has ? d + 1 : 0] - pr.ss[m]) : 0;
+              pr.L += pr.sl[m];
+            }
+            pr.pos = 0;
+            pr.fl = 5;
+          } else {
+            pr.fl = 0;
+            pr.L = 0;
+          }
+        }
+        if (pr.fl && pr.pos + 32 * UF >= pr.L) pr.fl |= 2;
+#pragma unroll
+        for (int u = 0; u < UF; ++u) {
+          int r = pr.pos + u * 32 + lane;
+          int code = (pr.fl && r < pr.n1) ? (pr.ss[0] + r) * 4 + 1 : 0;
+          r -= pr.sl[0];
+#pragma unroll
+          for (int m = 1; m < NSEG; ++m) {
+            code = (r >= 0 && r < pr.sl[m]) ? (pr.ss[m] + (r >> 1)) * 4 + 2 + (r & 1) : code;
+            r -= pr.sl[m];
+          }
+          jR[u] = pr.fl ? code : 0;
+          rec[u] = __ldcs(a.rec_syn8 + (jR[u] >> 2));
+        }
+      };
+      auto issue_q = [&](float4 (&q)[UF], float (&w)[UF], int (&js)[UF]) {
+#pragma unroll
+        for (int u = 0; u < UF; ++u) {
+          const int kind = jR[u] & 3;
+          const unsigned w0 = rec[u].x;
+          unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + ((w0 >> 22) & 127u);
+          unsigned word = row * 8u + (kind == 1 ? half1 : kind == 3 ? 4u : 0u);
+          word = kind ? word : 0u;  // slots without a synapse share one request
+          q[u] = __ldcg((const float4*)(a.Q + word));
+          w[u] = kind ? __uint_as_float(rec[u].y) : 0.f;
+          js[u] = jR[u];
+        }
+      };
+      auto compute = [&](const CPass& ps, const float4 (&q)[UF], const float (&w)[UF], const int (&js)[UF]) {
+        if (ps.fl & 1) {
+#pragma unroll
+          for (int b = 0; b < NB; ++b) acc1[b] = acc2[b] = 0.f;
+        }
+        const unsigned zm1 = (ps.code >> 17) & 31u, zm2 = (ps.code >> 22) & 31u;
+#pragma unroll
+        for (int u = 0; u < UF; ++u) {
+          float pj[NB];
+          unpack_half<NB, PACK>(q[u], pj);
+          const int kind = js[u] & 3;
+          const float w1 = kind == 3 ? 0.f : w[u], w2 = kind == 3 ? w[u] : 0.f;
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            acc1[b] += w1 * pj[b];
+            acc2[b] += w2 * pj[b];
+          }
+          if (zm1 | zm2) {
+            // the source neuron spiked at step t-1 (zm1) or t-2 (zm2): recurrent weight gradient; the two
+            // halves of a synapse are added up by its first lane, which is its only writer
+            const unsigned zm = kind == 3 ? zm2 : zm1;
+            float dwv = 0.f;
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+              if (zm & (1u << b)) dwv += pj[b];
+            const float other = __shfl_down_sync(0xffffffffu, dwv, 1);
+            if (kind == 2) dwv += other;
+            if (kind == 1 || kind == 2) a.dw_rec[js[u] >> 2] += dwv;
+          }
+        }
+        if (ps.fl & 2) {
+          const int k = (int)(ps.code & 0xffffu);
+          float v8[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            v8[i] = acc1[i % NB];
+            v8[i + 4] = acc2[i % NB];
+          }
+          const float tot = warp_reduce8(v8, lane);
+          const int idx = (lane >> 2) & 7, b = idx & 3;
+          if ((lane & 3) == 0 && b < B) {
+            if (idx < 4) gz1[b * chunkP + k] += tot;
+            else gz2[b * chunkP + k] = tot;
+          }
+          if (NB == 5) {
+            const float t5 = warp_reduce2(acc1[4 % NB], acc2[4 % NB], lane);
+            if (lane == 0) gz1[4 * chunkP + k] += t5;
+            if (lane == 16) gz2[4 * chunkP + k] = t5;
+          }
+        }
+      };
+      auto turn = [&](auto I) -> bool {
+        constexpr int i = decltype(I)::value;
+        if (!pr.fl) {
+#pragma unroll
+          for (int o = 1; o < NS; ++o)
+            if (ps_[(i + o) % NS].fl)
+              compute(ps_[(i + o) % NS], qS[(i + o) % NS], wS[(i + o) % NS], jS[(i + o) % NS]);
+          return false;
+        }
+        ps_[i] = CPass{pr.code, pr.fl};
+        issue_q(qS[i], wS[i], jS[i]);
+        issue_rec();
+        constexpr int x = (i + 1) % NS;  // the oldest pass
+        if (ps_[x].fl) {
+          compute(ps_[x], qS[x], wS[x], jS[x]);
+          ps_[x].fl = 0;
+        }
+        return true;
+      };
+      if (nq > 0) {
+        issue_rec();
+        for (;;) {
+          if (!turn(std::integral_constant<int, 0>{})) break;
+          if (!turn(std::integral_constant<int, 1>{})) break;
+        }
+      }
+    } else if (fast_rows) {
       // Packed-record path.  The unit of work is a pass: up to UF*32 consecutive synapses of one
       // row, one 8-byte record per synapse.  Warps draw rows from the queue of row descriptors
       // written in phase A.  Each warp keeps the records of the pass after next
@@ -838,17 +1168,17 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           for (int kb = 0; kb < D; ++kb) {
             const int sstep = d - (kb + 1);
             if (!(hbits & (1u << kb)) || sstep < 0 || sstep >= T) continue;
-            const float* Qp = a.Q + ((int64_t)(sstep % K) * Np + post) * C * QW;
+            const float* Qp = a.Q + qbase(sstep) + (int64_t)post * C * RS;
             float pj[BP_];
             if (PROJ) {
-              load_row<BP_, PACK>(Qp + sid * QW, pj);
+              load_row<BP_, PACK>(Qp + sid * RS, pj);
             } else {
 #pragma unroll
               for (int bb = 0; bb < BP_; ++bb) pj[bb] = 0.f;
 #pragma unroll
               for (int r = 0; r < R_; ++r) {
                 float q[BP_];
-                load_row<BP_, PACK>(Qp + r * QW, q);
+                load_row<BP_, PACK>(Qp + r * RS, q);
 #pragma unroll
                 for (int bb = 0; bb < BP_; ++bb) pj[bb] += q[bb] * basis_s[sid * R_ + r];
               }
@@ -978,9 +1308,9 @@ __global__ void finish_loss_kernel(float* acc, float* out) {
   }
 }
 
-template <int R_, int BP_, bool PROJ, int DT, bool PACK>
+template <int R_, int BP_, bool PROJ, int DT, bool PACK, bool PAIR = false>
 int launch_bwd_d(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream_t st) {
-  auto kern = rollout_bwd_kernel<R_, BP_, PROJ, DT, PACK>;
+  auto kern = rollout_bwd_kernel<R_, BP_, PROJ, DT, PACK, PAIR>;
   V1G_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0;
   V1G_CUDA(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, smem));
@@ -1001,9 +1331,19 @@ int launch_bwd(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream
   return launch_bwd_d<R_, BP_, PROJ, 0, PACK>(h, a, grid, smem, st);
 }
 
+// paired rows: projected mode with 16-byte rows (batch <= 4 in fp32, batch 5 as 24-bit floats)
+template <int R_, int BP_, bool PACK>
+int launch_bwd_pair(V1GHandle* h, const BwdArgs& a, int grid, size_t smem, cudaStream_t st) {
+  if (a.D == 5) return launch_bwd_d<R_, BP_, true, 5, PACK, true>(h, a, grid, smem, st);
+  return launch_bwd_d<R_, BP_, true, 0, PACK, true>(h, a, grid, smem, st);
+}
+
 template <int R_>
-int launch_bwd_r(V1GHandle* h, const BwdArgs& a, int BP, bool proj, bool pack, int grid, size_t smem,
+int launch_bwd_r(V1GHandle* h, const BwdArgs& a, int BP, bool proj, bool pack, bool pair, int grid, size_t smem,
                  cudaStream_t st) {
+  if (pair)
+    return BP == 4 ? launch_bwd_pair<R_, 4, false>(h, a, grid, smem, st)
+                   : launch_bwd_pair<R_, 8, true>(h, a, grid, smem, st);
   if (BP == 4)
     return proj ? launch_bwd<R_, 4, true, false>(h, a, grid, smem, st)
                 : launch_bwd<R_, 4, false, false>(h, a, grid, smem, st);
@@ -1050,11 +1390,16 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   if (plan.chunkP > 65535) return v1g_fail(h, V1G_ERANGE, "slice of %d neurons per block exceeds 65535", plan.chunkP);
   auto al = [](size_t b) { return (b + 15) & ~(size_t)15; };
   const size_t plane = (size_t)B * plan.chunkP;
-  const bool fast = proj && !h->opt_no_meta && h->src[V1G_SRC_REC].syn8 != nullptr;  // packed-record gather
-  size_t smem = al(sizeof(float) * S * R) + 2 * al(sizeof(float) * 2 * plane) + al(2 * plane) +
-                al(plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 8) + al(sizeof(int) * 8) +
-                al(sizeof(uint16_t) * plan.chunkP) + al(sizeof(int4) * plan.chunkP) +
-                (fast ? 0 : al(sizeof(int32_t) * ((size_t)plan.chunkP * D + 1))) +
+  const bool fast = proj && !h->opt_no_meta && h->src[V1G_SRC_REC].syn8 != nullptr &&
+                    h->src[V1G_SRC_REC].nnz > 0;  // packed-record gather
+  // paired rows (two steps per 32-byte row): 16-byte rows, packed records, one neuron per thread
+  const bool pair = fast && QW == 4 && plan.chunk <= NT && h->opt_pair_rows;
+  const int KP = ((D + 3) >> 1) + 1;  // pair slots covering D+3 consecutive steps at either alignment
+  size_t smem = al(sizeof(float) * S * R) + 2 * al(sizeof(float) * 2 * plane) + al(pair ? 0 : 2 * plane) +
+                al(pair ? 2 * plan.chunkP : plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 8) +
+                al(sizeof(int) * 8) + al(pair ? 0 : sizeof(uint16_t) * plan.chunkP) +
+                al(pair ? 0 : sizeof(int4) * plan.chunkP) + al(pair ? sizeof(uint32_t) * plan.chunkP : 0) +
+                ((fast && !pair) ? 0 : al(sizeof(int32_t) * ((size_t)plan.chunkP * D + 1))) +
                 al(sizeof(int) * (plan.chunkP + 1));
   const size_t state_bytes = al(sizeof(float) * plane * (3 + 2 * R));
   int state_in_smem = 0;
@@ -1085,7 +1430,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
     if ((rc = v1g_reserve(h, &h->state_ws, &h->state_ws_cap, (int64_t)(plane * (3 + 2 * R) * plan.grid)))) return rc;
 
   // scratch: Q ring, CSR-order weight gradients, loss tables
-  const int64_t q_elems = (int64_t)K * Np * C * QW;
+  const int64_t q_elems = pair ? (int64_t)KP * Np * C * 2 * QW : (int64_t)K * Np * C * QW;
   if (q_elems >= 0x7fffffffLL) return v1g_fail(h, V1G_ERANGE, "backward Q ring of %lld elements exceeds 32-bit indexing", (long long)q_elems);
   if ((rc = v1g_reserve(h, &h->dy_ring, &h->dy_ring_cap, q_elems))) return rc;
   const bool sync_samples = ls.sync_cost != 0.f && ls.n_sync_samples > 0;
@@ -1141,7 +1486,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   BwdArgs a;
   a.sync = sync_tables;
   a.osi_coef = osi_coef; a.osi_t0 = osi_t0; a.osi_t1 = osi_t1;
-  a.N = N; a.D = D; a.K = K; a.B = B; a.T = T; a.Np = Np;
+  a.N = N; a.D = D; a.K = K; a.KP = KP; a.B = B; a.T = T; a.Np = Np;
   a.chunk = plan.chunk; a.chunkP = plan.chunkP; a.S = S; a.C = C; a.n_bkg = c.n_bkg;
   a.state_in_smem = state_in_smem;
   a.bkg_in_smem = bkg_in_smem;
@@ -1150,7 +1495,7 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   const V1GSource& lsrc = h->src[V1G_SRC_LGN];
   const V1GSource& bk = h->src[V1G_SRC_BKG];
   a.rec_rowptr = rs.rowptr; a.rec_post = rs.post; a.rec_w = rs.w; a.rec_sid = rs.sid;
-  a.rec_syn8 = h->opt_no_meta ? nullptr : rs.syn8;
+  a.rec_syn8 = fast ? rs.syn8 : nullptr;
   a.rec_nnz = (int)rs.nnz;
   a.lgn_rowptr = lsrc.rowptr; a.lgn_post = lsrc.post; a.lgn_sid = lsrc.sid;
   a.bkg_inptr = bk.in_ptr; a.bkg_inpre = bk.in_pre; a.bkg_insid = bk.in_sid;
@@ -1207,8 +1552,8 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
       V1G_CUDA(h, cudaStreamSetAttribute(st, cudaStreamAttributeAccessPolicyWindow, &attr));
     }
   }
-  rc = (R == 4) ? launch_bwd_r<4>(h, a, BP, proj, pack, plan.grid, smem, st)
-                : launch_bwd_r<5>(h, a, BP, proj, pack, plan.grid, smem, st);
+  rc = (R == 4) ? launch_bwd_r<4>(h, a, BP, proj, pack, pair, plan.grid, smem, st)
+                : launch_bwd_r<5>(h, a, BP, proj, pack, pair, plan.grid, smem, st);
   if (h->opt_l2_window) {
     cudaStreamAttrValue attr;
     attr.accessPolicyWindow.base_ptr = nullptr;

@@ -19,6 +19,7 @@
 #include <algorithm>
 
 #include "v1g_rollout_fwd.cuh"
+#include "v1g_rng.cuh"
 
 namespace {
 
@@ -507,16 +508,18 @@ extern "C" int v1g_selftest_bounded_wait(V1GHandle* h, long long polls, void* st
   return V1G_OK;
 }
 
-extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x,
-                               const int32_t* bkg_counts, V1GState* state, uint8_t* z_out,
-                               float* v_out, int32_t save_for_bwd, void* stream) {
+// x: LGN spikes [B,T,n_lgn], or NULL with `rates` set (spikes drawn on the fly into the event list);
+// bkg_counts NULL: drawn on the device for the steps that state->noise_step[0] names.
+static int rollout_fwd_impl(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x,
+                            const V1GRateSource* rates, const int32_t* bkg_counts, V1GState* state,
+                            uint8_t* z_out, float* v_out, int32_t save_for_bwd, void* stream) {
   if (!h) return V1G_EINVAL;
   if (!h->params_set) return v1g_fail(h, V1G_ESTATE, "neuron parameters not set");
   for (int s = 0; s < V1G_NSRC; ++s)
     if (!h->src[s].rowptr) return v1g_fail(h, V1G_ESTATE, "connectivity of source %d not set", s);
   if (batch <= 0 || batch > V1G_MAX_BATCH)
     return v1g_fail(h, V1G_ERANGE, "batch=%d outside 1..%d", batch, V1G_MAX_BATCH);
-  if (n_steps < 0 || !x || !bkg_counts) return v1g_fail(h, V1G_EINVAL, "v1g_rollout_fwd: bad argument");
+  if (n_steps < 0 || (!x && !rates)) return v1g_fail(h, V1G_EINVAL, "v1g_rollout_fwd: bad argument");
   if (state && !(state->z_buf && state->v && state->r && state->asc && state->psc_rise && state->psc))
     return v1g_fail(h, V1G_EINVAL, "v1g_rollout_fwd: state has null members");
   cudaStream_t st = (cudaStream_t)stream;
@@ -525,20 +528,29 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
   h->tape_valid = false;
   if (T == 0) return V1G_OK;
   int rc;
+  if (!bkg_counts) {
+    // draw the counts into the handle's own buffer (kept for the backward pass when asked to save)
+    const int64_t nc = (int64_t)B * T * c.n_bkg;
+    if ((rc = v1g_reserve(h, &h->tape_counts_buf, &h->tape_counts_cap, nc))) return rc;
+    if ((rc = v1g_sample_bkg_internal(h, B, T, state ? state->noise_step : nullptr, 0, h->tape_counts_buf, st)))
+      return rc;
+    bkg_counts = h->tape_counts_buf;
+  }
 
   // ---- LGN events: ordered compaction of x[B,T,n_lgn] into a time-major list ----
   const int nseg = (c.n_lgn + V1G_SEG - 1) / V1G_SEG;
   const int64_t nsegs = (int64_t)B * T * nseg;
   if ((rc = v1g_reserve(h, &h->lgn_offsets, &h->lgn_offsets_cap, nsegs + 1))) return rc;
-  if ((rc = v1g_compact_count_scan(h, V1G_COMPACT_U8_PACKED, x, B * T, c.n_lgn, T, h->lgn_offsets,
-                                   nullptr, st)))
+  const int lgn_kind = x ? V1G_COMPACT_U8_PACKED : V1G_COMPACT_LGN_RATES;
+  const void* lgn_src = x ? (const void*)x : (const void*)rates;
+  if ((rc = v1g_compact_count_scan(h, lgn_kind, lgn_src, B * T, c.n_lgn, T, h->lgn_offsets, nullptr, st)))
     return rc;
   V1G_CUDA(h, cudaMemcpyAsync(h->h_count, h->d_count, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
   V1G_CUDA(h, cudaStreamSynchronize(st));
   const int64_t n_lgn_events = h->h_count[0];
   if ((rc = v1g_reserve(h, &h->lgn_entries, &h->lgn_entries_cap, n_lgn_events + 1))) return rc;
-  if ((rc = v1g_compact_fill(h, V1G_COMPACT_U8_PACKED, x, B * T, c.n_lgn, T, h->lgn_offsets,
-                             h->lgn_entries, n_lgn_events, st)))
+  if ((rc = v1g_compact_fill(h, lgn_kind, lgn_src, B * T, c.n_lgn, T, h->lgn_offsets, h->lgn_entries,
+                             n_lgn_events, st)))
     return rc;
   if ((rc = v1g_reserve(h, &h->lgn_ent4, &h->lgn_ent4_cap, n_lgn_events + 1))) return rc;
   if (n_lgn_events > 0) {
@@ -673,15 +685,35 @@ extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, con
     // the backward pass needs the counts again; keep a copy so that the caller's buffer may be
     // reused as soon as this call has been queued
     const int64_t nc = (int64_t)B * T * c.n_bkg;
-    if ((rc = v1g_reserve(h, &h->tape_counts_buf, &h->tape_counts_cap, nc))) return rc;
-    V1G_CUDA(h, cudaMemcpyAsync(h->tape_counts_buf, bkg_counts, (size_t)nc * sizeof(int32_t),
-                                cudaMemcpyDeviceToDevice, st));
+    if (bkg_counts != h->tape_counts_buf) {
+      if ((rc = v1g_reserve(h, &h->tape_counts_buf, &h->tape_counts_cap, nc))) return rc;
+      V1G_CUDA(h, cudaMemcpyAsync(h->tape_counts_buf, bkg_counts, (size_t)nc * sizeof(int32_t),
+                                  cudaMemcpyDeviceToDevice, st));
+    }
     h->tape_valid = true;
     h->tape_B = B;
     h->tape_T = T;
     h->tape_counts = h->tape_counts_buf;
   }
+  if (state && state->noise_step) return v1g_advance_noise_step(h, state->noise_step, B, T, st);
   return V1G_OK;
+}
+
+extern "C" int v1g_rollout_fwd(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x,
+                               const int32_t* bkg_counts, V1GState* state, uint8_t* z_out,
+                               float* v_out, int32_t save_for_bwd, void* stream) {
+  if (h && !x) return v1g_fail(h, V1G_EINVAL, "v1g_rollout_fwd: x is NULL");
+  return rollout_fwd_impl(h, batch, n_steps, x, nullptr, bkg_counts, state, z_out, v_out, save_for_bwd, stream);
+}
+
+extern "C" int v1g_rollout_fwd_rates(V1GHandle* h, int32_t batch, int32_t n_steps, const float* rates,
+                                     int64_t rates_batch_stride, int64_t lgn_seed,
+                                     const int32_t* bkg_counts, V1GState* state, uint8_t* z_out,
+                                     float* v_out, int32_t save_for_bwd, void* stream) {
+  if (!h) return V1G_EINVAL;
+  if (!rates || rates_batch_stride < 0) return v1g_fail(h, V1G_EINVAL, "v1g_rollout_fwd_rates: bad argument");
+  V1GRateSource src{rates, rates_batch_stride, (unsigned)lgn_seed, (unsigned)((uint64_t)lgn_seed >> 32)};
+  return rollout_fwd_impl(h, batch, n_steps, nullptr, &src, bkg_counts, state, z_out, v_out, save_for_bwd, stream);
 }
 
 extern "C" int v1g_rollout_fwd_host(V1GHandle* h, int32_t batch, int32_t n_steps,

@@ -139,7 +139,7 @@ class V1Column:
             dt=dt, dampening_factor=dampening_factor,
             recurrent_dampening=recurrent_dampening_factor,
             voltage_gradient_dampening=voltage_gradient_dampening, gauss_std=gauss_std,
-            pseudo_width=pseudo_width, lr_scale=lr_scale)
+            pseudo_width=pseudo_width, lr_scale=lr_scale, bkg_firing_rate=bkg_firing_rate)
         hp = C.c_void_p()
         rc = self._lib.v1g_create(C.byref(cfg), C.byref(hp))
         if rc != _lib.OK:
@@ -182,8 +182,12 @@ class V1Column:
             _source(_lib.SRC_BKG, bkg_input["indices"], bkg_input["weights"], bkg_input["syn_ids"],
                     self.n_bkg, input_weight_scale)
         self.refresh_weights()
-        self._noise_gen = torch.Generator(device=self.device)
-        self._noise_gen.manual_seed(self.noise_seed)
+        # keys of the device-side background sampler: noise_seed + replica_id * 1000003
+        # (models.py:869-877); one process drives one GPU here, so the replica is the process rank
+        replica = 0
+        if torch.distributed.is_available() and torch.distributed.is_initialized():
+            replica = torch.distributed.get_rank()
+        self.set_noise_seed(self.noise_seed, replica)
 
     # ---- plumbing ----------------------------------------------------------------------
     def _check(self, rc):
@@ -193,6 +197,14 @@ class V1Column:
         if getattr(self, "_libh", None):
             self._lib.v1g_destroy(self._libh)
             self._libh = None
+
+    def set_noise_seed(self, noise_seed, replica_id=None):
+        """Seed of the background sampler (``models.py:506``; the reference's training loop advances
+        it once per rollout, ``tf_utils.py:235-237``) and, optionally, the replica id that offsets it."""
+        self.noise_seed = int(noise_seed)
+        if replica_id is not None:
+            self.replica_id = int(replica_id)
+        self._check(self._lib.v1g_set_noise_seed(self._libh, self.noise_seed, self.replica_id))
 
     def set_option(self, name, value):
         self._check(self._lib.v1g_set_option(self._libh, name.encode(), int(value)))
@@ -359,8 +371,12 @@ class V1Column:
         for t in (z_buf, v, r, asc, psc_rise, psc):
             assert t.is_cuda and t.is_contiguous()
         assert r.dtype == torch.int8
+        noise_step = None
+        if len(state) > 6 and isinstance(state[6], torch.Tensor) and state[6].is_cuda:
+            assert state[6].dtype == torch.int32 and state[6].is_contiguous()
+            noise_step = state[6].data_ptr()
         return _lib.V1GState(z_buf.data_ptr(), v.data_ptr(), r.data_ptr(), asc.data_ptr(),
-                             psc_rise.data_ptr(), psc.data_ptr())
+                             psc_rise.data_ptr(), psc.data_ptr(), noise_step)
 
     # ---- reference operator interface ---------------------------------------------------
     @property
@@ -414,20 +430,33 @@ class V1Column:
     def calculate_input_current_from_spikes(self, x_t):
         return self._syn_currents(_lib.SRC_LGN, x_t)
 
-    def sample_bkg_counts(self, batch_size, n_steps=None):
-        """Poisson counts of the background nodes at ``rate*dt/1000`` per step.
+    def sample_bkg_counts(self, batch_size, n_steps=None, first_step=0):
+        """Poisson counts of the background nodes at ``bkg_firing_rate * dt / 1000`` per step, drawn by
+        the library's Philox sampler from ``(noise_seed + replica_id * 1000003, step)``, the key the
+        reference gives ``tf.random.stateless_poisson`` (``models.py:867-887``).  TensorFlow's random
+        stream itself is not reproduced, so runs that must match another implementation pass the
+        counts in explicitly.  ``[B, n_bkg]`` for ``n_steps=None``, else ``[B, n_steps, n_bkg]``."""
+        t_len = 1 if n_steps is None else int(n_steps)
+        out = torch.empty((batch_size, t_len, self.n_bkg), dtype=torch.int32, device=self.device)
+        self._check(self._lib.v1g_sample_bkg_counts(self._libh, batch_size, t_len, int(first_step),
+                                                    _ptr(out), _stream()))
+        return out[:, 0] if n_steps is None else out
 
-        The reference draws them inside ``calculate_noise_current`` with a TensorFlow stateless
-        Philox sampler; this stream is a different one (torch's), so runs that must match
-        another implementation pass the counts in explicitly.
-        """
-        shape = (batch_size, self.n_bkg) if n_steps is None else (batch_size, n_steps, self.n_bkg)
-        lam = torch.full(shape, self.bkg_firing_rate * 1e-3 * self._dt, device=self.device)
-        return torch.poisson(lam, generator=self._noise_gen).to(torch.int32)
+    def sample_lgn_spikes(self, rates, batch_size, seed):
+        """LGN spikes ``uniform < 1 - exp(-rates / 1000)`` (``stim_dataset.py:182-193``) as uint8
+        ``[B, T, n_lgn]`` from ``rates[T, n_lgn]`` (one table for all trials) or ``[B, T, n_lgn]``."""
+        rates = rates.to(torch.float32).contiguous()
+        stride = 0 if rates.dim() == 2 else rates.shape[1] * rates.shape[2]
+        t_len = rates.shape[-2]
+        out = torch.empty((batch_size, t_len, self.input_dim), dtype=torch.uint8, device=self.device)
+        self._check(self._lib.v1g_sample_lgn_spikes(self._libh, batch_size, t_len, _ptr(rates), stride,
+                                                    int(seed), _ptr(out), _stream()))
+        return out
 
     def calculate_noise_current(self, batch_size, noise_step=None, counts=None):
         if counts is None:
-            counts = self.sample_bkg_counts(batch_size)
+            step = int(noise_step[0]) if noise_step is not None else 0
+            counts = self.sample_bkg_counts(batch_size, first_step=step)
         return self._syn_currents(_lib.SRC_BKG, counts)
 
     def _dense_update_impl(self, batch_size, prev_z, v, r, asc, psc_rise, psc, rec_inputs):
@@ -476,15 +505,15 @@ class V1Column:
                 save_for_bwd=False):
         """``T`` steps in one persistent kernel.
 
-        ``x[B,T,n_lgn]`` uint8/bool LGN spikes, ``bkg_counts[B,T,n_bkg]`` int32 (sampled if
-        omitted).  ``state`` (a ``zero_state``-shaped tuple) is updated IN PLACE when given.
+        ``x[B,T,n_lgn]`` uint8/bool LGN spikes, ``bkg_counts[B,T,n_bkg]`` int32; without counts they
+        are drawn inside the library for the steps ``state[6][0]`` .. (``noise_step``; 0 without a
+        state).  ``state`` (a ``zero_state``-shaped tuple) is updated IN PLACE when given.
         Returns ``(z uint8 [B,T,N] or None, v float32 [B,T,N] or None)``.
         """
         b, t_len = x.shape[0], x.shape[1]
         x = x.to(torch.uint8).contiguous()
-        if bkg_counts is None:
-            bkg_counts = self.sample_bkg_counts(b, t_len)
-        bkg_counts = bkg_counts.to(torch.int32).contiguous()
+        if bkg_counts is not None:
+            bkg_counts = bkg_counts.to(torch.int32).contiguous()
         n = self._n_neurons
         z = torch.empty((b, t_len, n), dtype=torch.uint8, device=self.device) if return_z else None
         v = torch.empty((b, t_len, n), dtype=torch.float32, device=self.device) if return_v else None
@@ -492,6 +521,25 @@ class V1Column:
         self._saved = (x, bkg_counts) if save_for_bwd else None
         self._check(self._lib.v1g_rollout_fwd(self._libh, b, t_len, _ptr(x), _ptr(bkg_counts), st,
                                               _ptr(z), _ptr(v), int(save_for_bwd), _stream()))
+        return z, v
+
+    def rollout_rates(self, rates, lgn_seed, batch_size, bkg_counts=None, state=None, return_z=True,
+                      return_v=True, save_for_bwd=False):
+        """``rollout`` with the LGN spikes drawn on the device from firing rates (``rates[T,n_lgn]``
+        for all trials or ``[B,T,n_lgn]``, Hz) straight into the kernels' event list; nothing but the
+        seed comes from the host."""
+        rates = rates.to(torch.float32).contiguous()
+        stride = 0 if rates.dim() == 2 else rates.shape[1] * rates.shape[2]
+        b, t_len, n = int(batch_size), rates.shape[-2], self._n_neurons
+        if bkg_counts is not None:
+            bkg_counts = bkg_counts.to(torch.int32).contiguous()
+        z = torch.empty((b, t_len, n), dtype=torch.uint8, device=self.device) if return_z else None
+        v = torch.empty((b, t_len, n), dtype=torch.float32, device=self.device) if return_v else None
+        st = C.byref(self._state_struct(state)) if state is not None else None
+        self._saved = (rates, bkg_counts) if save_for_bwd else None
+        self._check(self._lib.v1g_rollout_fwd_rates(self._libh, b, t_len, _ptr(rates), stride, int(lgn_seed),
+                                                    _ptr(bkg_counts), st, _ptr(z), _ptr(v), int(save_for_bwd),
+                                                    _stream()))
         return z, v
 
     def rollout_host(self, x_host, bkg_counts_host, want_z=True, want_v=False):

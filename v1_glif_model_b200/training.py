@@ -112,10 +112,31 @@ class Trainer:
                                      learning_rate=learning_rate)
         self._sel = sel
 
-    def step(self, x, bkg_counts):
-        """Forward rollout, BPTT, gradient all-reduce, Exp-Adam update.  Returns losses[4]."""
+    def step(self, x, bkg_counts=None, state=None):
+        """Forward rollout, BPTT, gradient all-reduce, Exp-Adam update.  Returns losses[4].
+
+        Without ``bkg_counts`` the background noise is drawn on the device and the noise seed is
+        advanced by one afterwards, as the reference's loop does once per rollout
+        (``tf_utils.py:235-237``, ``multi_training.py:380``).  ``state`` is the carried state the
+        rollout starts from (updated in place), e.g. the gray-screen state of
+        ``multi_training.py:812-831``."""
         self.grads.zero_()
-        self.cell.rollout(x, bkg_counts, return_z=False, return_v=False, save_for_bwd=True)
+        self.cell.rollout(x, bkg_counts, state=state, return_z=False, return_v=False, save_for_bwd=True)
+        if bkg_counts is None:
+            self.cell.set_noise_seed(self.cell.noise_seed + 1)
+        return self._finish_step()
+
+    def step_rates(self, rates, lgn_seed, batch_size, state=None):
+        """``step`` with both stochastic inputs drawn on the device: LGN spikes from the firing rates
+        ``rates[T,n_lgn]`` / ``[B,T,n_lgn]`` with ``lgn_seed``, background counts from the cell's noise
+        seed.  Nothing but the seeds comes from the host."""
+        self.grads.zero_()
+        self.cell.rollout_rates(rates, lgn_seed, batch_size, state=state, return_z=False, return_v=False,
+                                save_for_bwd=True)
+        self.cell.set_noise_seed(self.cell.noise_seed + 1)
+        return self._finish_step()
+
+    def _finish_step(self):
         if self.order == "internal":
             cell = self.cell
             losses = cell.backward_internal(self.loss, self.grads.flat, self._losses)
