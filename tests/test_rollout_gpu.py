@@ -243,7 +243,8 @@ def test_synchrony_samples_are_taken_from_every_call():
         losses.append(float(cell.backward(spec)[3][0]))
         del samples, spec
     cell.synchronize()
-    assert losses[0] != losses[1] and losses[0] == losses[2]
+    # equal lists give equal losses up to the order of the atomic sums; different lists do not
+    assert abs(losses[0] - losses[1]) > 1e-3 * abs(losses[0]) and abs(losses[0] - losses[2]) <= 1e-5 * abs(losses[0])
 
 
 @pytest.mark.parametrize("batch", [1, 4, 6, 8])

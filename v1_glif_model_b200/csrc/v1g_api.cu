@@ -112,6 +112,11 @@ static void free_source(V1GSource& s) {
   cudaFree(s.in_perm);
   cudaFree(s.w_in);
   cudaFree(s.w_ref);
+  for (int p = 0; p < 2; ++p) {
+    cudaFree(s.pair_ptr[p]);
+    cudaFree(s.pair_rec[p]);
+    cudaFree(s.pair_j[p]);
+  }
   s = V1GSource();
 }
 
@@ -269,6 +274,11 @@ extern "C" int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz,
   }
   s.post_sorted = sorted;
   s.in_ptr_host = in_ptr;
+  if (source == V1G_SRC_REC && want_syn8) {
+    s.rowptr_host = rowptr;
+    s.syn8x_host.resize((size_t)nnz);
+    for (int64_t i = 0; i < nnz; ++i) s.syn8x_host[(size_t)i] = syn8[(size_t)i].x;
+  }
   int rc;
   if ((rc = upload(h, &s.rowptr, rowptr.data(), rowptr.size()))) return rc;
   if ((rc = upload(h, &s.post, post.data(), post.size()))) return rc;
@@ -372,6 +382,57 @@ __global__ void permute_weights_kernel(const float* __restrict__ w_ref,
   for (; i < nnz; i += stride) w[i] = w_ref[perm[i]];
 }
 
+// weights into the gather-ordered record copies of the paired backward ring
+__global__ void pair_weights_kernel(const float* __restrict__ w, const int32_t* __restrict__ pos,
+                                    uint2* __restrict__ rec, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) rec[i].y = __float_as_uint(w[pos[i]]);
+}
+
+static void refresh_pair_weights(V1GSource& s, cudaStream_t st) {
+  if (!s.pair_built) return;
+  for (int p = 0; p < 2; ++p) {
+    if (s.pair_len[p] == 0) continue;
+    const int blocks = (int)std::min<int64_t>((s.pair_len[p] + 255) / 256, 148 * 16);
+    pair_weights_kernel<<<blocks, 256, 0, st>>>(s.w, s.pair_j[p], s.pair_rec[p], s.pair_len[p]);
+    v1g_count_launches(1);
+  }
+}
+
+int v1g_build_pair_tables(V1GHandle* h, cudaStream_t st) {
+  V1GSource& s = h->src[V1G_SRC_REC];
+  if (s.pair_built) return V1G_OK;
+  if (s.rowptr_host.empty() || !s.syn8)
+    return v1g_fail(h, V1G_ESTATE, "the paired backward ring needs the packed records of the recurrent source");
+  const int D = s.delays;
+  const int64_t n_src = s.n_src;
+  for (int p = 0; p < 2; ++p) {
+    std::vector<int32_t> ptr((size_t)n_src + 1), pos;
+    std::vector<uint2> rec;
+    pos.reserve((size_t)s.nnz);
+    for (int64_t n = 0; n < n_src; ++n) {
+      ptr[(size_t)n] = (int32_t)pos.size();
+      const int32_t* rp = s.rowptr_host.data() + n * D;
+      for (int j = rp[0]; j < rp[1]; ++j) pos.push_back(j);            // delay 1
+      for (int d = 1 + p; d < D; d += 2)                                // delays 2 + p, 4 + p, ...
+        for (int j = rp[d]; j < rp[d + 1]; ++j) pos.push_back(j);
+    }
+    ptr[(size_t)n_src] = (int32_t)pos.size();
+    rec.resize(pos.size());
+    for (size_t i = 0; i < pos.size(); ++i) rec[i] = make_uint2(s.syn8x_host[(size_t)pos[i]], 0u);
+    s.pair_len[p] = (int64_t)pos.size();
+    int rc;
+    if ((rc = upload(h, &s.pair_ptr[p], ptr.data(), ptr.size()))) return rc;
+    if ((rc = upload(h, &s.pair_rec[p], rec.data(), rec.size()))) return rc;
+    if ((rc = upload(h, &s.pair_j[p], pos.data(), pos.size()))) return rc;
+  }
+  s.pair_built = true;
+  refresh_pair_weights(s, st);
+  V1G_CUDA(h, cudaGetLastError());
+  return V1G_OK;
+}
+
 // copy the weights into the packed synapse records of the backward gather
 __global__ void syn8_weights_kernel(const float* __restrict__ w, uint2* __restrict__ syn8, int64_t nnz) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -400,6 +461,7 @@ extern "C" int v1g_set_weights(V1GHandle* h, int source, const float* w, void* s
     syn8_weights_kernel<<<blocks, threads, 0, st>>>(s.w, s.syn8, s.nnz);
     v1g_count_launches(1);
   }
+  refresh_pair_weights(s, st);
   if (!s.pos_set) {
     // the sign of each weight at construction is what SignedConstraint preserves (models.py:647-666)
     if (!s.pos_int) V1G_CUDA(h, cudaMalloc((void**)&s.pos_int, (size_t)s.nnz));
@@ -455,6 +517,7 @@ extern "C" int v1g_expadam_update_internal(V1GHandle* h, const float* grads_flat
         syn8_weights_kernel<<<blocks, 256, 0, st>>>(s.w, s.syn8, s.nnz);
         v1g_count_launches(1);
       }
+      refresh_pair_weights(s, st);
       if (src == V1G_SRC_BKG) {
         // the background weights also exist in caller's and CSR order (operator-level entry points)
         const int blocks = (int)std::min<int64_t>((s.nnz + 255) / 256, 148 * 16);

@@ -51,6 +51,16 @@ struct V1GSource {
   std::vector<int32_t> order_host;
   std::vector<int64_t> row_splits_host;
   std::vector<int32_t> in_ptr_host;  // host copy of in_ptr
+  // Recurrent source, built on first use of the paired backward ring: per delay parity p the records
+  // of every source neuron in gather order (its delay-1 bucket, then its buckets of delay d >= 2 with
+  // d - 1 = 1 + p, 3 + p, ...), the row starts and the CSR position of every entry.
+  std::vector<int32_t> rowptr_host;   // host copy of rowptr
+  std::vector<uint32_t> syn8x_host;   // host copy of the first word of syn8
+  int32_t* pair_ptr[2] = {nullptr, nullptr};  // [n_src + 1]
+  uint2* pair_rec[2] = {nullptr, nullptr};
+  int32_t* pair_j[2] = {nullptr, nullptr};
+  int64_t pair_len[2] = {0, 0};
+  bool pair_built = false;
 };
 
 struct V1GHandle {
@@ -153,6 +163,9 @@ void v1g_count_launches(int n);
 
 // message returned by v1g_last_error(NULL), for entry points that take no handle
 void v1g_set_global_error(const char* msg);
+
+// gather-ordered record tables of the recurrent source for the paired backward ring (built once)
+int v1g_build_pair_tables(V1GHandle* h, cudaStream_t st);
 
 #define V1G_CUDA(h, call)                                                              \
   do {                                                                                 \

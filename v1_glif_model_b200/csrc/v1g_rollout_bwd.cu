@@ -37,11 +37,13 @@
 // Everything read was published at least two iterations earlier, as in the unpaired loop, so the
 // lagged counters are unchanged.  Requests per reverse step: 0.2 + 0.8 / 2 of the unpaired count for
 // uniform delays 1..5.  Measured on B200 (66,634 neurons, batch 5, T=150, one launch each): L2 read
-// requests 645 M -> 409 M and the L1-to-L2 request port 52 % -> 25 % busy, but 4.33 G instead of
-// 2.20 G warp instructions (slot-to-synapse mapping, two accumulator sets) at 57 % issue utilisation:
-// 6.6 ms against 4.5 ms.  The unpaired loop is therefore the default; it is bound by the latency of
-// its dependent chains (20 % of stalls wait for L2, 30 % for shared memory and shuffles), not by
-// the request count.
+// requests 645 M -> 400 M, the L1-to-L2 request port 52 % -> 33 % busy and the L1 data pipe
+// 55 % -> 47 %, but 2.65 G instead of 2.20 G warp instructions (two steps' values to unpack and
+// accumulate per entry, a second warp reduction per row): 4.59 ms against 4.49 ms, and 40.3 against
+// 39.3 us per reverse step at T=500 (gather 26.7 against 28.8 us, tape phase 5.0 against 3.3 us).
+// The unpaired loop therefore stays the default: neither loop is bound by the request count; both
+// spend most of a turn of the software pipeline waiting on its dependent chain (queue pop, row
+// descriptor, records, Q rows, warp reduction), of which a warp runs one per row.
 #include <algorithm>
 #include <type_traits>
 
@@ -52,6 +54,12 @@ namespace {
 struct BwdArgs {
   int N, D, K, B, T, Np, chunk, chunkP, S, C, n_bkg, state_in_smem, bkg_in_smem, bkg_cap;
   int KP;  // paired mode: ring slots, each holding the steps (2p, 2p-1)
+  // paired mode: per delay parity p the synapse records of a neuron in gather order (delay-1 bucket,
+  // then the buckets of delay d >= 2 with d - 1 == 1 + p mod 2), row starts, and CSR position of every entry
+  const int32_t* pair_ptr[2];
+  const uint2* pair_rec[2];
+  const int32_t* pair_j[2];
+  int pair_last[2];  // last valid index of each record array (clamp for lanes past a row's end)
   const int32_t *rec_rowptr, *rec_post;
   const float* rec_w;
   const uint8_t* rec_sid;
@@ -107,7 +115,7 @@ struct BwdArgs {
 #define V1G_BWD_STAGES 2  // Q-row buffers of the gather pipeline (registers: 20 per stage)
 #endif
 #ifndef V1G_BWD_PAIR_GROUPS
-#define V1G_BWD_PAIR_GROUPS 4  // 32-lane groups of a pass of the paired gather
+#define V1G_BWD_PAIR_GROUPS 3  // 32-entry groups of a pass of the paired gather (32-byte rows)
 #endif
 constexpr int NT = V1G_BWD_NT;
 constexpr int NW = NT / 32;
@@ -175,6 +183,13 @@ __device__ __forceinline__ void load_row(const float* p, float (&q)[BP_]) {
 #pragma unroll
   for (int v = 0; v < (PACK ? 1 : BP_ / 4); ++v) raw[v] = __ldcg((const float4*)p + v);
   unpack_row<BP_, PACK>(raw, q);
+}
+
+// one 32-byte pair row {Q(tau), Q(tau-1)} with a single load instruction
+__device__ __forceinline__ void load_pair(const float* p, float4& lo, float4& hi) {
+  asm volatile("ld.global.cg.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w), "=f"(hi.x), "=f"(hi.y), "=f"(hi.z), "=f"(hi.w)
+               : "l"(p));
 }
 
 // the NB batch values of one 16-byte row: five 24-bit floats (PACK) or four fp32 words
@@ -267,12 +282,12 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   int* s_misc = (int*)take(sizeof(int) * 8);  // [1] abort flag, [2+p] rows queued, [4+p] next queue slot (p = parity of the iteration)
   int* slot_s = (int*)take(sizeof(int) * 8);  // first Q row of step t+1+d, d = 0..7
   uint16_t* rowq_s = (uint16_t*)take(PAIR ? 0 : sizeof(uint16_t) * chunkP);  // rows to walk this step
-  int4* rowd_s = (int4*)take(PAIR ? 0 : sizeof(int4) * chunkP);  // the same rows as {first synapse, end, row | spike mask << 16, 0}
-  // paired mode: rows to walk as row | single << 16 | spike mask(t-1) << 17 | spike mask(t-2) << 22
-  uint32_t* rowc_s = (uint32_t*)take(PAIR ? sizeof(uint32_t) * chunkP : 0);
-  // row pointers of the slice: on chip for the gathers that read them per row, from global
-  // memory (two loads per neuron and step) for the unpaired packed-record gather
-  const bool rp_on_chip = PAIR || !fast_rows;
+  // the same rows as {first synapse, end, row | spike mask << 16, 0}; paired mode: {first entry, end,
+  // row | spike mask(t-1) << 16 | spike mask(t-2) << 21, 0} over the gather-ordered records
+  int4* rowd_s = (int4*)take(sizeof(int4) * chunkP);
+  // row pointers of the slice: on chip for the gather that reads them per row pass, from global
+  // memory (two loads per neuron and step) for the packed-record gathers
+  const bool rp_on_chip = !fast_rows;
   int32_t* rp_s = (int32_t*)take(rp_on_chip ? sizeof(int32_t) * ((size_t)chunkP * D + 1) : 0);
   const int32_t* rpx = rp_on_chip ? rp_s : a.rec_rowptr + (int64_t)n0 * D;
   int* bkptr_s = (int*)take(sizeof(int) * (chunkP + 1));  // background in-synapse ranges, slice-relative
@@ -555,15 +570,13 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         base = __shfl_sync(0xffffffffu, base, 0);
         if (walk) {
           const unsigned zm1 = f1 >> 1, zm2 = f2 >> 1;
-          rowc_s[base + __popc(wm & ((1u << lane) - 1u))] =
-              (unsigned)tid | ((f1 & 1u) << 16) | (zm1 << 17) | (zm2 << 22);
-          const int32_t* rp = rp_s + tid * D;
-          const int len = (f1 & 1u) ? rp[1] - rp[0] : 0;
-          int lenc = 0;
-          for (int d = 1 + ((t - 1) & 1); d < D; d += 2) lenc += rp[d + 1] - rp[d];
+          const int32_t* pp = a.pair_ptr[(t - 1) & 1] + n0 + tid;
+          const int j0 = pp[0], j1 = pp[1];
+          rowd_s[base + __popc(wm & ((1u << lane) - 1u))] = make_int4(j0, j1, tid | (int)(zm1 << 16) | (int)(zm2 << 21), 0);
+          const int len1 = rpx[tid * D + 1] - rpx[tid * D];   // delay-1 entries (step t-1 only)
           c_rows += 1ull + (unsigned long long)((D - ((t - 1) & 1)) / 2);
-          c_events += (unsigned long long)(len + lenc);
-          c_dw += (unsigned long long)(len + lenc) * __popc(zm1) + (unsigned long long)lenc * __popc(zm2);
+          c_events += (unsigned long long)(j1 - j0);
+          c_dw += (unsigned long long)(j1 - j0) * __popc(zm1) + (unsigned long long)(j1 - j0 - len1) * __popc(zm2);
         }
       }
     } else
@@ -768,130 +781,100 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       return __shfl_sync(0xffffffffu, q, 0);
     };
     if (PAIR) {
-      // Paired gather.  A queued row contributes, in this iteration, its delay-1 bucket (step t-1 only,
-      // if that step needs the row) and the buckets of delay d >= 2 with t-1+d even (steps t-1 and t-2).
-      // The L1-to-L2 port counts one request per distinct 128-byte line of a load instruction, whatever
-      // the lanes' access width (a 256-bit load per lane costs two), so a synapse of delay >= 2 takes TWO
-      // ADJACENT LANES: the even one loads the first 16-byte half of the pair row (Q(t-1+d), for step
-      // t-1), the odd one the second half (Q(t-2+d), for step t-2) - one line, one request, two steps.
-      // A delay-1 synapse takes one lane.  These lane slots form one virtual row (delay-1 bucket padded
-      // to an even length, then two slots per synapse of the other buckets); a pass is UF*32 consecutive
-      // slots.  The software pipeline is the one of the unpaired path: records of the pass after next
-      // and Q halves of the next pass in flight while the current one is accumulated.
-      constexpr int NB = PACK ? 5 : BP_;                      // batch values a row carries
+      // Paired gather.  The records of a neuron are stored a second time in gather order, once per
+      // delay parity: its delay-1 bucket (serves step t-1 only) followed by the buckets of delay d >= 2
+      // with t-1+d even (one 32-byte pair row {Q(t-1+d), Q(t-2+d)} serves the steps t-1 and t-2).  A
+      // row is therefore one contiguous range, walked exactly like the unpaired packed-record path:
+      // passes of UF*32 entries, records of the pass after next and pair rows of the next pass in
+      // flight while the current one is accumulated.
+      constexpr int NB = PACK ? 5 : BP_;  // batch values a row carries
       constexpr int UF = V1G_BWD_PAIR_GROUPS, NS = 2;
-      constexpr int NSEG = 1 + (DT > 0 ? DT / 2 : V1G_MAX_DELAY / 2);  // delay-1 bucket + buckets of one parity
-      const int cpar = (t - 1) & 1;                           // first bucket of this iteration's parity is 1 + cpar
-      const unsigned half1 = (t & 1) ? 4u : 0u;               // words from the pair row to Q(t): second half when t is odd
-      float* const gz1 = gzB;                                 // spike gradient of step t-1: add
-      float* const gz2 = gzC;                                 // spike gradient of step t-2: first contribution
-      // sl[0] / sl[m]: SLOTS of the segment (delay-1 bucket rounded up to even; two per synapse else)
-      struct VRow { int ss[NSEG], sl[NSEG], n1, L, pos; unsigned code; int fl; };  // fl: 1 first pass, 2 last pass, 4 valid
-      struct CPass { unsigned code; int fl; };
-      VRow pr;
-      pr.n1 = 0; pr.L = 0; pr.pos = 0; pr.code = 0; pr.fl = 0;
-#pragma unroll
-      for (int m = 0; m < NSEG; ++m) pr.ss[m] = pr.sl[m] = 0;
-      CPass ps_[NS];
+      const int cpar = (t - 1) & 1;
+      const bool todd = t & 1;            // Q(t) is the second half of its pair when t is odd
+      const uint2* const prec = a.pair_rec[cpar];
+      const int plast = a.pair_last[cpar];
+      float* const gz1 = gzB;             // spike gradient of step t-1: add
+      float* const gz2 = gzC;             // spike gradient of step t-2: first contribution
+      struct Pass { int jb, j1, kz, fl; };  // kz = row | spike mask(t-1) << 16 | spike mask(t-2) << 21; fl: 1 first pass of its row, 4 valid
+      Pass pr{0, 0, 0, 0};
+      Pass ps_[NS];
       uint2 rec[UF];
-      int jR[UF];            // slot of the pass in `rec`: synapse * 4 + kind (1 delay 1, 2 first half, 3 second half), 0 = none
-      float4 qS[NS][UF];
+      float4 qLo[NS][UF], qHi[NS][UF];
       float wS[NS][UF];
-      int jS[NS][UF];
+      int cS[NS];           // bit u: entry u of the pass is a delay-1 entry
       float acc1[NB], acc2[NB];
 #pragma unroll
-      for (int i = 0; i < NS; ++i) ps_[i] = CPass{0u, 0};
+      for (int i = 0; i < NS; ++i) {
+        ps_[i] = Pass{0, 0, 0, 0};
+        cS[i] = 0;
+      }
 #pragma unroll
       for (int b = 0; b < NB; ++b) acc1[b] = acc2[b] = 0.f;
       auto issue_rec = [&]() {  // advance pr to the following pass and request its records
-        if (pr.fl && pr.pos + 32 * UF < pr.L) {
-          pr.pos += 32 * UF;
+        if (pr.fl && pr.jb + 32 * UF < pr.j1) {
+          pr.jb += 32 * UF;
           pr.fl = 4;
         } else {
           const int q = pop_row();
           if (q < nq) {
-            const unsigned code = rowc_s[q];
-            const int32_t* rp = rp_s + (int)(code & 0xffffu) * D;
-            pr.code = code;
-            pr.ss[0] = rp[0];
-            pr.n1 = (code & 0x10000u) ? rp[1] - rp[0] : 0;
-            pr.sl[0] = (pr.n1 + 1) & ~1;
-            pr.L = pr.sl[0];
-#pragma unroll
-            for (int m = 1; m < NSEG; ++m) {
-              const int d = 2 * m - 1 + cpar;      // bucket index = delay - 1
-              const bool has = d < D;
-              pr.ss[m] = has ? rp[has ? d : 0] : 0;
-              pr.sl[m] = has ? 2 * (rp[has ? d + 1 : 0] - pr.ss[m]) : 0;
-              pr.L += pr.sl[m];
-            }
-            pr.pos = 0;
-            pr.fl = 5;
+            const int4 d = rowd_s[q];
+            pr = Pass{d.x, d.y, d.z, 5};
           } else {
-            pr.fl = 0;
-            pr.L = 0;
+            pr = Pass{0, 0, 0, 0};
           }
         }
-        if (pr.fl && pr.pos + 32 * UF >= pr.L) pr.fl |= 2;
 #pragma unroll
-        for (int u = 0; u < UF; ++u) {
-          int r = pr.pos + u * 32 + lane;
-          int code = (pr.fl && r < pr.n1) ? (pr.ss[0] + r) * 4 + 1 : 0;
-          r -= pr.sl[0];
-#pragma unroll
-          for (int m = 1; m < NSEG; ++m) {
-            code = (r >= 0 && r < pr.sl[m]) ? (pr.ss[m] + (r >> 1)) * 4 + 2 + (r & 1) : code;
-            r -= pr.sl[m];
-          }
-          jR[u] = pr.fl ? code : 0;
-          rec[u] = __ldcs(a.rec_syn8 + (jR[u] >> 2));
-        }
+        for (int u = 0; u < UF; ++u) rec[u] = __ldcs(prec + min(pr.jb + u * 32 + lane, plast));
       };
-      auto issue_q = [&](float4 (&q)[UF], float (&w)[UF], int (&js)[UF]) {
+      auto issue_q = [&](const Pass& ps, float4 (&lo)[UF], float4 (&hi)[UF], float (&w)[UF], int& c) {
+        c = 0;
 #pragma unroll
         for (int u = 0; u < UF; ++u) {
-          const int kind = jR[u] & 3;
+          const bool in_row = ps.jb + u * 32 + lane < ps.j1;
           const unsigned w0 = rec[u].x;
           unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + ((w0 >> 22) & 127u);
-          unsigned word = row * 8u + (kind == 1 ? half1 : kind == 3 ? 4u : 0u);
-          word = kind ? word : 0u;  // slots without a synapse share one request
-          q[u] = __ldcg((const float4*)(a.Q + word));
-          w[u] = kind ? __uint_as_float(rec[u].y) : 0.f;
-          js[u] = jR[u];
+          row = in_row ? row : 0u;  // lanes past the end of the row share one request
+          load_pair(a.Q + (size_t)row * 8u, lo[u], hi[u]);
+          w[u] = in_row ? __uint_as_float(rec[u].y) : 0.f;
+          c |= ((w0 >> 29) == 0u) ? (1 << u) : 0;
         }
       };
-      auto compute = [&](const CPass& ps, const float4 (&q)[UF], const float (&w)[UF], const int (&js)[UF]) {
+      auto compute = [&](const Pass& ps, const float4 (&lo)[UF], const float4 (&hi)[UF], const float (&w)[UF],
+                         const int c) {
         if (ps.fl & 1) {
 #pragma unroll
           for (int b = 0; b < NB; ++b) acc1[b] = acc2[b] = 0.f;
         }
-        const unsigned zm1 = (ps.code >> 17) & 31u, zm2 = (ps.code >> 22) & 31u;
+        const unsigned zm1 = ((unsigned)ps.kz >> 16) & 31u, zm2 = ((unsigned)ps.kz >> 21) & 31u;
 #pragma unroll
         for (int u = 0; u < UF; ++u) {
-          float pj[NB];
-          unpack_half<NB, PACK>(q[u], pj);
-          const int kind = js[u] & 3;
-          const float w1 = kind == 3 ? 0.f : w[u], w2 = kind == 3 ? w[u] : 0.f;
+          float pl[NB], ph[NB];
+          unpack_half<NB, PACK>(lo[u], pl);
+          unpack_half<NB, PACK>(hi[u], ph);
+          const bool d1 = (c >> u) & 1;
+          const bool sw = d1 && todd;      // delay 1 with Q(t) in the second half
+          const float w2 = d1 ? 0.f : w[u];
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
-            acc1[b] += w1 * pj[b];
-            acc2[b] += w2 * pj[b];
+            acc1[b] += w[u] * (sw ? ph[b] : pl[b]);
+            acc2[b] += w2 * ph[b];
           }
           if (zm1 | zm2) {
-            // the source neuron spiked at step t-1 (zm1) or t-2 (zm2): recurrent weight gradient; the two
-            // halves of a synapse are added up by its first lane, which is its only writer
-            const unsigned zm = kind == 3 ? zm2 : zm1;
-            float dwv = 0.f;
+            // the source neuron spiked at step t-1 (zm1) or t-2 (zm2): recurrent weight gradient
+            const int js = ps.jb + u * 32 + lane;
+            if (js < ps.j1) {
+              float dwv = 0.f;
 #pragma unroll
-            for (int b = 0; b < NB; ++b)
-              if (zm & (1u << b)) dwv += pj[b];
-            const float other = __shfl_down_sync(0xffffffffu, dwv, 1);
-            if (kind == 2) dwv += other;
-            if (kind == 1 || kind == 2) a.dw_rec[js[u] >> 2] += dwv;
+              for (int b = 0; b < NB; ++b) {
+                if (zm1 & (1u << b)) dwv += sw ? ph[b] : pl[b];
+                if (!d1 && (zm2 & (1u << b))) dwv += ph[b];
+              }
+              a.dw_rec[a.pair_j[cpar][js]] += dwv;  // this lane is the only writer of the synapse
+            }
           }
         }
-        if (ps.fl & 2) {
-          const int k = (int)(ps.code & 0xffffu);
+        if (ps.jb + 32 * UF >= ps.j1) {
+          const int k = ps.kz & 0xffff;
           float v8[8];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -917,15 +900,15 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
 #pragma unroll
           for (int o = 1; o < NS; ++o)
             if (ps_[(i + o) % NS].fl)
-              compute(ps_[(i + o) % NS], qS[(i + o) % NS], wS[(i + o) % NS], jS[(i + o) % NS]);
+              compute(ps_[(i + o) % NS], qLo[(i + o) % NS], qHi[(i + o) % NS], wS[(i + o) % NS], cS[(i + o) % NS]);
           return false;
         }
-        ps_[i] = CPass{pr.code, pr.fl};
-        issue_q(qS[i], wS[i], jS[i]);
+        ps_[i] = pr;
+        issue_q(ps_[i], qLo[i], qHi[i], wS[i], cS[i]);
         issue_rec();
         constexpr int x = (i + 1) % NS;  // the oldest pass
         if (ps_[x].fl) {
-          compute(ps_[x], qS[x], wS[x], jS[x]);
+          compute(ps_[x], qLo[x], qHi[x], wS[x], cS[x]);
           ps_[x].fl = 0;
         }
         return true;
@@ -1393,13 +1376,16 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   const bool fast = proj && !h->opt_no_meta && h->src[V1G_SRC_REC].syn8 != nullptr &&
                     h->src[V1G_SRC_REC].nnz > 0;  // packed-record gather
   // paired rows (two steps per 32-byte row): 16-byte rows, packed records, one neuron per thread
-  const bool pair = fast && QW == 4 && plan.chunk <= NT && h->opt_pair_rows;
+  bool pair = fast && QW == 4 && plan.chunk <= NT && h->opt_pair_rows;
   const int KP = ((D + 3) >> 1) + 1;  // pair slots covering D+3 consecutive steps at either alignment
+  if (pair && (rc = v1g_build_pair_tables(h, st))) return rc;
+  // a delay parity without any entry leaves nothing to clamp the lanes past a row's end to
+  if (pair && std::min(h->src[V1G_SRC_REC].pair_len[0], h->src[V1G_SRC_REC].pair_len[1]) < 1) pair = false;
   size_t smem = al(sizeof(float) * S * R) + 2 * al(sizeof(float) * 2 * plane) + al(pair ? 0 : 2 * plane) +
                 al(pair ? 2 * plan.chunkP : plan.chunkP) + al(sizeof(int) * B * c.n_bkg) + al(sizeof(int) * 8) +
                 al(sizeof(int) * 8) + al(pair ? 0 : sizeof(uint16_t) * plan.chunkP) +
-                al(pair ? 0 : sizeof(int4) * plan.chunkP) + al(pair ? sizeof(uint32_t) * plan.chunkP : 0) +
-                ((fast && !pair) ? 0 : al(sizeof(int32_t) * ((size_t)plan.chunkP * D + 1))) +
+                al(sizeof(int4) * plan.chunkP) +
+                (fast ? 0 : al(sizeof(int32_t) * ((size_t)plan.chunkP * D + 1))) +
                 al(sizeof(int) * (plan.chunkP + 1));
   const size_t state_bytes = al(sizeof(float) * plane * (3 + 2 * R));
   int state_in_smem = 0;
@@ -1496,6 +1482,13 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   const V1GSource& bk = h->src[V1G_SRC_BKG];
   a.rec_rowptr = rs.rowptr; a.rec_post = rs.post; a.rec_w = rs.w; a.rec_sid = rs.sid;
   a.rec_syn8 = fast ? rs.syn8 : nullptr;
+  for (int p2 = 0; p2 < 2; ++p2) {
+    a.pair_ptr[p2] = rs.pair_ptr[p2];
+    a.pair_rec[p2] = rs.pair_rec[p2];
+    a.pair_j[p2] = rs.pair_j[p2];
+  }
+  a.pair_last[0] = (int)rs.pair_len[0] - 1;
+  a.pair_last[1] = (int)rs.pair_len[1] - 1;
   a.rec_nnz = (int)rs.nnz;
   a.lgn_rowptr = lsrc.rowptr; a.lgn_post = lsrc.post; a.lgn_sid = lsrc.sid;
   a.bkg_inptr = bk.in_ptr; a.bkg_inpre = bk.in_pre; a.bkg_insid = bk.in_sid;
