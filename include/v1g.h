@@ -318,6 +318,19 @@ int v1g_rollout_fwd_host(V1GHandle* h, int32_t batch, int32_t n_steps, const uin
                          const int32_t* bkg_counts_host, uint8_t* z_out_host, float* v_out_host,
                          int32_t save_for_bwd, void* stream);
 
+/* Forward-only evaluation through HOST buffers at full device speed: the rollout runs from the zero
+ * state in chunks of chunk_steps steps (0 = automatic) with the state carried on the device, while
+ * the inputs of the next chunk and the spikes of the previous one travel on two further streams.
+ * z_format 0: z_out_host[B,T,N] uint8 as the reference's evaluator stores them
+ * (osi_dsi_estimator.py:297-305); z_format 1: z_out_host[B,T,ceil(N/32)] uint32 with the spike of
+ * neuron n in bit n % 32 of word n / 32 (an eighth of the bytes to copy).  z_out_host may be NULL.
+ * The copies overlap with the computation only when the host buffers are pinned (page-locked);
+ * pageable buffers work but are copied at the speed of a staged copy.  Returns after all results
+ * have arrived. */
+int v1g_rollout_fwd_host_pipelined(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x_host,
+                                   const int32_t* bkg_counts_host, void* z_out_host, int32_t z_format,
+                                   int32_t chunk_steps, void* stream);
+
 /* BPTT over the saved rollout (tape.gradient in multi_training.py:493).  The loss is the
  * in-kernel specification plus optional explicit gradients g_z[B,T,N], g_v[B,T,N] (nullable).
  * Weight gradients are ACCUMULATED into d_w_* (caller zeroes them), each in its source's synapse

@@ -112,6 +112,25 @@ def test_rollout_through_host_buffers():
     assert rel_err(v_host, v_dev) <= TOL_STATE
 
 
+@pytest.mark.parametrize("pinned", [False, True])
+def test_pipelined_rollout_through_host_buffers(pinned):
+    """The chunked, copy-overlapped host entry point returns the spikes of the plain device rollout,
+    as bytes and as one bit per neuron-step, for ragged chunk lengths and pageable or pinned inputs."""
+    cfg, dicts, orc, cell = _cells("small")
+    x, c = make_inputs(cfg, seq_len=60)
+    z_dev, _ = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda())
+    want = z_dev.cpu()
+    xh, ch = (torch.from_numpy(x).pin_memory(), torch.from_numpy(c).pin_memory()) if pinned else (x, c)
+    for chunk in (0, 17, 60, 1):
+        got = cell.rollout_host_pipelined(xh, ch, z_format="uint8", chunk_steps=chunk)
+        assert torch.equal(got, want), chunk
+        bits = cell.rollout_host_pipelined(xh, ch, z_format="bits", chunk_steps=chunk).numpy().view(np.uint32)
+        n = cfg.n_neurons
+        unpacked = ((bits[..., :, None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(*bits.shape[:2], -1)[..., :n]
+        assert np.array_equal(unpacked.astype(np.uint8), want.numpy()), chunk
+        assert not np.any(((bits[..., -1] >> np.uint32(n % 32)) != 0) & (n % 32 != 0))   # padding bits are zero
+
+
 def test_golden_fixture_forward_and_gradients():
     g = np.load(os.path.join(ROOT, "tests", "golden", "tiny_rollout.npz"))
     cfg, dicts, orc, cell = _cells("tiny", **KW)

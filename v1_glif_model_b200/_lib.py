@@ -84,6 +84,7 @@ SIGNATURES = {
     "v1g_rollout_fwd": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, C.POINTER(V1GState), _P, _P,
                                   C.c_int32, _P]),
     "v1g_rollout_fwd_host": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P, _P, C.c_int32, _P]),
+    "v1g_rollout_fwd_host_pipelined": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P, C.c_int32, C.c_int32, _P]),
     "v1g_rollout_bwd": (C.c_int, [_P, C.POINTER(V1GLossSpec), _P, _P, _P, _P, _P, _P, _P]),
     "v1g_expadam_update": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64, C.c_float, C.c_float,
                                      C.c_float, C.c_float, C.c_int64, C.c_float, _P]),

@@ -157,6 +157,12 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   cudaFree(h->stage_counts);
   cudaFree(h->stage_z);
   cudaFree(h->stage_v);
+  cudaFree(h->stage_bits);
+  cudaFree(h->pipe_state);
+  if (h->pipe_in) cudaStreamDestroy(h->pipe_in);
+  if (h->pipe_out) cudaStreamDestroy(h->pipe_out);
+  for (int i = 0; i < 6; ++i)
+    if (h->pipe_ev[i]) cudaEventDestroy(h->pipe_ev[i]);
   cudaFree(h->phase_ns);
   for (int i = 0; i < 4; ++i)
     if (h->ev[i]) cudaEventDestroy(h->ev[i]);

@@ -137,6 +137,13 @@ struct V1GHandle {
   uint8_t* stage_z = nullptr;
   float* stage_v = nullptr;
   int64_t stage_x_cap = 0, stage_counts_cap = 0, stage_z_cap = 0, stage_v_cap = 0;
+  // pipelined host-buffer entry point: copy streams, events, bit-packed spikes, carried state
+  cudaStream_t pipe_in = nullptr, pipe_out = nullptr;
+  cudaEvent_t pipe_ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  uint32_t* stage_bits = nullptr;
+  int64_t stage_bits_cap = 0;
+  float* pipe_state = nullptr;
+  int64_t pipe_state_cap = 0;
   // tuning (tests shrink these to exercise multi-block paths on tiny nets)
   int opt_chunk = 0;          // neurons per block in the rollout kernels (0 = auto)
   int opt_force_global = 0;   // keep rollout state in global memory even if it fits on chip

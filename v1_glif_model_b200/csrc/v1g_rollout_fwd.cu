@@ -746,3 +746,125 @@ extern "C" int v1g_rollout_fwd_host(V1GHandle* h, int32_t batch, int32_t n_steps
                                 cudaMemcpyDeviceToHost, st));
   return v1g_synchronize(h, st);
 }
+
+
+// ------------------------------------------------------------------------------------------
+// Forward-only evaluation through host buffers, pipelined
+// ------------------------------------------------------------------------------------------
+namespace {
+// z[rows][N] uint8 -> bits[rows][nw] uint32 (bit n % 32 of word n / 32): one warp per 32 words,
+// a ballot per word, one coalesced store of the 32 words
+__global__ void __launch_bounds__(256) pack_bits_kernel(const uint8_t* __restrict__ z, int64_t rows, int N, int nw,
+                                                        uint32_t* __restrict__ bits) {
+  const int lane = threadIdx.x & 31;
+  const int64_t groups_per_row = (nw + 31) / 32;
+  const int64_t n_groups = rows * groups_per_row;
+  for (int64_t g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); g < n_groups;
+       g += (int64_t)gridDim.x * (blockDim.x >> 5)) {
+    const int64_t row = g / groups_per_row;
+    const int w0 = (int)(g - row * groups_per_row) * 32;
+    const uint8_t* zr = z + row * N;
+    uint32_t mine = 0;
+    for (int i = 0; i < 32; ++i) {
+      const int n = (w0 + i) * 32 + lane;
+      const unsigned bal = __ballot_sync(0xffffffffu, n < N && zr[n] != 0);
+      if (i == lane) mine = bal;
+    }
+    if (w0 + lane < nw) bits[row * nw + w0 + lane] = mine;
+  }
+}
+}  // namespace
+
+extern "C" int v1g_rollout_fwd_host_pipelined(V1GHandle* h, int32_t batch, int32_t n_steps, const uint8_t* x_host,
+                                              const int32_t* bkg_counts_host, void* z_out_host, int32_t z_format,
+                                              int32_t chunk_steps, void* stream) {
+  if (!h) return V1G_EINVAL;
+  if (batch <= 0 || batch > V1G_MAX_BATCH || n_steps < 0 || !x_host || !bkg_counts_host || z_format < 0 ||
+      z_format > 1 || chunk_steps < 0)
+    return v1g_fail(h, V1G_EINVAL, "v1g_rollout_fwd_host_pipelined: bad argument");
+  if (n_steps == 0) return V1G_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const V1GConfig& c = h->cfg;
+  const int B = batch, T = n_steps, N = c.n_neurons, R = c.n_receptors, D = c.max_delay;
+  const int nw = (N + 31) / 32;
+  int ct = chunk_steps > 0 ? chunk_steps : std::min(std::max(T / 10, 50), 500);
+  ct = std::min(ct, T);
+  int rc;
+  // streams and events of the pipeline
+  if (!h->pipe_in) {
+    V1G_CUDA(h, cudaStreamCreateWithFlags(&h->pipe_in, cudaStreamNonBlocking));
+    V1G_CUDA(h, cudaStreamCreateWithFlags(&h->pipe_out, cudaStreamNonBlocking));
+    for (int i = 0; i < 6; ++i) V1G_CUDA(h, cudaEventCreateWithFlags(&h->pipe_ev[i], cudaEventDisableTiming));
+  }
+  cudaEvent_t* in_ready = h->pipe_ev;      // [2] inputs of the buffer are on the device
+  cudaEvent_t* done = h->pipe_ev + 2;      // [2] the rollout over the buffer has finished
+  cudaEvent_t* out_done = h->pipe_ev + 4;  // [2] the results of the buffer are on the host
+  // double buffers and the carried state
+  const int64_t nx = (int64_t)B * ct * c.n_lgn, nc = (int64_t)B * ct * c.n_bkg, nz = (int64_t)B * ct * N;
+  const int64_t nb = (int64_t)B * ct * nw;
+  if ((rc = v1g_reserve(h, &h->stage_x, &h->stage_x_cap, 2 * nx))) return rc;
+  if ((rc = v1g_reserve(h, &h->stage_counts, &h->stage_counts_cap, 2 * nc))) return rc;
+  if (z_out_host && (rc = v1g_reserve(h, &h->stage_z, &h->stage_z_cap, 2 * nz))) return rc;
+  if (z_out_host && z_format == 1 && (rc = v1g_reserve(h, &h->stage_bits, &h->stage_bits_cap, 2 * nb))) return rc;
+  const int64_t sf = (int64_t)B * N * (D + 1 + 2 + 2 * R);  // z_buf, v, asc, psc_rise, psc
+  if ((rc = v1g_reserve(h, &h->pipe_state, &h->pipe_state_cap, sf + ((int64_t)B * N + 3) / 4))) return rc;
+  V1G_CUDA(h, cudaMemsetAsync(h->pipe_state, 0, (size_t)(sf + ((int64_t)B * N + 3) / 4) * sizeof(float), st));
+  V1GState state;
+  state.z_buf = h->pipe_state;
+  state.v = state.z_buf + (int64_t)B * N * D;
+  state.asc = state.v + (int64_t)B * N;
+  state.psc_rise = state.asc + (int64_t)B * N * 2;
+  state.psc = state.psc_rise + (int64_t)B * N * R;
+  state.r = (int8_t*)(state.psc + (int64_t)B * N * R);
+  state.noise_step = nullptr;
+  // the side streams start after what is queued on the caller's stream
+  V1G_CUDA(h, cudaEventRecord(done[0], st));
+  V1G_CUDA(h, cudaEventRecord(done[1], st));
+  V1G_CUDA(h, cudaEventRecord(out_done[0], st));
+  V1G_CUDA(h, cudaEventRecord(out_done[1], st));
+  const int n_chunks = (T + ct - 1) / ct;
+  auto copy_in = [&](int k) -> int {
+    const int s = k & 1, t0 = k * ct, len = std::min(ct, T - t0);
+    V1G_CUDA(h, cudaStreamWaitEvent(h->pipe_in, done[s], 0));  // the rollout that read this buffer is through
+    V1G_CUDA(h, cudaMemcpy2DAsync(h->stage_x + s * nx, (size_t)len * c.n_lgn, x_host + (int64_t)t0 * c.n_lgn,
+                                  (size_t)T * c.n_lgn, (size_t)len * c.n_lgn, B, cudaMemcpyHostToDevice, h->pipe_in));
+    V1G_CUDA(h, cudaMemcpy2DAsync(h->stage_counts + s * nc, (size_t)len * c.n_bkg * 4,
+                                  bkg_counts_host + (int64_t)t0 * c.n_bkg, (size_t)T * c.n_bkg * 4,
+                                  (size_t)len * c.n_bkg * 4, B, cudaMemcpyHostToDevice, h->pipe_in));
+    V1G_CUDA(h, cudaEventRecord(in_ready[s], h->pipe_in));
+    return V1G_OK;
+  };
+  if ((rc = copy_in(0))) return rc;
+  for (int k = 0; k < n_chunks; ++k) {
+    const int s = k & 1, t0 = k * ct, len = std::min(ct, T - t0);
+    if (k + 1 < n_chunks && (rc = copy_in(k + 1))) return rc;
+    V1G_CUDA(h, cudaStreamWaitEvent(st, in_ready[s], 0));
+    V1G_CUDA(h, cudaStreamWaitEvent(st, out_done[s], 0));  // the previous results of this buffer have left
+    uint8_t* zc = z_out_host ? h->stage_z + s * nz : nullptr;
+    if ((rc = rollout_fwd_impl(h, B, len, h->stage_x + s * nx, nullptr, h->stage_counts + s * nc, &state, zc,
+                               nullptr, 0, st)))
+      return rc;
+    if (z_out_host && z_format == 1) {
+      const int64_t rows = (int64_t)B * len;
+      pack_bits_kernel<<<(unsigned)std::min<int64_t>((rows * ((nw + 31) / 32) + 7) / 8, (int64_t)h->n_sms * 16), 256, 0,
+                         st>>>(zc, rows, N, nw, h->stage_bits + s * nb);
+      v1g_count_launches(1);
+      V1G_CUDA(h, cudaGetLastError());
+    }
+    V1G_CUDA(h, cudaEventRecord(done[s], st));
+    if (z_out_host) {
+      V1G_CUDA(h, cudaStreamWaitEvent(h->pipe_out, done[s], 0));
+      if (z_format == 1)
+        V1G_CUDA(h, cudaMemcpy2DAsync((uint32_t*)z_out_host + (int64_t)t0 * nw, (size_t)T * nw * 4,
+                                      h->stage_bits + s * nb, (size_t)len * nw * 4, (size_t)len * nw * 4, B,
+                                      cudaMemcpyDeviceToHost, h->pipe_out));
+      else
+        V1G_CUDA(h, cudaMemcpy2DAsync((uint8_t*)z_out_host + (int64_t)t0 * N, (size_t)T * N, zc, (size_t)len * N,
+                                      (size_t)len * N, B, cudaMemcpyDeviceToHost, h->pipe_out));
+      V1G_CUDA(h, cudaEventRecord(out_done[s], h->pipe_out));
+    }
+  }
+  V1G_CUDA(h, cudaStreamSynchronize(h->pipe_out));
+  V1G_CUDA(h, cudaStreamSynchronize(h->pipe_in));
+  return v1g_synchronize(h, st);
+}

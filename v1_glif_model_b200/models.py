@@ -555,6 +555,31 @@ class V1Column:
             z.ctypes.data if want_z else None, v.ctypes.data if want_v else None, 0, _stream()))
         return z, v
 
+    def rollout_host_pipelined(self, x_host, bkg_counts_host, z_format="uint8", chunk_steps=0):
+        """Forward-only evaluation from host buffers (``osi_dsi_estimator.py:280-305``) with input
+        copies, computation and result copies overlapped.  ``x_host`` / ``bkg_counts_host``: NumPy
+        arrays or CPU tensors, ``[B,T,n_lgn]`` uint8 and ``[B,T,n_bkg]`` int32; pinned tensors are
+        copied at full speed.  Returns a PINNED CPU tensor that the cell reuses on the next call with
+        the same shape: ``[B,T,N]`` uint8, or for ``z_format="bits"`` ``[B,T,ceil(N/32)]`` int32 with
+        the spike of neuron ``n`` in bit ``n % 32`` of word ``n // 32``."""
+        xt = x_host if isinstance(x_host, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(x_host, dtype=np.uint8))
+        ct = bkg_counts_host if isinstance(bkg_counts_host, torch.Tensor) else \
+            torch.from_numpy(np.ascontiguousarray(bkg_counts_host, dtype=np.int32))
+        assert xt.dtype == torch.uint8 and ct.dtype == torch.int32 and xt.is_contiguous() and ct.is_contiguous()
+        b, t_len, n = xt.shape[0], xt.shape[1], self._n_neurons
+        bits = z_format == "bits"
+        shape = (b, t_len, (n + 31) // 32) if bits else (b, t_len, n)
+        cache = self.__dict__.setdefault("_host_out", {})
+        out = cache.get((bits, shape))
+        if out is None:
+            out = torch.empty(shape, dtype=torch.int32 if bits else torch.uint8).pin_memory()
+            cache.clear()
+            cache[(bits, shape)] = out
+        self._check(self._lib.v1g_rollout_fwd_host_pipelined(
+            self._libh, b, t_len, xt.data_ptr(), ct.data_ptr(), out.data_ptr(), 1 if bits else 0,
+            int(chunk_steps), _stream()))
+        return out
+
     def backward(self, loss=None, g_z=None, g_v=None, accumulate_into=None):
         """BPTT over the rollout saved by ``rollout(..., save_for_bwd=True)``.
 
