@@ -369,6 +369,31 @@ int v1g_expadam_update_internal(V1GHandle* h, const float* grads_flat, float* m_
                                 int32_t train_mask, float lr, float beta1, float beta2, float eps,
                                 int64_t step, float grad_scale, void* stream);
 
+/* Weight regularisers of the reference on a weight vector w[n] whose synapses carry an integer group
+ * id (the edge type): value ADDED to loss_out[0] (device, nullable), gradient ACCUMULATED into grad[n].
+ * w, group_ids and grad share one synapse order, whichever it is.
+ *   kind 0  MeanStiffRegularizer (loss_functions.py:171-220): strength * mean_g (mean_g(w) - target[g])^2;
+ *           with denominator != NULL (penalize_relative_change, max(|initial mean|, 1e-4))
+ *           strength * sqrt(mean_g ((mean_g(w) - target[g]) / denominator[g])^2).  target[n_groups].
+ *   kind 1  EarthMoversDistanceRegularizer (loss_functions.py:536-601): strength * mean_g mean_i
+ *           |sort(w_g)_i - y_g,i|.  target[n] = the initial weights sorted ascending inside each group,
+ *           groups in ascending id order; group_offsets[n_groups + 1] = where each group starts in it.
+ * All pointers are device pointers. */
+int v1g_weight_regularizer(V1GHandle* h, int32_t kind, const float* w, const int32_t* group_ids, int64_t n,
+                           int32_t n_groups, const float* target, const int32_t* group_offsets,
+                           const float* denominator, float strength, float* loss_out, float* grad,
+                           void* stream);
+
+/* perm_out_host[i] (HOST, [nnz]) = position, in the caller's synapse arrays, of the synapse that the
+ * library's internal order of a source holds at position i: what converts per-synapse tables (such as
+ * the group ids above) to the order of v1g_rollout_bwd_internal's gradient buffer. */
+int v1g_get_internal_order(V1GHandle* h, int source, int32_t* perm_out_host);
+
+/* Device address of the weights the kernels read, in the library's internal order (read-only view;
+ * stays valid until the connectivity of the source is set again).  What a regulariser evaluated in
+ * the internal order takes as w. */
+int v1g_internal_weights(V1GHandle* h, int source, const float** w_out);
+
 /* Current weights of a source in the caller's synapse order (device pointer, [nnz]). */
 int v1g_get_weights(V1GHandle* h, int source, float* w_out, void* stream);
 

@@ -163,3 +163,43 @@ def orientation_selectivity_loss(z, angle, tuning_angle, type_ids, osi_targets, 
     cnt = torch.as_tensor(type_counts, dtype=dt)
     per_type = (osi - torch.as_tensor(osi_targets, dtype=dt)) ** 2 + (dsi - torch.as_tensor(dsi_targets, dtype=dt)) ** 2
     return cost * loss_scale * (per_type * cnt).sum() / cnt.sum()
+
+
+def regularizer_groups(edge_type_ids):
+    """``(idx, n_groups, order, row_splits)``: dense group index per synapse (``np.unique(...,
+    return_inverse=True)``), and the synapse positions grouped by it with the original order kept
+    inside a group (``_build_group_order_numba``, ``loss_functions.py:20-61``)."""
+    import numpy as np
+    _, idx = np.unique(np.asarray(edge_type_ids), return_inverse=True)
+    n_groups = int(idx.max()) + 1 if idx.size else 0
+    order = np.argsort(idx, kind="stable")
+    row_splits = np.concatenate([[0], np.cumsum(np.bincount(idx, minlength=n_groups))])
+    return idx.astype(np.int64), n_groups, order.astype(np.int64), row_splits.astype(np.int64)
+
+
+def mean_stiff_regularizer(w, idx, n_groups, initial_weights, strength, relative=False):
+    """``MeanStiffRegularizer`` (``loss_functions.py:171-220``): the mean weight per edge type against
+    the mean of the initial weights; ``relative`` = ``penalize_relative_change`` (deviation divided by
+    ``max(|initial mean|, 1e-4)``, root of the mean square)."""
+    idx_t = torch.as_tensor(idx, dtype=torch.int64)
+    w0 = torch.as_tensor(initial_weights, dtype=w.dtype)
+    cnt = torch.zeros(n_groups, dtype=w.dtype).index_add(0, idx_t, torch.ones_like(w0))
+    target = torch.zeros(n_groups, dtype=w.dtype).index_add(0, idx_t, w0) / cnt
+    mean = torch.zeros(n_groups, dtype=w.dtype).index_add(0, idx_t, w) / torch.clamp(cnt, min=1.0)
+    if relative:
+        denom = torch.clamp(target.abs(), min=1e-4)
+        return strength * torch.sqrt(torch.mean(((mean - target) / denom) ** 2))
+    return strength * torch.mean((mean - target) ** 2)
+
+
+def emd_regularizer(w, order, row_splits, initial_weights, strength):
+    """``EarthMoversDistanceRegularizer`` (``loss_functions.py:536-601``): per edge type the mean
+    absolute difference between the sorted current and the sorted initial weights, averaged over the
+    types."""
+    w0 = torch.as_tensor(initial_weights, dtype=w.dtype)
+    order_t = torch.as_tensor(order, dtype=torch.int64)
+    terms = []
+    for g in range(len(row_splits) - 1):
+        sel = order_t[int(row_splits[g]):int(row_splits[g + 1])]
+        terms.append((torch.sort(w[sel]).values - torch.sort(w0[sel]).values).abs().mean())
+    return strength * torch.stack(terms).mean()

@@ -153,8 +153,48 @@ def osi_fixture(ref_root):
     print(f"wrote {path}")
 
 
+def regularizer_fixture(ref_root):
+    """The reference's weight regularisers (``MeanStiffRegularizer`` in both forms,
+    ``loss_functions.py:171-220``, and ``EarthMoversDistanceRegularizer``, ``:536-601``) built from the
+    600-neuron synthetic net with seeded edge types, evaluated on perturbed weights: value and gradient
+    with respect to the weights (fp64)."""
+    lf = load_reference_losses(ref_root)
+    sys.modules["other_v1_utils"].connection_type_ids = lambda network: network["synapses"]["edge_type_ids"]
+    tf_standin.set_policy_dtype(torch.float64)
+    cfg = synth.CONFIGS["small"]
+    net, _, _ = synth.make_network(cfg, 4)
+    rng = np.random.Generator(np.random.PCG64(21))
+    nnz = net["synapses"]["indices"].shape[0]
+    # edge types with gaps in their ids and very different sizes, one with a single synapse
+    edge_types = rng.choice(np.array([3, 4, 9, 17, 18, 40, 41, 77]), size=nnz,
+                            p=np.array([30, 20, 15, 12, 10, 8, 4, 1]) / 100.0).astype(np.int64)
+    edge_types[0] = 500
+    net["synapses"]["edge_type_ids"] = edge_types
+    vscale = (net["node_params"]["V_th"] - net["node_params"]["E_L"]).astype(np.float32)
+    w0 = np.asarray(net["synapses"]["weights"], dtype=np.float32) / \
+        vscale[np.asarray(net["node_type_ids"])[net["synapses"]["indices"][:, 0]]]
+    w = (w0.astype(np.float64) * rng.lognormal(0.0, 0.3, nnz))          # the weights after some training
+    out = dict(edge_type_ids=edge_types, initial_weights=w0, weights=w)
+    for tag, make in (("mean_stiff", lambda: lf.MeanStiffRegularizer(0.7, net, penalize_relative_change=False, dtype=torch.float64)),
+                      ("mean_stiff_relative", lambda: lf.MeanStiffRegularizer(0.7, net, penalize_relative_change=True, dtype=torch.float64)),
+                      ("emd", lambda: lf.EarthMoversDistanceRegularizer(0.7, net, dtype=torch.float64))):
+        reg = make()
+        x = torch.from_numpy(w).requires_grad_(True)
+        loss = reg(x)
+        loss.backward()
+        out["loss_" + tag], out["grad_" + tag] = loss.item(), x.grad.numpy()
+        print(f"{tag}: loss {loss.item():.6e}")
+    path = os.path.join(HERE, "reference_weight_regularizers.npz")
+    np.savez_compressed(path, strength=0.7, **out)
+    print(f"wrote {path}")
+
+
 if __name__ == "__main__":
     root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("V1_GLIF_REFERENCE", "V1_GLIF_model")
+    if len(sys.argv) > 2 and sys.argv[2] == "regularizers":
+        regularizer_fixture(root)
+        sys.exit(0)
     main()
     sync_fixture(root)
     osi_fixture(root)
+    regularizer_fixture(root)

@@ -54,6 +54,10 @@ class RaggedTensor:
     def row_lengths(self):
         return self.row_splits[1:] - self.row_splits[:-1]
 
+    def __getitem__(self, i):
+        i = _i(i)
+        return self.flat_values[int(self.row_splits[i]):int(self.row_splits[i + 1])]
+
     def _gather_rows(self, rows):
         start = self.row_splits[rows]
         length = self.row_splits[rows + 1] - start

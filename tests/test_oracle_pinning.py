@@ -179,3 +179,54 @@ def test_cuda_expadam_equals_reference_optimizer_code():
         assert rel_err(m, f["m"][k]) <= 1e-6 and rel_err(v, f["v"][k]) <= 1e-6
         assert rel_err(w, f["w"][k]) <= 1e-6
         assert np.array_equal(w.cpu().numpy() == 0, f["w"][k] == 0)
+
+
+def _regularizer_fixture():
+    return np.load(os.path.join(ROOT, "tests", "golden", "reference_weight_regularizers.npz"))
+
+
+@pytest.mark.parametrize("tag", ["mean_stiff", "mean_stiff_relative", "emd"])
+def test_oracle_weight_regularizers_equal_reference_loss_code(tag):
+    """``oracle/losses.py`` forms of the reference's weight regularisers against value and gradient that
+    ``MeanStiffRegularizer`` / ``EarthMoversDistanceRegularizer`` produced for the same weights (fp64)."""
+    from oracle import losses
+    f = _regularizer_fixture()
+    idx, n_groups, order, splits = losses.regularizer_groups(f["edge_type_ids"])
+    w = torch.from_numpy(f["weights"]).requires_grad_(True)
+    s = float(f["strength"])
+    if tag == "emd":
+        loss = losses.emd_regularizer(w, order, splits, f["initial_weights"].astype(np.float64), s)
+    else:
+        loss = losses.mean_stiff_regularizer(w, idx, n_groups, f["initial_weights"].astype(np.float64), s,
+                                             relative=tag.endswith("relative"))
+    loss.backward()
+    want = float(f["loss_" + tag])
+    assert abs(loss.item() - want) <= 1e-10 * abs(want)
+    assert rel_err(w.grad, f["grad_" + tag]) <= 1e-9
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tag", ["mean_stiff", "mean_stiff_relative", "emd"])
+def test_cuda_weight_regularizers_equal_reference_loss_code(tag):
+    """The device kernels against the same reference-generated fixture (fp32 arithmetic: value within
+    1e-5, gradient within 1e-4)."""
+    from oracle import losses
+    from v1_glif_model_b200.training import WeightRegularizer
+    from util import make_cells
+    f = _regularizer_fixture()
+    cfg, dicts, orc, cell = make_cells("small", seed=4)
+    kind = "emd" if tag == "emd" else "mean_stiff"
+    reg = WeightRegularizer(cell, kind, f["edge_type_ids"], f["initial_weights"], float(f["strength"]),
+                            relative=tag.endswith("relative"))
+    w = torch.from_numpy(f["weights"].astype(np.float32)).cuda()
+    grad = torch.zeros_like(w)
+    loss = torch.zeros(1, device="cuda")
+    reg(w, grad, loss)
+    torch.cuda.synchronize()
+    want = float(f["loss_" + tag])
+    assert abs(float(loss) - want) <= 1e-5 * abs(want)
+    assert rel_err(grad, f["grad_" + tag]) <= 1e-4
+    # the gradient is accumulated, the value added
+    reg(w, grad, loss)
+    torch.cuda.synchronize()
+    assert abs(float(loss) - 2 * want) <= 2e-5 * abs(want) and rel_err(grad, 2 * f["grad_" + tag]) <= 1e-4

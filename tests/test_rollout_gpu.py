@@ -468,6 +468,30 @@ def test_internal_order_training_equals_reference_order_training():
     assert rel_err(results[1][3], results[0][3]) <= 1e-5
 
 
+def test_training_with_weight_regularizers_in_both_orders():
+    """Mean-stiff and EMD regularisers added to the reduced gradient: the step in the library's own
+    synapse order gives the weights of the step in the caller's order."""
+    from v1_glif_model_b200.training import Trainer, WeightRegularizer
+    results = []
+    for order in ("reference", "internal"):
+        cfg, dicts, orc, cell = _cells("small", **KW)
+        x, c = make_inputs(cfg)
+        rng = np.random.Generator(np.random.PCG64(8))
+        edge_types = rng.integers(0, 6, cell.recurrent_weight_values.numel())
+        w0 = cell.recurrent_weight_values.cpu().numpy()
+        regs = [WeightRegularizer(cell, "mean_stiff", edge_types, w0, 5.0, relative=True, order=order),
+                WeightRegularizer(cell, "emd", edge_types, w0, 2.0, order=order)]
+        tgt = torch.from_numpy(synth.make_rate_targets(cfg)).cuda() / 1000.0
+        tr = Trainer(cell, dict(LOSS, rate_target=tgt), learning_rate=5e-3, order=order, regularizers=regs)
+        for _ in range(3):
+            losses = tr.step(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda())
+        cell.synchronize()
+        results.append([w.clone() for w in tr.weights()] + [losses.clone()])
+    assert rel_err(results[1][0], results[0][0]) <= 1e-5
+    assert rel_err(results[1][3], results[0][3]) <= 1e-5
+    assert float(results[0][3][0]) > 0
+
+
 def test_full_size_column_properties():
     """66,634-neuron column, batch 5: size-independent checks (no oracle at this size)."""
     from v1_glif_model_b200.models import V1Column

@@ -92,6 +92,10 @@ SIGNATURES = {
     "v1g_rollout_bwd_internal": (C.c_int, [_P, C.POINTER(V1GLossSpec), _P, _P, _P, _P, _P]),
     "v1g_expadam_update_internal": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_float, C.c_float,
                                               C.c_float, C.c_float, C.c_int64, C.c_float, _P]),
+    "v1g_weight_regularizer": (C.c_int, [_P, C.c_int32, _P, _P, C.c_int64, C.c_int32, _P, _P, _P, C.c_float,
+                                         _P, _P, _P]),
+    "v1g_get_internal_order": (C.c_int, [_P, C.c_int, _P]),
+    "v1g_internal_weights": (C.c_int, [_P, C.c_int, C.POINTER(_P)]),
     "v1g_get_weights": (C.c_int, [_P, C.c_int, _P, _P]),
     "v1g_get_counters": (C.c_int, [_P, C.POINTER(V1GCounters)]),
     "v1g_synchronize": (C.c_int, [_P, _P]),

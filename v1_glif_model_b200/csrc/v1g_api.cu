@@ -140,6 +140,7 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   cudaFree(h->lgn_ent4);
   cudaFree(h->tape_stats);
   cudaFree(h->rate_scratch);
+  cudaFree(h->reg_scratch);
   cudaFree(h->sync_scratch);
   cudaFree(h->osi_scratch);
   cudaFree(h->lgn_offsets);

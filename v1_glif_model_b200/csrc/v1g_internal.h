@@ -129,6 +129,8 @@ struct V1GHandle {
   int64_t sync_scratch_cap = 0;
   int32_t* rate_scratch = nullptr;  // sort buffers of the rate-distribution target
   int64_t rate_scratch_cap = 0;
+  int32_t* reg_scratch = nullptr;  // group sums / sort buffers of the weight regularisers
+  int64_t reg_scratch_cap = 0;
   float* loss_scratch = nullptr;  // rate sums [N], pop counts [B][T], bin grads, partial losses
   int64_t loss_scratch_cap = 0;
   // staging for the host-buffer entry point

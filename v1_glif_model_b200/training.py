@@ -78,6 +78,64 @@ class ExponentiatedAdam:
                 raise _lib.V1GError(rc, "v1g_expadam_update failed")
 
 
+class _DevicePointer:
+    """A raw device address with a length, duck-typed like the two tensor methods the regulariser uses."""
+
+    def __init__(self, address, n):
+        self._address, self._n = address, n
+
+    def data_ptr(self):
+        return self._address
+
+    def numel(self):
+        return self._n
+
+
+class WeightRegularizer:
+    """A weight regulariser of the reference on the device: ``kind="mean_stiff"``
+    (``MeanStiffRegularizer``, ``loss_functions.py:171-220``; ``relative`` = ``penalize_relative_change``)
+    or ``kind="emd"`` (``EarthMoversDistanceRegularizer``, ``:536-601``).
+
+    ``edge_type_ids`` and ``initial_weights`` (the weights after division by the voltage scale, as the
+    reference prepares them) are per recurrent synapse in the caller's order.  ``order="internal"``
+    converts both to the library's own synapse order, the order of ``Trainer``'s gradient buffer.
+    Calling the object adds ``strength * value`` to ``loss[0]`` and the gradient to ``grad``."""
+
+    def __init__(self, cell, kind, edge_type_ids, initial_weights, strength, relative=False, order="reference",
+                 source=_lib.SRC_REC):
+        import numpy as np
+        self.cell, self.kind, self.strength = cell, {"mean_stiff": 0, "emd": 1}[kind], float(strength)
+        ids = np.asarray(edge_type_ids)
+        w0 = np.asarray(initial_weights, dtype=np.float64)
+        if order == "internal":
+            perm = np.empty(ids.shape[0], dtype=np.int32)
+            cell._check(cell._lib.v1g_get_internal_order(cell._libh, source, perm.ctypes.data))
+            ids, w0 = ids[perm], w0[perm]
+        _, idx = np.unique(ids, return_inverse=True)
+        self.n_groups = int(idx.max()) + 1
+        counts = np.bincount(idx, minlength=self.n_groups)
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cell.device)
+        self.group_ids = dev(idx.astype(np.int32))
+        self.offsets, self.denominator = None, None
+        if self.kind == 0:
+            target = np.bincount(idx, weights=w0, minlength=self.n_groups) / counts
+            self.target = dev(target.astype(np.float32))
+            if relative:
+                self.denominator = dev(np.maximum(np.abs(target), 1e-4).astype(np.float32))
+        else:
+            by_group = np.lexsort((w0, idx))            # groups ascending, weights ascending inside
+            self.target = dev(w0[by_group].astype(np.float32))
+            self.offsets = dev(np.concatenate([[0], np.cumsum(counts)]).astype(np.int32))
+
+    def __call__(self, w, grad, loss=None):
+        c = self.cell
+        p = lambda t: t.data_ptr() if t is not None else None
+        c._check(c._lib.v1g_weight_regularizer(
+            c._libh, self.kind, w.data_ptr(), self.group_ids.data_ptr(), w.numel(), self.n_groups,
+            self.target.data_ptr(), p(self.offsets), p(self.denominator), self.strength, p(loss), grad.data_ptr(),
+            C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+
 class Trainer:
     """One replica of the data-parallel training loop (batch sharded over ranks).
 
@@ -88,8 +146,11 @@ class Trainer:
     """
 
     def __init__(self, cell, loss, learning_rate=1e-3, train_input=True, train_noise=False,
-                 group=None, order="internal"):
+                 group=None, order="internal", regularizers=()):
         self.cell = cell
+        # weight regularisers of the recurrent weights (WeightRegularizer objects built with the same
+        # `order`); their gradient joins the reduced gradient once, their value the total loss
+        self.regularizers = tuple(regularizers)
         self.order = order
         self.lr = learning_rate
         self.group = group
@@ -144,6 +205,13 @@ class Trainer:
             # here (V1GError, code ETIMEOUT) before the gradients reach the other replicas or the weights
             cell.synchronize()
             self.grads.all_reduce(self.group)
+            if self.regularizers:
+                w_int = C.c_void_p()
+                cell._check(cell._lib.v1g_internal_weights(cell._libh, _lib.SRC_REC, C.byref(w_int)))
+                n_rec = self.grads.sizes[0]
+                w_view = _DevicePointer(w_int.value, n_rec)
+                for reg in self.regularizers:
+                    reg(w_view, self.grads.views[0], losses)
             self.iterations += 1
             cell._check(cell._lib.v1g_expadam_update_internal(
                 cell._libh, self.grads.flat.data_ptr(), self.m.data_ptr(), self.v.data_ptr(),
@@ -153,6 +221,8 @@ class Trainer:
         _, _, _, losses = self.cell.backward(self.loss, accumulate_into=self.grads.views)
         self.cell.synchronize()                  # as above: no update from an aborted rollout
         self.grads.all_reduce(self.group)
+        for reg in self.regularizers:
+            reg(self.cell.recurrent_weight_values, self.grads.views[0], losses)
         self.opt.apply_gradients([self.grads.views[i] for i in self._sel])
         self.cell.refresh_weights()
         return losses
