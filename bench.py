@@ -260,7 +260,7 @@ def workload_config(cfg, n_gpus, t_len):
 class Bench:
     """One rank: cell, trainer, inputs and timing helpers of a configuration."""
 
-    def __init__(self, cfg, t_len, rank, world, dev, options=()):
+    def __init__(self, cfg, t_len, rank, world, dev, options=(), mutate=None):
         import torch.distributed as dist
         from v1_glif_model_b200.models import V1Column
         from v1_glif_model_b200.training import Trainer
@@ -268,6 +268,8 @@ class Bench:
         self.dist, self.cfg, self.t_len, self.rank, self.world, self.dev = dist, cfg, t_len, rank, world, dev
         self.b = b = cfg.batch
         self.dicts = synth.make_network(cfg, 0)
+        if mutate is not None:
+            mutate(*self.dicts)
         self.cell = cell = V1Column(*self.dicts, device=dev, **CELL_KW)
         self.options = tuple(options)
         for name, value in options:
@@ -467,6 +469,10 @@ def run_ours(args):
         line["cpu_baseline"] = cpu_baseline(cfg, bench.dicts, args)
     else:
         line["cpu_baseline"] = None
+    if world == 1 and not args.no_real_basis and args.config == "C4":
+        del bench
+        torch.cuda.empty_cache()
+        line["real_basis"] = real_basis_record(args, rank, world, dev)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -567,6 +573,52 @@ def stress_record(args, rank, world, dev):
             "roofline_fwd_kernel": {"kernel": "rollout_fwd_kernel", "achieved": fb / (fwd_ms * 1e-3) / 1e9,
                                     "frac": fb / (fwd_ms * 1e-3) / 1e9 / peak, "kernel_ms": fwd_ms},
             "events_per_step": {k: cnt[k] / t_len for k in ("rec_events", "lgn_events", "bkg_events", "dw_events")}}
+
+
+def real_basis_record(args, rank, world, dev):
+    """The full-size column with the reference's own synaptic basis instead of the synthetic one-hot
+    one: 4 time constants and 121 synapse types whose rows of basis weights are dense and partly
+    negative (synaptic_data/tau_basis.npy and basis_function_weights.csv of the reference, carried by
+    the committed fixture tests/golden/reference_small_real_basis.npz).  Up to 4 atomics per delivered
+    synapse in the forward rollout; the backward ring holds the raw per-channel adjoints and a synapse
+    reads 4 rows."""
+    import dataclasses
+    path = os.path.join(ROOT, "tests", "golden", "reference_small_real_basis.npz")
+    if not os.path.exists(path):
+        return {"unavailable": "fixture with the reference's basis tables not found"}
+    g = np.load(path)
+    tau, basis = g["tau_syn"], g["synaptic_basis_weights"]
+    cfg = dataclasses.replace(synth.CONFIGS["C4"], n_receptors=int(tau.size))
+
+    def mutate(net, lgn, bkg):
+        rng = np.random.Generator(np.random.PCG64(12))
+        net["tau_syn"], net["synaptic_basis_weights"] = tau, basis
+        for d in (net["synapses"], lgn, bkg):
+            d["syn_ids"] = rng.integers(0, basis.shape[0], d["syn_ids"].shape[0]).astype(np.uint8)
+    t_len = args.real_basis_seq_len
+    bench = Bench(cfg, t_len, rank, world, dev, mutate=mutate)
+    cell = bench.cell
+    for k in range(2):
+        bench.step_resident(k)
+    steps = 3
+    ms = bench.timed(bench.step_resident, steps) / steps
+    bench.step_resident()
+    fwd_ms, bwd_ms = cell.last_kernel_ms(0), cell.last_kernel_ms(1)
+    cnt = cell.counters()
+    n, r, b = cfg.n_neurons, cfg.n_receptors, cfg.batch
+    peak, _ = measured_peaks()
+    nnz_rec = bench.dicts[0]["synapses"]["indices"].shape[0]
+    bb, fb = bwd_bytes_per_launch(cnt, n, r, b, t_len, nnz_rec), fwd_bytes_per_launch(cnt, n, r, b, t_len)
+    return {"workload": f"C4 column with the reference's basis (R={r}, S={basis.shape[0]} dense rows), batch {b}, "
+                        f"T={t_len}, fwd+bwd training step",
+            "value": world * b * n * t_len / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
+            "mean_rate_hz": cnt["spikes"] / (b * n * t_len) * 1000.0,
+            "note": "input weights are those calibrated for the one-hot basis, so the activity regime differs",
+            "roofline": {"bound": "hbm", "kernel": "rollout_bwd_kernel (raw rows)", "achieved": bb / (bwd_ms * 1e-3) / 1e9,
+                         "peak": peak, "unit": "GB/s", "frac": bb / (bwd_ms * 1e-3) / 1e9 / peak, "kernel_ms": bwd_ms,
+                         "algorithmic_bytes_per_launch": bb, "traffic": None},
+            "roofline_fwd_kernel": {"achieved": fb / (fwd_ms * 1e-3) / 1e9, "frac": fb / (fwd_ms * 1e-3) / 1e9 / peak,
+                                    "kernel_ms": fwd_ms}}
 
 
 def forward_only(bench, args):
@@ -685,6 +737,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fwd", action="store_true")
     ap.add_argument("--no-stress", action="store_true")
+    ap.add_argument("--no-real-basis", action="store_true")
+    ap.add_argument("--real-basis-seq-len", type=int, default=200, help="T of the record with the reference's basis")
     ap.add_argument("--lib-option", action="append", default=[], metavar="NAME=VALUE",
                     help="library tuning option for the training cell, e.g. pair_rows=1 (repeatable)")
     args = ap.parse_args()

@@ -39,7 +39,12 @@ CASES = {"reference_tiny": dict(config="tiny", seed=0, hard_reset=False),
                                  store_cotangents=False),
          # the Gaussian pseudo-derivative (spike_gauss / gauss_pseudo, models.py:17-21, 36-50, 1106-1107)
          "reference_small_gauss": dict(config="small", seed=5, hard_reset=False, batch=2, seq_len=30,
-                                       store_cotangents=False, pseudo_gauss=True, gauss_std=0.3)}
+                                       store_cotangents=False, pseudo_gauss=True, gauss_std=0.3),
+         # the reference's own synaptic basis: 4 time constants (synaptic_data/tau_basis.npy) and the 121
+         # rows of basis weights with negative entries (synaptic_data/basis_function_weights.csv); the
+         # fixture carries both tables, so the tests that use it need no reference tree
+         "reference_small_real_basis": dict(config="small", seed=6, hard_reset=False, batch=3, seq_len=30,
+                                            store_cotangents=False, real_basis=True)}
 
 
 def load_reference_models(ref_root):
@@ -56,11 +61,24 @@ def load_reference_models(ref_root):
 
 
 def run_case(models, name, config, seed, hard_reset, batch=None, seq_len=None, store_cotangents=True,
-             pseudo_gauss=False, gauss_std=0.5):
+             pseudo_gauss=False, gauss_std=0.5, real_basis=False, ref_root=None):
     import dataclasses
     cfg = synth.CONFIGS[config]
     cfg = dataclasses.replace(cfg, batch=batch or cfg.batch, seq_len=seq_len or cfg.seq_len)
+    extra = {}
+    if real_basis:
+        cfg = dataclasses.replace(cfg, n_receptors=4)
     net, lgn, bkg = synth.make_network(cfg, seed)
+    if real_basis:
+        from v1_glif_model_b200 import load_sparse
+        load_sparse.load_basis(os.path.join(ref_root, "synaptic_data", "tau_basis.npy"),
+                               os.path.join(ref_root, "synaptic_data", "basis_function_weights.csv"), network=net)
+        rng = np.random.Generator(np.random.PCG64(seed + 5))
+        n_types = net["synaptic_basis_weights"].shape[0]
+        for d in (net["synapses"], lgn, bkg):
+            d["syn_ids"] = rng.integers(0, n_types, d["syn_ids"].shape[0]).astype(np.uint8)
+        extra = dict(tau_syn=net["tau_syn"], synaptic_basis_weights=net["synaptic_basis_weights"],
+                     syn_ids_rec=net["synapses"]["syn_ids"], syn_ids_lgn=lgn["syn_ids"], syn_ids_bkg=bkg["syn_ids"])
     x = synth.make_lgn_spikes(cfg, cfg.batch, cfg.seq_len, seed)
     counts = synth.make_bkg_counts(cfg, cfg.batch, cfg.seq_len, seed)
     cwd = os.getcwd()
@@ -101,7 +119,7 @@ def run_case(models, name, config, seed, hard_reset, batch=None, seq_len=None, s
         dw_rec=cell.recurrent_weight_values.grad.numpy(),
         dw_lgn=cell.input_weight_values.grad.numpy(), dw_bkg=cell.bkg_input_weights.grad.numpy(),
         pre_ind_order=cell.pre_ind_table.flat_values.numpy(),
-        pre_ind_row_splits=cell.pre_ind_table.row_splits.numpy(),
+        pre_ind_row_splits=cell.pre_ind_table.row_splits.numpy(), **extra,
         **{"kw_" + k: v for k, v in KW.items() if isinstance(v, float)})
     print("wrote", out, os.path.getsize(out), "bytes; spikes:", int(z.sum()))
 
@@ -112,7 +130,7 @@ def main():
     only = sys.argv[2:]
     for name, spec in CASES.items():
         if not only or name in only:
-            run_case(models, name, **spec)
+            run_case(models, name, ref_root=ref_root, **spec)
 
 
 if __name__ == "__main__":

@@ -14,7 +14,8 @@ import torch
 from util import TOL_GRAD, TOL_STATE, make_case, rel_err
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-CASES = ["reference_tiny", "reference_tiny_hard_reset", "reference_small", "reference_small_gauss"]
+CASES = ["reference_tiny", "reference_tiny_hard_reset", "reference_small", "reference_small_gauss",
+         "reference_small_real_basis"]
 
 
 def _load(name):
@@ -26,6 +27,20 @@ def _load(name):
     if "pseudo_gauss" in g.files and bool(g["pseudo_gauss"]):
         kw.update(pseudo_gauss=True, gauss_std=float(g["gauss_std"]))
     return g, kw
+
+
+def _case_kwargs(g):
+    """Arguments of ``make_case`` that rebuild the fixture's network: for the fixture with the
+    reference's own synaptic basis (4 time constants, 121 rows of basis weights) the tables and the
+    synapse types stored in it replace the synthetic one-hot basis."""
+    if "synaptic_basis_weights" not in g.files:
+        return {}
+
+    def mutate(net, lgn, bkg):
+        net["tau_syn"] = g["tau_syn"]
+        net["synaptic_basis_weights"] = g["synaptic_basis_weights"]
+        net["synapses"]["syn_ids"], lgn["syn_ids"], bkg["syn_ids"] = g["syn_ids_rec"], g["syn_ids_lgn"], g["syn_ids_bkg"]
+    return dict(n_receptors=int(g["tau_syn"].size), mutate=mutate)
 
 
 def _cotangents(g):
@@ -43,7 +58,7 @@ def _cotangents(g):
 @pytest.mark.parametrize("name", CASES)
 def test_oracle_equals_reference_cell(name):
     g, kw = _load(name)
-    cfg, dicts, orc = make_case(str(g["config"]), seed=int(g["seed"]), dtype=torch.float64, **kw)
+    cfg, dicts, orc = make_case(str(g["config"]), seed=int(g["seed"]), dtype=torch.float64, **_case_kwargs(g), **kw)
     # the CSR table the reference built (make_pre_ind_table) is reproduced exactly
     assert np.array_equal(orc.pre_ind_table.order.numpy(), g["pre_ind_order"])
     assert np.array_equal(orc.pre_ind_table.row_splits.numpy(), g["pre_ind_row_splits"])
@@ -65,7 +80,7 @@ def test_oracle_equals_reference_cell(name):
 def test_cuda_path_equals_reference_cell(name):
     from v1_glif_model_b200.models import V1Column
     g, kw = _load(name)
-    cfg, dicts, _ = make_case(str(g["config"]), seed=int(g["seed"]), **kw)
+    cfg, dicts, _ = make_case(str(g["config"]), seed=int(g["seed"]), **_case_kwargs(g), **kw)
     cell = V1Column(*dicts, **kw)
     order, splits = cell.pre_ind_table(0)
     assert np.array_equal(order, g["pre_ind_order"]) and np.array_equal(splits, g["pre_ind_row_splits"])

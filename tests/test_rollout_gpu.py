@@ -478,7 +478,10 @@ def test_training_with_weight_regularizers_in_both_orders():
         x, c = make_inputs(cfg)
         rng = np.random.Generator(np.random.PCG64(8))
         edge_types = rng.integers(0, 6, cell.recurrent_weight_values.numel())
-        w0 = cell.recurrent_weight_values.cpu().numpy()
+        # the "initial" weights differ from the current ones (as after some training): at the very first
+        # step of the reference's setting every deviation is exactly zero and its rounding noise alone
+        # would set the sign of the sign-normalised Exp-Adam step of synapses without any other gradient
+        w0 = cell.recurrent_weight_values.cpu().numpy() * rng.lognormal(0.0, 0.3, edge_types.size).astype(np.float32)
         regs = [WeightRegularizer(cell, "mean_stiff", edge_types, w0, 5.0, relative=True, order=order),
                 WeightRegularizer(cell, "emd", edge_types, w0, 2.0, order=order)]
         tgt = torch.from_numpy(synth.make_rate_targets(cfg)).cuda() / 1000.0
@@ -487,8 +490,8 @@ def test_training_with_weight_regularizers_in_both_orders():
             losses = tr.step(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda())
         cell.synchronize()
         results.append([w.clone() for w in tr.weights()] + [losses.clone()])
-    assert rel_err(results[1][0], results[0][0]) <= 1e-5
-    assert rel_err(results[1][3], results[0][3]) <= 1e-5
+    assert rel_err(results[1][0], results[0][0]) <= 1e-4
+    assert rel_err(results[1][3], results[0][3]) <= 1e-4
     assert float(results[0][3][0]) > 0
 
 

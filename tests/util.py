@@ -89,8 +89,9 @@ def first_spike_divergence(z, z_ref, v_ref, ulps=16):
     return t_first
 
 
-def make_case(name, seed=0, dense_basis=False, n_receptors=None, **cell_kwargs):
-    """(cfg, dicts, oracle cell, inputs) for a synthetic configuration."""
+def make_case(name, seed=0, dense_basis=False, n_receptors=None, mutate=None, **cell_kwargs):
+    """(cfg, dicts, oracle cell, inputs) for a synthetic configuration; ``mutate(net, lgn, bkg)`` may
+    edit the dictionaries before the cells are built."""
     from oracle.cell_torch import OracleV1Column
     cfg = synth.CONFIGS[name] if isinstance(name, str) else name
     if n_receptors is not None:
@@ -103,6 +104,8 @@ def make_case(name, seed=0, dense_basis=False, n_receptors=None, **cell_kwargs):
         net["synaptic_basis_weights"] = rng.normal(0.3, 0.6, (s_types, cfg.n_receptors)).astype(np.float32)
         for d in (net["synapses"], lgn, bkg):
             d["syn_ids"] = rng.integers(0, s_types, d["syn_ids"].shape[0]).astype(np.uint8)
+    if mutate is not None:
+        mutate(net, lgn, bkg)
     oracle = OracleV1Column(net, lgn, bkg, **cell_kwargs)
     return cfg, (net, lgn, bkg), oracle
 

@@ -13,26 +13,28 @@
 
 namespace {
 
-// sum[g] += w, cnt[g] += 1 with a block-level pre-reduction for runs of equal ids
+// sum[g] += w, cnt[g] += 1.  The sums are kept in double precision: the penalty is built on the small
+// difference between a group's mean and its target, which float atomics in arbitrary order would
+// blur (and a sign-normalised optimiser step would then follow the noise).
 __global__ void __launch_bounds__(256) group_sum_kernel(const float* __restrict__ w, const int32_t* __restrict__ gid,
-                                                        int64_t n, float* __restrict__ sum, float* __restrict__ cnt) {
+                                                        int64_t n, double* __restrict__ sum, double* __restrict__ cnt) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const int g = gid[i];
-    atomicAdd(sum + g, w[i]);
-    atomicAdd(cnt + g, 1.f);
+    atomicAdd(sum + g, (double)w[i]);
+    atomicAdd(cnt + g, 1.0);
   }
 }
 
 // coef[g] = d loss / d mean_g / count_g; loss_out[0] += loss  (one block)
-__global__ void __launch_bounds__(256) mean_stiff_coef_kernel(const float* __restrict__ sum, const float* __restrict__ cnt,
+__global__ void __launch_bounds__(256) mean_stiff_coef_kernel(const double* __restrict__ sum, const double* __restrict__ cnt,
                                                               const float* __restrict__ target,
                                                               const float* __restrict__ denom, int G, float strength,
                                                               float* __restrict__ coef, float* loss_out) {
   __shared__ float red[256];
   float acc = 0.f;
   for (int g = threadIdx.x; g < G; g += blockDim.x) {
-    const float c = fmaxf(cnt[g], 1.f);          // unsorted_segment_mean: empty segments have mean 0
-    float d = sum[g] / c - target[g];
+    const float c = fmaxf((float)cnt[g], 1.f);   // unsorted_segment_mean: empty segments have mean 0
+    float d = (float)(sum[g] / (double)c - (double)target[g]);
     if (denom) d /= denom[g];
     acc += d * d;
   }
@@ -46,8 +48,8 @@ __global__ void __launch_bounds__(256) mean_stiff_coef_kernel(const float* __res
   const float loss = denom ? sqrtf(ms) : ms;
   // d loss / d d_g: plain 2 d_g / G; relative d_g / (G sqrt(ms))
   for (int g = threadIdx.x; g < G; g += blockDim.x) {
-    const float c = fmaxf(cnt[g], 1.f);
-    float d = sum[g] / c - target[g];
+    const float c = fmaxf((float)cnt[g], 1.f);
+    float d = (float)(sum[g] / (double)c - (double)target[g]);
     float dd;
     if (denom) {
       d /= denom[g];
@@ -114,12 +116,12 @@ extern "C" int v1g_weight_regularizer(V1GHandle* h, int32_t kind, const float* w
   const int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)h->n_sms * 16);
   int rc;
   if (kind == 0) {
-    // scratch: sum[G] | cnt[G] | coef[G]
-    if ((rc = v1g_reserve(h, &h->reg_scratch, &h->reg_scratch_cap, 3 * (int64_t)n_groups))) return rc;
-    float* sum = (float*)h->reg_scratch;
-    float* cnt = sum + n_groups;
-    float* coef = cnt + n_groups;
-    V1G_CUDA(h, cudaMemsetAsync(sum, 0, sizeof(float) * 2 * n_groups, st));
+    // scratch: sum[G] | cnt[G] (double) | coef[G] (float)
+    if ((rc = v1g_reserve(h, &h->reg_scratch, &h->reg_scratch_cap, 5 * (int64_t)n_groups + 2))) return rc;
+    double* sum = (double*)(((uintptr_t)h->reg_scratch + 7) & ~(uintptr_t)7);
+    double* cnt = sum + n_groups;
+    float* coef = (float*)(cnt + n_groups);
+    V1G_CUDA(h, cudaMemsetAsync(sum, 0, sizeof(double) * 2 * n_groups, st));
     group_sum_kernel<<<blocks, 256, 0, st>>>(w, group_ids, n, sum, cnt);
     mean_stiff_coef_kernel<<<1, 256, 0, st>>>(sum, cnt, target, denominator, n_groups, strength, coef, loss_out);
     add_group_coef_kernel<<<blocks, 256, 0, st>>>(group_ids, coef, n, grad);

@@ -571,12 +571,13 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         if (walk) {
           const unsigned zm1 = f1 >> 1, zm2 = f2 >> 1;
           const int32_t* pp = a.pair_ptr[(t - 1) & 1] + n0 + tid;
-          const int j0 = pp[0], j1 = pp[1];
+          const int len1 = rpx[tid * D + 1] - rpx[tid * D];   // delay-1 entries: they lead the row and serve step t-1 only
+          const int skip = (f1 & 1u) ? 0 : len1;              // not needed when only step t-2 asks for the row
+          const int j0 = pp[0] + skip, j1 = pp[1];
           rowd_s[base + __popc(wm & ((1u << lane) - 1u))] = make_int4(j0, j1, tid | (int)(zm1 << 16) | (int)(zm2 << 21), 0);
-          const int len1 = rpx[tid * D + 1] - rpx[tid * D];   // delay-1 entries (step t-1 only)
           c_rows += 1ull + (unsigned long long)((D - ((t - 1) & 1)) / 2);
           c_events += (unsigned long long)(j1 - j0);
-          c_dw += (unsigned long long)(j1 - j0) * __popc(zm1) + (unsigned long long)(j1 - j0 - len1) * __popc(zm2);
+          c_dw += (unsigned long long)(j1 - j0) * __popc(zm1) + (unsigned long long)(j1 - pp[0] - len1) * __popc(zm2);
         }
       }
     } else
