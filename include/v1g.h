@@ -233,6 +233,41 @@ int v1g_sample_bkg_counts(V1GHandle* h, int32_t batch, int32_t n_steps, int32_t 
 int v1g_sample_lgn_spikes(V1GHandle* h, int32_t batch, int32_t n_steps, const float* rates,
                           int64_t rates_batch_stride, int64_t seed, uint8_t* x_out, void* stream);
 
+/* ---- LGN front end: movie -> firing rates (lgn_model/lgn.py:481-528, helpers :54-96) ------------
+ * The stage upstream of the cell: every frame is filtered with the Gaussian of each unit's spatial
+ * size class (conv2d, padding SAME, divided by the same filter applied to a frame of ones), sampled
+ * bilinearly at the unit's position and at that of its non-dominant subfield (spatial_response),
+ * then filtered in time per unit, scaled, offset by the spontaneous rate and rectified
+ * (firing_rates_from_spatial).  The tables are the arrays the reference's LGN.__init__ prepares and
+ * caches (positions already scaled and clamped to the frame, lgn.py:386-393). */
+typedef struct V1GLgn V1GLgn;
+typedef struct V1GLgnTables {       /* all HOST pointers */
+  int32_t n_units, height, width;   /* frame [height, width]; the reference uses 120 x 240 */
+  int32_t n_classes;                /* spatial size classes (self.gaussian_filters) */
+  const int32_t* filter_sizes;      /* [n_classes] side k of each square filter, odd */
+  const float* filters;             /* the filters back to back, row-major k x k each */
+  const int32_t* unit_class;        /* [n_units] class of each unit (self.spatial_range_indices) */
+  const float *x, *y;               /* [n_units] position in pixels, 0 <= x <= width-1, 0 <= y <= height-1 */
+  const float *non_dominant_x, *non_dominant_y;
+  int32_t len_dom, len_non_dom;     /* taps of the temporal kernels */
+  const float* dom_temporal_kernels;      /* [len_dom, n_units], last tap = current frame */
+  const float* non_dom_temporal_kernels;  /* [len_non_dom, n_units] */
+  const float *amplitude, *non_dom_amplitude, *is_composite, *spontaneous_firing_rates; /* [n_units] */
+  int32_t bmtk_compat;              /* 1: divide by the filtered frame of ones (the reference's default) */
+} V1GLgnTables;
+
+int v1g_lgn_create(const V1GLgnTables* tables, V1GLgn** out);
+int v1g_lgn_destroy(V1GLgn* lgn);
+const char* v1g_lgn_last_error(const V1GLgn* lgn);
+
+/* movie[n_frames, height, width] float32 (device) -> rates_out[n_frames, n_units] in Hz (device,
+ * nullable) and, if wanted, the two spatial responses spatial_out[2, n_frames, n_units] (dominant,
+ * non-dominant; device, nullable) that LGN.spatial_response returns.  With movie == NULL the
+ * spatial responses in spatial_out are an INPUT and only the temporal stage runs
+ * (LGN.firing_rates_from_spatial).  The rates feed v1g_sample_lgn_spikes / v1g_rollout_fwd_rates. */
+int v1g_lgn_firing_rates(V1GLgn* lgn, const float* movie, int32_t n_frames, float* spatial_out,
+                         float* rates_out, void* stream);
+
 /* ---- operator level (one TensorFlow-level callable each) ---------------------------------- */
 
 /* tf.where(x > 0) (models.py:128, 826, 890): row-major coordinates of the positive entries of

@@ -266,6 +266,28 @@ def _conv1d(x, kernel, stride=1, padding="VALID"):
     return out.permute(0, 2, 1)
 
 
+def _conv2d(x, kernel, strides=None, padding="SAME"):
+    # x [batch, h, w, in_ch], kernel [kh, kw, in_ch, out_ch]; odd kernels, so SAME pads evenly
+    assert padding == "SAME" and kernel.shape[0] % 2 == 1 and kernel.shape[1] % 2 == 1
+    out = torch.nn.functional.conv2d(x.permute(0, 3, 1, 2), kernel.permute(3, 2, 0, 1),
+                                     padding=(kernel.shape[0] // 2, kernel.shape[1] // 2))
+    return out.permute(0, 2, 3, 1)
+
+
+def _depthwise_conv2d(x, kernel, strides=None, padding="VALID"):
+    # x [batch, h, w, ch], kernel [kh, kw, ch, 1] -> [batch, h - kh + 1, w - kw + 1, ch]
+    assert padding == "VALID" and kernel.shape[3] == 1
+    out = torch.nn.functional.conv2d(x.permute(0, 3, 1, 2), kernel.permute(2, 3, 0, 1), groups=x.shape[3])
+    return out.permute(0, 2, 3, 1)
+
+
+def _pad(x, paddings, **kw):
+    flat = []
+    for before, after in reversed([tuple(p) for p in paddings]):
+        flat += [int(before), int(after)]
+    return torch.nn.functional.pad(x, flat)
+
+
 def install():
     """Register the stand-in as ``tensorflow`` in ``sys.modules`` and return it."""
     tf = types.ModuleType("tensorflow")
@@ -306,6 +328,9 @@ def install():
     tf.sqrt = torch.sqrt
     tf.pow = torch.pow
     tf.cos = torch.cos
+    tf.floor = torch.floor
+    tf.pad = _pad
+    tf.Tensor = torch.Tensor
     tf.IndexedSlices = type("IndexedSlices", (), {})
     tf.reduce_sum = _reduce(torch.sum)
     tf.reduce_mean = _reduce(torch.mean)
@@ -317,11 +342,12 @@ def install():
     tf.math = types.SimpleNamespace(unsorted_segment_sum=_unsorted_segment_sum, exp=torch.exp,
                                     log=torch.log,
                                     reduce_variance=lambda x, axis=None: torch.var(x, dim=axis, unbiased=False),
-                                    cos=torch.cos, square=torch.square,
+                                    cos=torch.cos, square=torch.square, ceil=torch.ceil,
                                     unsorted_segment_mean=_unsorted_segment_mean)
     tf.TensorArray = _TensorArray
     tf.squeeze = lambda x, axis=None: x.squeeze() if axis is None else x.squeeze(axis)
-    tf.nn = types.SimpleNamespace(relu=torch.relu, sigmoid=torch.sigmoid, conv1d=_conv1d,
+    tf.nn = types.SimpleNamespace(relu=torch.relu, sigmoid=torch.sigmoid, conv1d=_conv1d, conv2d=_conv2d,
+                                  depthwise_conv2d=_depthwise_conv2d,
                                   softplus=torch.nn.functional.softplus,
                                   softmax=lambda x, axis=-1: torch.softmax(x, dim=axis))
     tf.sparse = types.SimpleNamespace(SparseTensor=SparseTensor,

@@ -30,6 +30,16 @@ class V1GState(C.Structure):
                 ("psc_rise", C.c_void_p), ("psc", C.c_void_p), ("noise_step", C.c_void_p)]
 
 
+class V1GLgnTables(C.Structure):
+    _fields_ = [("n_units", C.c_int32), ("height", C.c_int32), ("width", C.c_int32), ("n_classes", C.c_int32),
+                ("filter_sizes", C.c_void_p), ("filters", C.c_void_p), ("unit_class", C.c_void_p),
+                ("x", C.c_void_p), ("y", C.c_void_p), ("non_dominant_x", C.c_void_p), ("non_dominant_y", C.c_void_p),
+                ("len_dom", C.c_int32), ("len_non_dom", C.c_int32), ("dom_temporal_kernels", C.c_void_p),
+                ("non_dom_temporal_kernels", C.c_void_p), ("amplitude", C.c_void_p),
+                ("non_dom_amplitude", C.c_void_p), ("is_composite", C.c_void_p),
+                ("spontaneous_firing_rates", C.c_void_p), ("bmtk_compat", C.c_int32)]
+
+
 class V1GLossSpec(C.Structure):
     _fields_ = [("rate_target", C.c_void_p), ("v_lo", C.c_void_p), ("rate_cost", C.c_float),
                 ("voltage_cost", C.c_float), ("sync_cost", C.c_float), ("fano_target", C.c_float),
@@ -74,6 +84,10 @@ SIGNATURES = {
     "v1g_sample_lgn_spikes": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P, _P]),
     "v1g_rollout_fwd_rates": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P,
                                         C.POINTER(V1GState), _P, _P, C.c_int32, _P]),
+    "v1g_lgn_create": (C.c_int, [C.POINTER(V1GLgnTables), C.POINTER(_P)]),
+    "v1g_lgn_destroy": (C.c_int, [_P]),
+    "v1g_lgn_last_error": (C.c_char_p, [_P]),
+    "v1g_lgn_firing_rates": (C.c_int, [_P, _P, C.c_int32, _P, _P, _P]),
     "v1g_compact_spikes": (C.c_int, [_P, _P, C.c_int32, C.c_int64, _P, C.c_int64, _P, _P]),
     "v1g_compact_spikes_noalloc": (C.c_int, [_P, C.c_int32, C.c_int64, _P, C.c_int64, _P, _P]),
     "v1g_syn_currents_fwd": (C.c_int, [_P, C.c_int, _P, C.c_int32, _P, _P]),
