@@ -370,6 +370,10 @@ def run_ours(args):
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # stdout carries the JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.only_lgn:                 # the LGN record alone (a small run for a profiler)
+        if rank == 0:
+            print(json.dumps({"lgn": lgn_record(args, dev)}))
+        return
     options = [(o.split("=")[0], int(o.split("=")[1])) for o in args.lib_option]
     cfg = synth.CONFIGS[args.config]
     t_len = args.seq_len or cfg.seq_len
@@ -473,6 +477,9 @@ def run_ours(args):
         del bench
         torch.cuda.empty_cache()
         line["real_basis"] = real_basis_record(args, rank, world, dev)
+    if world == 1 and not args.no_lgn and args.config == "C4":
+        torch.cuda.empty_cache()
+        line["lgn"] = lgn_record(args, dev)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -621,6 +628,39 @@ def real_basis_record(args, rank, world, dev):
                                     "kernel_ms": fwd_ms}}
 
 
+def lgn_record(args, dev):
+    """The step upstream of the cell's input: movie -> LGN firing rates (lgn_model/lgn.py:481-528) at the
+    reference's sizes: 120 x 240 frames, 17,400 units in 14 spatial size classes, temporal kernels of 250 ms."""
+    from v1_glif_model_b200.lgn import LGN
+    height, width, n_units, n_frames, taps = 120, 240, 17400, args.lgn_frames, 250
+    sides = tuple(range(3, 31, 2))
+    tb = synth.make_lgn_tables(n_units, height, width, sides, taps, taps, seed=4)
+    lgn = LGN(**tb, row_size=height, col_size=width)
+    movie = torch.rand((n_frames, height, width), device=dev) * 2 - 1
+    for _ in range(3):
+        lgn.firing_rates(movie)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    reps = 5
+    torch.cuda.synchronize()
+    ev[0].record()
+    for _ in range(reps):
+        lgn.spatial_response(movie)
+    ev[1].record()
+    for _ in range(reps):
+        rates = lgn.firing_rates(movie)
+    ev[2].record()
+    torch.cuda.synchronize()
+    spatial_ms, total_ms = ev[0].elapsed_time(ev[1]) / reps, ev[1].elapsed_time(ev[2]) / reps
+    stencil_taps = 2 * sum(float(len(idx)) * (s + 1) ** 2 for idx, s in zip(tb["spatial_range_indices"], sides))
+    flops = 2.0 * n_frames * (stencil_taps + n_units * 2 * taps)
+    return {"workload": f"movie -> LGN firing rates: {n_frames} frames of {height} x {width}, {n_units} units, "
+                        f"{len(sides)} filter sizes up to {sides[-1]} taps wide, {taps}-ms temporal kernels",
+            "value": n_frames / (total_ms * 1e-3), "unit": "frames/s", "ms": total_ms, "spatial_kernel_ms": spatial_ms,
+            "gflops": flops / (total_ms * 1e-3) / 1e9, "mean_rate_hz": float(rates.mean()),
+            "note": "movie resident on the device; two kernels per call (stencils over frames held in shared "
+                    "memory, temporal filter); inputs (115 MB per 1000 frames) exceed L2 together with the outputs"}
+
+
 def forward_only(bench, args):
     """Configuration 3: forward-only rollout, batch 5, T=2500, from the warmed-up state."""
     cell, lib, dev = bench.cell, bench.lib, bench.dev
@@ -738,6 +778,9 @@ def main():
     ap.add_argument("--no-fwd", action="store_true")
     ap.add_argument("--no-stress", action="store_true")
     ap.add_argument("--no-real-basis", action="store_true")
+    ap.add_argument("--no-lgn", action="store_true")
+    ap.add_argument("--only-lgn", action="store_true", help="run the LGN front-end record and nothing else")
+    ap.add_argument("--lgn-frames", type=int, default=1000, help="frames of the movie of the LGN record")
     ap.add_argument("--real-basis-seq-len", type=int, default=200, help="T of the record with the reference's basis")
     ap.add_argument("--lib-option", action="append", default=[], metavar="NAME=VALUE",
                     help="library tuning option for the training cell, e.g. pair_rows=1 (repeatable)")

@@ -53,25 +53,8 @@ def test_oracle_in_double_agrees_with_float():
 
 
 def random_tables(rng, n_units, height, width, sides, len_dom, len_non_dom):
-    x = rng.uniform(0, width - 1, n_units).astype(np.float32)
-    y = rng.uniform(0, height - 1, n_units).astype(np.float32)
-    x[:4], y[:4] = [0, width - 1, 0, width - 1], [0, 0, height - 1, height - 1]
-    cls = rng.integers(0, len(sides), n_units)
-    cls[:len(sides)] = np.arange(len(sides))
-    filters = []
-    for side in sides:
-        r = np.arange(side) - side // 2
-        g = np.exp(-(r[:, None] ** 2 + r[None, :] ** 2) / (2 * (side / 6.0 + 0.2) ** 2))
-        filters.append((g / g.sum()).astype(np.float32)[..., None, None])
-    comp = (rng.random(n_units) < 0.3).astype(np.float32)
-    return dict(x=x, y=y, non_dominant_x=np.clip(x + rng.normal(0, 4, n_units), 0, width - 1).astype(np.float32),
-                non_dominant_y=np.clip(y + rng.normal(0, 4, n_units), 0, height - 1).astype(np.float32),
-                gaussian_filters=filters, spatial_range_indices=[np.where(cls == c)[0].astype(np.int32) for c in range(len(sides))],
-                dom_temporal_kernels=rng.normal(0, 0.2, (len_dom, n_units)).astype(np.float32),
-                non_dom_temporal_kernels=(rng.normal(0, 0.2, (len_non_dom, n_units)) * comp).astype(np.float32),
-                amplitude=rng.uniform(-3, 3, n_units).astype(np.float32),
-                non_dom_amplitude=(rng.uniform(-3, 3, n_units) * comp).astype(np.float32), is_composite=comp,
-                spontaneous_firing_rates=rng.uniform(0.5, 6, n_units).astype(np.float32))
+    from v1_glif_model_b200 import synth
+    return synth.make_lgn_tables(n_units, height, width, sides, len_dom, len_non_dom, seed=int(rng.integers(1 << 30)))
 
 
 def device_lgn(tb, height, width, compat=True):
@@ -112,6 +95,20 @@ def test_device_matches_oracle_at_the_reference_frame_size():
     # frames shorter than the temporal kernels, and an empty movie
     close(lgn.firing_rates(movie[:5]).cpu(), want[:5])
     assert lgn.firing_rates(movie[:0]).shape == (0, n_units)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("height,width", [(200, 240), (300, 320)])
+def test_device_matches_oracle_for_frames_beyond_shared_memory(height, width):
+    """Two 120 x 240 frames fit in one block's shared memory; a 200 x 240 frame fits alone and a 300 x 320
+    frame does not fit at all (its pixels are then read from global memory)."""
+    rng = np.random.Generator(np.random.PCG64(height))
+    tb = random_tables(rng, 300, height, width, (5, 11), 9, 7)
+    movie = np.clip(rng.normal(0, 0.5, (7, height, width)), -1, 1).astype(np.float32)
+    dom, non_dom = oracle_lgn.spatial_response(torch.from_numpy(movie).double(), tb)
+    got_dom, got_non_dom = device_lgn(tb, height, width).spatial_response(movie)
+    close(got_dom.cpu(), dom)
+    close(got_non_dom.cpu(), non_dom)
 
 
 @pytest.mark.gpu

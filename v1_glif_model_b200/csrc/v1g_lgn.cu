@@ -12,12 +12,18 @@
 // tables are set: the four bilinear corners of the filtered frame are the same movie patch seen
 // through four shifted copies of the filter, each divided by its own edge normaliser, so
 //     response[t, u] = sum over a (k+1) x (k+1) patch of E[u][dy][dx] * movie[t, y0+dy, x0+dx]
-// with taps outside the frame dropped (they are the zero padding).  A thread block takes one frame
-// into shared memory (a 120 x 240 frame is 115 KB) and evaluates every stencil from there, so the
-// movie is read from HBM once.  The temporal filter keeps a sliding window per thread: TT outputs of
-// one unit per thread reuse every loaded sample and kernel value TT times.
+// with taps outside the frame dropped (they are the zero padding; their weights are stored as 0 and
+// the coordinates clamped, so the inner loop has no branch).  Stencils are sorted by side and stored
+// in groups of 32, one per lane of a warp, tap-major (weight of tap p of lane l at [p][l]), so a warp
+// reads one 128-byte line per tap and its lanes run the same trip count.  A thread block takes two
+// frames, interleaved pixel by pixel, into shared memory (two 120 x 240 frames are 225 KB) and
+// evaluates every stencil on both from there: the movie is read from HBM once, a weight fetched from
+// L2 serves two frames, and one 8-byte shared-memory load brings both pixels.  The temporal filter
+// keeps a sliding window per thread: TT outputs of one unit per thread reuse every loaded sample and
+// kernel value TT times.
 #include <math.h>
 
+#include <algorithm>
 #include <vector>
 
 #include "v1g_internal.h"
@@ -25,10 +31,11 @@
 struct V1GLgn {
   int n_units = 0, height = 0, width = 0, len_dom = 0, len_non_dom = 0;
   int device = 0, n_sms = 0, smem_optin = 0;
-  // stencils of the dominant [0, U) and non-dominant [U, 2U) subfields
-  int32_t* st_off = nullptr;   // [2U + 1] first weight of each stencil
-  int32_t* st_geo = nullptr;   // [2U][3] = (y0, x0, side)
-  float* st_w = nullptr;       // weights, row-major side x side
+  // stencils of the dominant [0, U) and non-dominant [U, 2U) subfields, sorted by side, 32 per group
+  int n_groups = 0;
+  int2* st_grp = nullptr;      // [n_groups] = (first tap of the group in st_w / 32, side)
+  int4* st_slot = nullptr;     // [n_groups * 32] = (y0, x0, subfield * U + unit or -1 for an empty lane, 0)
+  float* st_w = nullptr;       // per group [side * side][32]
   float *k_dom = nullptr, *k_non_dom = nullptr;  // [len][U]
   float *amp = nullptr, *non_dom_amp = nullptr, *composite = nullptr, *spont = nullptr;
   float* spatial = nullptr;    // [2][T][U] scratch, grown on demand
@@ -57,43 +64,74 @@ int lgn_upload(V1GLgn* l, T** dst, const T* src, size_t n) {
   return V1G_OK;
 }
 
-// one block per frame: the frame goes to shared memory, every (unit, subfield) stencil is evaluated
-// from it; out[s][t][u]
-__global__ void __launch_bounds__(512) lgn_spatial_kernel(const float* __restrict__ movie, int T, int H, int W, int U,
-                                                          const int32_t* __restrict__ st_off,
-                                                          const int32_t* __restrict__ st_geo,
-                                                          const float* __restrict__ st_w, float* __restrict__ out,
-                                                          int frame_in_smem) {
+// one block per F consecutive frames: they go to shared memory interleaved ([pixel][F]) and every
+// stencil group is evaluated from there, one group per warp at a time; out[s][t][u].  With F == 1 and
+// IN_SMEM false (frames larger than shared memory) the pixels are read from global memory.
+constexpr int TB = 8;
+template <int F, bool IN_SMEM>
+__global__ void __launch_bounds__(1024) lgn_spatial_kernel(const float* __restrict__ movie, int T, int H, int W, int U,
+                                                          int n_groups, const int2* __restrict__ st_grp,
+                                                          const int4* __restrict__ st_slot,
+                                                          const float* __restrict__ st_w, float* __restrict__ out) {
   extern __shared__ float frame_s[];
-  for (int t = blockIdx.x; t < T; t += gridDim.x) {
-    const float* frame = movie + (int64_t)t * H * W;
-    if (frame_in_smem) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const int HW = H * W;
+  for (int t0 = blockIdx.x * F; t0 < T; t0 += gridDim.x * F) {
+    const int nf = min(F, T - t0);
+    const float* frame = movie + (int64_t)t0 * HW;
+    if (IN_SMEM) {
       __syncthreads();
-      for (int i = threadIdx.x; i < H * W; i += blockDim.x) frame_s[i] = frame[i];
+      for (int i = threadIdx.x; i < HW; i += blockDim.x) {
+#pragma unroll
+        for (int f = 0; f < F; ++f) frame_s[i * F + f] = f < nf ? frame[(int64_t)f * HW + i] : 0.f;
+      }
       __syncthreads();
-      frame = frame_s;
     }
-    for (int su = threadIdx.x; su < 2 * U; su += blockDim.x) {
-      const int y0 = st_geo[3 * su], x0 = st_geo[3 * su + 1], side = st_geo[3 * su + 2];
-      const float* w = st_w + st_off[su];
-      float acc = 0.f;
-      for (int dy = 0; dy < side; ++dy) {
-        const int y = y0 + dy;
-        if (y < 0 || y >= H) continue;
-        const float* row = frame + y * W;
-        for (int dx = 0; dx < side; ++dx) {
-          const int x = x0 + dx;
-          if (x >= 0 && x < W) acc += w[dy * side + dx] * row[x];
+    for (int g = warp; g < n_groups; g += n_warps) {
+      const int2 gd = st_grp[g];
+      const int4 sl = st_slot[g * 32 + lane];
+      const int side = gd.y;
+      const float* w = st_w + (int64_t)gd.x * 32 + lane;
+      float acc[F];
+#pragma unroll
+      for (int f = 0; f < F; ++f) acc[f] = 0.f;
+      // the taps of the patch in row-major order, TB at a time so that TB weight loads are in flight;
+      // the table pads every group to a multiple of TB taps with zero weights (their clamped
+      // coordinates stay inside the frame)
+      const int taps = (side * side + TB - 1) / TB * TB;
+      int dy = 0, dx = 0;
+      for (int p = 0; p < taps; p += TB) {
+        float wv[TB];
+#pragma unroll
+        for (int j = 0; j < TB; ++j) wv[j] = w[(p + j) * 32];
+#pragma unroll
+        for (int j = 0; j < TB; ++j) {
+          const int px = min(max(sl.x + dy, 0), H - 1) * W + min(max(sl.y + dx, 0), W - 1);
+          if (F == 2) {
+            const float2 v = IN_SMEM ? *reinterpret_cast<const float2*>(frame_s + 2 * px)
+                                     : *reinterpret_cast<const float2*>(frame + 2 * px);
+            acc[0] += wv[j] * v.x;
+            acc[F - 1] += wv[j] * v.y;
+          } else {
+            acc[0] += wv[j] * (IN_SMEM ? frame_s[px] : frame[px]);
+          }
+          if (++dx == side) { dx = 0; ++dy; }
         }
       }
-      const int s = su >= U ? 1 : 0, u = su - s * U;
-      out[((int64_t)s * T + t) * U + u] = acc;
+      if (sl.z >= 0) {
+        const int sub = sl.z >= U ? 1 : 0, u = sl.z - sub * U;
+#pragma unroll
+        for (int f = 0; f < F; ++f)
+          if (f < nf) out[((int64_t)sub * T + t0 + f) * U + u] = acc[f];
+      }
     }
   }
 }
 
 // rates[t][u] = relu(amp * f_dom + spont) + composite * relu(nd_amp * f_nd + spont), f = causal filter
-// of the unit's samples: f[t] = sum_j K[j] * s[t - (L - 1) + j] with s = 0 before the movie starts
+// of the unit's samples: f[t] = sum_j K[j] * s[t - (L - 1) + j] with s = 0 before the movie starts.
+// A thread owns TT consecutive outputs of one unit and walks the taps TT at a time over a window of
+// 2 TT samples held in registers: 2 TT loads feed TT * TT multiply-adds.
 constexpr int TT = 8;
 __global__ void __launch_bounds__(256) lgn_temporal_kernel(const float* __restrict__ spatial, int T, int U,
                                                            const float* __restrict__ k_dom, int len_dom,
@@ -107,20 +145,31 @@ __global__ void __launch_bounds__(256) lgn_temporal_kernel(const float* __restri
   if (u >= U) return;
   float f[2][TT];
 #pragma unroll
-  for (int i = 0; i < TT; ++i) f[0][i] = f[1][i] = 0.f;
   for (int s = 0; s < 2; ++s) {
-    const float* kern = s ? k_nd : k_dom;
+    const float* kern = (s ? k_nd : k_dom) + u;
     const int L = s ? len_nd : len_dom;
-    const float* smp = spatial + (int64_t)s * T * U;
-    // sample index q runs over t0 - (L - 1) .. t0 + TT - 1; output i uses kernel tap j = q - (t0 + i) + L - 1
-    for (int q = t0 - (L - 1); q < t0 + TT; ++q) {
-      if (q < 0 || q >= T) continue;
-      const float v = smp[(int64_t)q * U + u];
+    const float* smp = spatial + (int64_t)s * T * U + u;
+    auto sample = [&](int q) { return q >= 0 && q < T ? smp[(int64_t)q * U] : 0.f; };
 #pragma unroll
-      for (int i = 0; i < TT; ++i) {
-        const int j = q - (t0 + i) + L - 1;
-        if (j >= 0 && j < L) f[s][i] += kern[(int64_t)j * U + u] * v;
+    for (int i = 0; i < TT; ++i) f[s][i] = 0.f;
+    // output i, tap j reads sample t0 + i - (L - 1) + j; win[i + jj] is that sample for tap j0 + jj
+    float win[2 * TT];
+    const int q0 = t0 - (L - 1);
+#pragma unroll
+    for (int i = 0; i < TT; ++i) win[i] = sample(q0 + i);
+    for (int j0 = 0; j0 < L; j0 += TT) {
+      float kv[TT];
+#pragma unroll
+      for (int jj = 0; jj < TT; ++jj) {
+        kv[jj] = j0 + jj < L ? kern[(int64_t)(j0 + jj) * U] : 0.f;
+        win[TT + jj] = sample(q0 + j0 + TT + jj);
       }
+#pragma unroll
+      for (int jj = 0; jj < TT; ++jj)
+#pragma unroll
+        for (int i = 0; i < TT; ++i) f[s][i] += kv[jj] * win[i + jj];
+#pragma unroll
+      for (int i = 0; i < TT; ++i) win[i] = win[TT + i];
     }
   }
   const float a = amp[u], an = nd_amp[u], c = composite[u], sp = spont[u];
@@ -162,8 +211,8 @@ extern "C" int v1g_lgn_create(const V1GLgnTables* tb, V1GLgn** out) {
       }
     return s;
   };
-  std::vector<int32_t> off((size_t)2 * U + 1, 0), geo((size_t)2 * U * 3);
-  std::vector<float> w;
+  struct Stencil { int y0, x0, side; std::vector<float> w; };
+  std::vector<Stencil> sts((size_t)2 * U);
   for (int su = 0; su < 2 * U; ++su) {
     const int s = su >= U, u = su - s * U;
     const int c = tb->unit_class[u];
@@ -186,13 +235,39 @@ extern "C" int v1g_lgn_create(const V1GLgnTables* tb, V1GLgn** out) {
       for (int dy = 0; dy < k; ++dy)
         for (int dx = 0; dx < k; ++dx) e[(size_t)(dy + oy) * side + dx + ox] += scale * (double)g[dy * k + dx];
     }
-    off[su] = (int32_t)w.size();
-    geo[3 * su] = yf - r;
-    geo[3 * su + 1] = xf - r;
-    geo[3 * su + 2] = side;
-    for (double v : e) w.push_back((float)v);
+    Stencil& st = sts[su];
+    st.y0 = yf - r; st.x0 = xf - r; st.side = side;
+    st.w.resize(e.size());
+    for (int dy = 0; dy < side; ++dy)
+      for (int dx = 0; dx < side; ++dx) {
+        const int yy = st.y0 + dy, xx = st.x0 + dx;
+        const bool inside = yy >= 0 && yy < H && xx >= 0 && xx < W;   // outside: the frame's zero padding
+        st.w[(size_t)dy * side + dx] = inside ? (float)e[(size_t)dy * side + dx] : 0.f;
+      }
   }
-  off[(size_t)2 * U] = (int32_t)w.size();
+  std::vector<int> order((size_t)2 * U);
+  for (int i = 0; i < 2 * U; ++i) order[i] = i;
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return sts[a].side < sts[b].side; });
+  const int n_groups = (2 * U + 31) / 32;
+  std::vector<int2> grp((size_t)n_groups);
+  std::vector<int4> slot((size_t)n_groups * 32, make_int4(0, 0, -1, 0));
+  int64_t taps = 0;
+  for (int gi = 0; gi < n_groups; ++gi) {
+    const int last = std::min(2 * U, (gi + 1) * 32) - 1;
+    grp[gi] = make_int2((int)taps, sts[order[last]].side);   // sorted: the last lane has the widest patch
+    taps += ((int64_t)grp[gi].y * grp[gi].y + TB - 1) / TB * TB;   // padded with zero weights
+  }
+  if (taps * 32 > (int64_t)INT32_MAX) return lgn_fail(nullptr, V1G_EINVAL, "v1g_lgn_create: stencil table too large");
+  std::vector<float> w((size_t)taps * 32, 0.f);
+  for (int i = 0; i < 2 * U; ++i) {
+    const int gi = i >> 5, ln = i & 31, gside = grp[gi].y;
+    const Stencil& st = sts[order[i]];
+    slot[i] = make_int4(st.y0, st.x0, order[i], 0);
+    // a narrower stencil sits in the top-left corner of the group's patch; the rest stays 0
+    for (int dy = 0; dy < st.side; ++dy)
+      for (int dx = 0; dx < st.side; ++dx)
+        w[((size_t)grp[gi].x + (size_t)dy * gside + dx) * 32 + ln] = st.w[(size_t)dy * st.side + dx];
+  }
 
   V1GLgn* l = new V1GLgn();
   l->n_units = U; l->height = H; l->width = W; l->len_dom = tb->len_dom; l->len_non_dom = tb->len_non_dom;
@@ -204,7 +279,8 @@ extern "C" int v1g_lgn_create(const V1GLgnTables* tb, V1GLgn** out) {
   l->n_sms = prop.multiProcessorCount;
   l->smem_optin = (int)prop.sharedMemPerBlockOptin;
   int rc = V1G_OK;
-  if ((rc = lgn_upload(l, &l->st_off, off.data(), off.size())) || (rc = lgn_upload(l, &l->st_geo, geo.data(), geo.size())) ||
+  l->n_groups = n_groups;
+  if ((rc = lgn_upload(l, &l->st_grp, grp.data(), grp.size())) || (rc = lgn_upload(l, &l->st_slot, slot.data(), slot.size())) ||
       (rc = lgn_upload(l, &l->st_w, w.data(), w.size())) ||
       (rc = lgn_upload(l, &l->k_dom, tb->dom_temporal_kernels, (size_t)tb->len_dom * U)) ||
       (rc = lgn_upload(l, &l->k_non_dom, tb->non_dom_temporal_kernels, (size_t)tb->len_non_dom * U)) ||
@@ -221,7 +297,7 @@ extern "C" int v1g_lgn_create(const V1GLgnTables* tb, V1GLgn** out) {
 
 extern "C" int v1g_lgn_destroy(V1GLgn* l) {
   if (!l) return V1G_OK;
-  cudaFree(l->st_off); cudaFree(l->st_geo); cudaFree(l->st_w); cudaFree(l->k_dom); cudaFree(l->k_non_dom);
+  cudaFree(l->st_grp); cudaFree(l->st_slot); cudaFree(l->st_w); cudaFree(l->k_dom); cudaFree(l->k_non_dom);
   cudaFree(l->amp); cudaFree(l->non_dom_amp); cudaFree(l->composite); cudaFree(l->spont); cudaFree(l->spatial);
   delete l;
   return V1G_OK;
@@ -248,12 +324,15 @@ extern "C" int v1g_lgn_firing_rates(V1GLgn* l, const float* movie, int32_t n_fra
     spatial = l->spatial;
   }
   const size_t frame_bytes = (size_t)l->height * l->width * sizeof(float);
-  const int in_smem = frame_bytes <= (size_t)l->smem_optin ? 1 : 0;
-  if (in_smem)
-    LGN_CUDA(l, cudaFuncSetAttribute(lgn_spatial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)frame_bytes));
   if (movie) {
-    lgn_spatial_kernel<<<std::min(T, l->n_sms * 4), 512, in_smem ? frame_bytes : 0, st>>>(
-        movie, T, l->height, l->width, U, l->st_off, l->st_geo, l->st_w, spatial, in_smem);
+    const int F = 2 * frame_bytes <= (size_t)l->smem_optin ? 2 : 1;
+    const int in_smem = (size_t)F * frame_bytes <= (size_t)l->smem_optin ? 1 : 0;
+    const size_t smem = in_smem ? F * frame_bytes : 0;
+    auto kern = F == 2 ? lgn_spatial_kernel<2, true> : in_smem ? lgn_spatial_kernel<1, true> : lgn_spatial_kernel<1, false>;
+    if (in_smem) LGN_CUDA(l, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int blocks = std::max(1, std::min((T + F - 1) / F, l->n_sms * (in_smem ? 1 : 4)));
+    kern<<<blocks, 1024, smem, st>>>(movie, T, l->height, l->width, U, l->n_groups, l->st_grp, l->st_slot, l->st_w,
+                                    spatial);
     v1g_count_launches(1);
   }
   if (rates_out) {

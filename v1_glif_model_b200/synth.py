@@ -260,3 +260,32 @@ def make_sync_samples(cfg: SynthConfig | str, network, batch: int, n_samples: in
     bins_ms = np.unique(np.maximum(1, np.round(np.logspace(-3, 0, 20) * 1000.0).astype(np.int64)))
     targets = (1.0 + 0.6 * np.log10(bins_ms)).astype(np.float32)
     return samples, bins_ms.astype(np.int32), targets
+
+
+def make_lgn_tables(n_units: int, height: int, width: int, filter_sides=(3, 5, 9), len_dom: int = 20,
+                    len_non_dom: int = 17, seed: int = 0):
+    """Synthetic tables of the LGN front end in the shapes the reference caches (``lgn_model/lgn.py:355-472``):
+    unit positions in pixels (the first four on the frame's corners), one normalised Gaussian filter per
+    spatial size class and the unit indices of each class, per-unit temporal kernels ``[taps, n_units]`` (zero
+    for the non-dominant subfield of non-composite units), amplitudes and spontaneous rates."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    x = rng.uniform(0, width - 1, n_units).astype(np.float32)
+    y = rng.uniform(0, height - 1, n_units).astype(np.float32)
+    x[:4], y[:4] = [0, width - 1, 0, width - 1], [0, 0, height - 1, height - 1]
+    cls = rng.integers(0, len(filter_sides), n_units)
+    cls[:len(filter_sides)] = np.arange(len(filter_sides))
+    filters = []
+    for side in filter_sides:
+        r = np.arange(side) - side // 2
+        g = np.exp(-(r[:, None] ** 2 + r[None, :] ** 2) / (2 * (side / 6.0 + 0.2) ** 2))
+        filters.append((g / g.sum()).astype(np.float32)[..., None, None])
+    comp = (rng.random(n_units) < 0.3).astype(np.float32)
+    return dict(x=x, y=y, non_dominant_x=np.clip(x + rng.normal(0, 4, n_units), 0, width - 1).astype(np.float32),
+                non_dominant_y=np.clip(y + rng.normal(0, 4, n_units), 0, height - 1).astype(np.float32),
+                gaussian_filters=filters,
+                spatial_range_indices=[np.where(cls == c)[0].astype(np.int32) for c in range(len(filter_sides))],
+                dom_temporal_kernels=rng.normal(0, 0.2, (len_dom, n_units)).astype(np.float32),
+                non_dom_temporal_kernels=(rng.normal(0, 0.2, (len_non_dom, n_units)) * comp).astype(np.float32),
+                amplitude=rng.uniform(-3, 3, n_units).astype(np.float32),
+                non_dom_amplitude=(rng.uniform(-3, 3, n_units) * comp).astype(np.float32), is_composite=comp,
+                spontaneous_firing_rates=rng.uniform(0.5, 6, n_units).astype(np.float32))
