@@ -595,7 +595,9 @@ def real_basis_record(args, rank, world, dev):
         return {"unavailable": "fixture with the reference's basis tables not found"}
     g = np.load(path)
     tau, basis = g["tau_syn"], g["synaptic_basis_weights"]
-    cfg = dataclasses.replace(synth.CONFIGS["C4"], n_receptors=int(tau.size))
+    # background / LGN weight scales recalibrated for this basis (its rows sum to 1.2-2.7 over four
+    # channels instead of one unit entry) so that the column settles near 4 Hz as in configuration 4
+    cfg = dataclasses.replace(synth.CONFIGS["C4"], n_receptors=int(tau.size), bkg_weight_pa=17.3, lgn_weight_pa=3.05)
 
     def mutate(net, lgn, bkg):
         rng = np.random.Generator(np.random.PCG64(12))
@@ -620,7 +622,7 @@ def real_basis_record(args, rank, world, dev):
                         f"T={t_len}, fwd+bwd training step",
             "value": world * b * n * t_len / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
             "mean_rate_hz": cnt["spikes"] / (b * n * t_len) * 1000.0,
-            "note": "input weights are those calibrated for the one-hot basis, so the activity regime differs",
+            "note": "synapse types drawn uniformly from the 121 rows; input weight scales calibrated for this basis",
             "roofline": {"bound": "hbm", "kernel": "rollout_bwd_kernel (raw rows)", "achieved": bb / (bwd_ms * 1e-3) / 1e9,
                          "peak": peak, "unit": "GB/s", "frac": bb / (bwd_ms * 1e-3) / 1e9 / peak, "kernel_ms": bwd_ms,
                          "algorithmic_bytes_per_launch": bb, "traffic": None},

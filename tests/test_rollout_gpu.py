@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from util import TOL_GRAD, TOL_STATE, first_spike_divergence, make_case, make_inputs, rel_err
+from util import TOL_GRAD, TOL_STATE, assert_grad_close, first_spike_divergence, make_case, make_inputs, rel_err
 from v1_glif_model_b200 import synth
 
 pytestmark = pytest.mark.gpu
@@ -362,6 +362,38 @@ def test_bptt_batch_of_five(options):
     cell.synchronize()
     for got, want in zip(grads[:3], go):
         assert rel_err(got, want) <= TOL_GRAD
+
+
+@pytest.mark.parametrize("batch,nrec,options", [
+    (3, 4, ()),                      # lane quads over fp32 16-byte rows
+    (5, 4, ()),                      # lane quads over 24-bit rows
+    (5, 4, (("no_q_pack", 1),)),     # 32-byte rows: the gather over plain arrays
+    (5, 4, (("no_meta", 1),)),
+    (8, 4, ()),
+    (5, 5, ()),                      # five channels do not divide a warp: plain-array gather
+    (5, 4, (("rollout_chunk", 64), ("state_in_global", 1))),
+])
+def test_bptt_with_more_synapse_types_than_ring_channels(batch, nrec, options):
+    """More than 8 synapse types (the reference's basis table has 121 rows over 4 channels): the
+    backward ring holds the raw per-channel adjoints and a synapse contracts them with its basis row.
+    With 4 channels in 16-byte rows a quad of lanes shares a synapse (one lane per channel); every
+    other shape walks plain arrays.  Long rows (several passes), rows that spike (weight gradient over
+    the quad) and rows shorter than a pass are all in the 600-neuron net."""
+    kw = dict(KW, dense_basis=True, n_receptors=nrec)
+    cfg, dicts, orc, cell = _cells("small", options, **kw)
+    assert dicts[0]["synaptic_basis_weights"].shape[0] > 8
+    x, c = make_inputs(cfg, batch=batch, seq_len=40)
+    zo, lo, go = _oracle_grads(orc, cfg, x, c, cell.voltage_scale, torch.float32)
+    z, _ = cell.rollout(torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda(), save_for_bwd=True)
+    assert torch.equal(z.cpu().float(), zo)
+    assert int(z.sum()) > 100
+    tgt = torch.from_numpy(synth.make_rate_targets(cfg)).cuda() / 1000.0
+    vlo = torch.from_numpy((-20.0 / cell.voltage_scale).astype(np.float32)).cuda()
+    grads = cell.backward(dict(LOSS, rate_target=tgt, v_lo=vlo))
+    cell.synchronize()
+    assert abs(float(grads[3][0]) - lo) <= 1e-4 * abs(lo)
+    for name, got, want in zip(("dW_rec", "dW_lgn", "dW_bkg"), grads[:3], go):
+        assert_grad_close(got, want, name)
 
 
 def test_bptt_from_carried_state_counts_pending_spikes():

@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
     return (int64_t)(step % K) * Np * C * QW;
   };
 
-  const bool fast_rows = PROJ && a.rec_syn8 != nullptr;  // packed-record gather
+  const bool fast_rows = a.rec_syn8 != nullptr;  // packed-record gather (in raw mode the host offers it only for R = 4 and 16-byte rows)
   unsigned char* sp_ = smem_raw;
   auto take = [&](size_t bytes) {
     unsigned char* p = sp_;
@@ -932,9 +932,19 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       // the rollout need no test: their ring slots still hold the zeros of the initial clear.
       // Lanes past the end of a row read a neighbouring record (always inside the array) and get
       // weight zero.
+      // Raw mode (more than 8 synapse types: the ring holds the R = 4 channels of a neuron as four
+      // consecutive 16-byte rows, one 64-byte half line): a QUAD of lanes shares a synapse, lane q of
+      // it takes channel q, so that one load instruction touches one line per synapse (8 per warp)
+      // instead of four; a lane accumulates w * basis[sid][q] * Q[post][q][b], and the reduction over
+      // the warp at the end of the row sums channels and synapses alike.
+      constexpr bool QUAD = !PROJ;
+      constexpr int LPS = QUAD ? 4 : 1;      // lanes per synapse
+      constexpr int SPG = 32 / LPS;          // synapses per 32-lane group
       constexpr int NB = PACK ? 5 : BP_;     // batch values a row really carries
       constexpr int QV = QW / 4;             // 16-byte words per Q row
-      constexpr int UF = QV == 1 ? V1G_BWD_GROUPS : 2;  // 32-synapse groups per pass
+      constexpr int UF = QV == 1 ? V1G_BWD_GROUPS : 2;  // 32-lane groups per pass
+      constexpr int SPP = SPG * UF;          // synapses per pass
+      const int lsyn = lane / LPS, lch = lane % LPS;
       constexpr int NS = V1G_BWD_STAGES;
       struct Pass { int jb, j1, kz, fl; };   // kz = row | spike mask << 16; fl: 1 first pass of its row, 4 valid
       const int jmax = a.rec_nnz - 1;
@@ -943,14 +953,15 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       uint2 rec[UF];
       float4 qS[NS][UF][QV];
       float wS[NS][UF];
+      unsigned sidS[QUAD ? NS : 1];  // raw mode: the synapse types of the pass, 8 bits per group (for the weight gradient)
       float acc[BP_];
 #pragma unroll
       for (int i = 0; i < NS; ++i) ps_[i] = Pass{0, 0, 0, 0};
 #pragma unroll
       for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
       auto issue_rec = [&]() {  // advance pr to the following pass and request its records
-        if (pr.fl && pr.jb + 32 * UF < pr.j1) {
-          pr.jb += 32 * UF;
+        if (pr.fl && pr.jb + SPP < pr.j1) {
+          pr.jb += SPP;
           pr.fl = 4;
         } else {
           const int q = pop_row();  // warps that drew long rows, or rows with spikes, take fewer
@@ -962,22 +973,28 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           }
         }
 #pragma unroll
-        for (int u = 0; u < UF; ++u) rec[u] = __ldcs(a.rec_syn8 + min(pr.jb + u * 32 + lane, jmax));
+        for (int u = 0; u < UF; ++u) rec[u] = __ldcs(a.rec_syn8 + min(pr.jb + u * SPG + lsyn, jmax));
       };
-      auto issue_q = [&](const Pass& ps, float4 (&q)[UF][QV], float (&w)[UF]) {  // Q rows of the pass in rec
+      auto issue_q = [&](const Pass& ps, float4 (&q)[UF][QV], float (&w)[UF], unsigned& sids) {  // Q rows of the pass in rec
+        if (QUAD) sids = 0u;
 #pragma unroll
         for (int u = 0; u < UF; ++u) {
-          const bool in_row = ps.jb + u * 32 + lane < ps.j1;
+          const bool in_row = ps.jb + u * SPG + lsyn < ps.j1;
           const unsigned w0 = rec[u].x;
-          unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + ((w0 >> 22) & 127u);
+          const unsigned sid = (w0 >> 22) & 127u;
+          unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + (QUAD ? (unsigned)lch : sid);
           row = in_row ? row : 0u;  // lanes past the end of the row share one request
           const float4* qp = (const float4*)(a.Q + row * (unsigned)QW);  // < 2^31 words, checked by the host
 #pragma unroll
           for (int v = 0; v < QV; ++v) q[u][v] = __ldcg(qp + v);
           w[u] = in_row ? __uint_as_float(rec[u].y) : 0.f;
+          if (QUAD) {
+            w[u] *= basis_s[sid * R_ + lch];
+            sids |= sid << (8 * u);
+          }
         }
       };
-      auto compute = [&](const Pass& ps, const float4 (&q)[UF][QV], const float (&w)[UF]) {
+      auto compute = [&](const Pass& ps, const float4 (&q)[UF][QV], const float (&w)[UF], unsigned sids) {
         if (ps.fl & 1) {
 #pragma unroll
           for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
@@ -999,8 +1016,18 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
             unpack_row<BP_, PACK>(q[u], pj);
 #pragma unroll
             for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
-            const int j = ps.jb + u * 32 + lane;
-            if (j < ps.j1) {
+            const int j = ps.jb + u * SPG + lsyn;
+            if (QUAD) {
+              float dwv = 0.f;
+#pragma unroll
+              for (int b = 0; b < NB; ++b)
+                if (zm & (1u << b)) dwv += pj[b];
+              // contract with the synapse's basis row over the four lanes of the quad
+              dwv *= basis_s[((sids >> (8 * u)) & 127u) * R_ + lch];
+              dwv += __shfl_xor_sync(0xffffffffu, dwv, 1);
+              dwv += __shfl_xor_sync(0xffffffffu, dwv, 2);
+              if (j < ps.j1 && lch == 0) a.dw_rec[j] += dwv;  // this lane is the only writer of the synapse
+            } else if (j < ps.j1) {
               float dwv = 0.f;
 #pragma unroll
               for (int b = 0; b < NB; ++b)
@@ -1009,7 +1036,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
             }
           }
         }
-        if (ps.jb + 32 * UF >= ps.j1) reduce_store(acc, ps.kz & 0xffff);
+        if (ps.jb + SPP >= ps.j1) reduce_store(acc, ps.kz & 0xffff);
       };
       // one turn of the pipeline with buffer I: false when the warp has no further pass
       auto turn = [&](auto I) -> bool {
@@ -1018,15 +1045,15 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           // accumulate what is still in flight, oldest first
 #pragma unroll
           for (int o = 1; o < NS; ++o)
-            if (ps_[(i + o) % NS].fl) compute(ps_[(i + o) % NS], qS[(i + o) % NS], wS[(i + o) % NS]);
+            if (ps_[(i + o) % NS].fl) compute(ps_[(i + o) % NS], qS[(i + o) % NS], wS[(i + o) % NS], sidS[QUAD ? (i + o) % NS : 0]);
           return false;
         }
         ps_[i] = pr;
-        issue_q(ps_[i], qS[i], wS[i]);
+        issue_q(ps_[i], qS[i], wS[i], sidS[QUAD ? i : 0]);
         issue_rec();
         constexpr int x = (i + 1) % NS;  // the oldest pass
         if (ps_[x].fl) {
-          compute(ps_[x], qS[x], wS[x]);
+          compute(ps_[x], qS[x], wS[x], sidS[QUAD ? x : 0]);
           ps_[x].fl = 0;
         }
         return true;
@@ -1374,10 +1401,11 @@ static int rollout_bwd_impl(V1GHandle* h, const V1GLossSpec* loss, const float* 
   if (plan.chunkP > 65535) return v1g_fail(h, V1G_ERANGE, "slice of %d neurons per block exceeds 65535", plan.chunkP);
   auto al = [](size_t b) { return (b + 15) & ~(size_t)15; };
   const size_t plane = (size_t)B * plan.chunkP;
-  const bool fast = proj && !h->opt_no_meta && h->src[V1G_SRC_REC].syn8 != nullptr &&
-                    h->src[V1G_SRC_REC].nnz > 0;  // packed-record gather
+  // packed-record gather: projected rows, or raw rows of four channels in 16 bytes each (lane quads)
+  const bool fast = (proj || (R == 4 && QW == 4)) && !h->opt_no_meta && h->src[V1G_SRC_REC].syn8 != nullptr &&
+                    h->src[V1G_SRC_REC].nnz > 0;
   // paired rows (two steps per 32-byte row): 16-byte rows, packed records, one neuron per thread
-  bool pair = fast && QW == 4 && plan.chunk <= NT && h->opt_pair_rows;
+  bool pair = fast && proj && QW == 4 && plan.chunk <= NT && h->opt_pair_rows;
   const int KP = ((D + 3) >> 1) + 1;  // pair slots covering D+3 consecutive steps at either alignment
   if (pair && (rc = v1g_build_pair_tables(h, st))) return rc;
   // a delay parity without any entry leaves nothing to clamp the lanes past a row's end to
