@@ -370,9 +370,10 @@ def run_ours(args):
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # stdout carries the JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
-    if args.only_lgn:                 # the LGN record alone (a small run for a profiler)
+    if args.only_lgn or args.only_real_basis:    # one side record alone (a small run for a profiler)
         if rank == 0:
-            print(json.dumps({"lgn": lgn_record(args, dev)}))
+            print(json.dumps({"lgn": lgn_record(args, dev)} if args.only_lgn else
+                             {"real_basis": real_basis_record(args, rank, 1, dev)}))
         return
     options = [(o.split("=")[0], int(o.split("=")[1])) for o in args.lib_option]
     cfg = synth.CONFIGS[args.config]
@@ -782,6 +783,7 @@ def main():
     ap.add_argument("--no-real-basis", action="store_true")
     ap.add_argument("--no-lgn", action="store_true")
     ap.add_argument("--only-lgn", action="store_true", help="run the LGN front-end record and nothing else")
+    ap.add_argument("--only-real-basis", action="store_true", help="run the reference-basis record and nothing else")
     ap.add_argument("--lgn-frames", type=int, default=1000, help="frames of the movie of the LGN record")
     ap.add_argument("--real-basis-seq-len", type=int, default=200, help="T of the record with the reference's basis")
     ap.add_argument("--lib-option", action="append", default=[], metavar="NAME=VALUE",

@@ -114,6 +114,17 @@ struct BwdArgs {
 #ifndef V1G_BWD_STAGES
 #define V1G_BWD_STAGES 2  // Q-row buffers of the gather pipeline (registers: 20 per stage)
 #endif
+// Raw-mode gather (more than 8 synapse types, 4 channels in 16-byte rows): lanes that share a synapse
+// and 32-lane groups per pass.  Measured on B200 (66,634 neurons, batch 5, the reference's 121 x 4
+// basis, us per reverse step): 4 lanes x 4 groups 65.2, 2 lanes (two channels each, one 256-bit load)
+// x 2 groups 61.0, x 3 groups 56.8, x 4 groups 65.9 (spills), 1 lane x 1 group 71.6; the gather over
+// plain arrays that this path replaced 111.
+#ifndef V1G_BWD_RAW_LANES
+#define V1G_BWD_RAW_LANES 2
+#endif
+#ifndef V1G_BWD_RAW_GROUPS
+#define V1G_BWD_RAW_GROUPS 3
+#endif
 #ifndef V1G_BWD_PAIR_GROUPS
 #define V1G_BWD_PAIR_GROUPS 3  // 32-entry groups of a pass of the paired gather (32-byte rows)
 #endif
@@ -933,16 +944,19 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       // Lanes past the end of a row read a neighbouring record (always inside the array) and get
       // weight zero.
       // Raw mode (more than 8 synapse types: the ring holds the R = 4 channels of a neuron as four
-      // consecutive 16-byte rows, one 64-byte half line): a QUAD of lanes shares a synapse, lane q of
-      // it takes channel q, so that one load instruction touches one line per synapse (8 per warp)
-      // instead of four; a lane accumulates w * basis[sid][q] * Q[post][q][b], and the reduction over
-      // the warp at the end of the row sums channels and synapses alike.
+      // consecutive 16-byte rows, one 64-byte half line): LPS lanes share a synapse, each taking
+      // CPL = 4 / LPS channels, so that one load instruction touches one line per synapse instead of
+      // four; a lane accumulates w * basis[sid][c] * Q[post][c][b] over its channels, and the reduction
+      // over the warp at the end of the row sums channels and synapses alike.
       constexpr bool QUAD = !PROJ;
-      constexpr int LPS = QUAD ? 4 : 1;      // lanes per synapse
+      constexpr int LPS = QUAD ? V1G_BWD_RAW_LANES : 1;  // lanes per synapse
+      constexpr int CPL = QUAD ? 4 / LPS : 1;            // channels (16-byte rows) a lane loads
       constexpr int SPG = 32 / LPS;          // synapses per 32-lane group
       constexpr int NB = PACK ? 5 : BP_;     // batch values a row really carries
       constexpr int QV = QW / 4;             // 16-byte words per Q row
-      constexpr int UF = QV == 1 ? V1G_BWD_GROUPS : 2;  // 32-lane groups per pass
+      constexpr int QVL = QV * CPL;          // 16-byte words per lane and synapse
+      constexpr int UF = QUAD ? V1G_BWD_RAW_GROUPS : QV == 1 ? V1G_BWD_GROUPS : 2;  // 32-lane groups per pass
+      static_assert(!QUAD || UF <= 4, "the synapse types of a pass are kept as four 8-bit fields of one word");
       constexpr int SPP = SPG * UF;          // synapses per pass
       const int lsyn = lane / LPS, lch = lane % LPS;
       constexpr int NS = V1G_BWD_STAGES;
@@ -951,8 +965,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       Pass pr{0, 0, 0, 0};
       Pass ps_[NS];
       uint2 rec[UF];
-      float4 qS[NS][UF][QV];
-      float wS[NS][UF];
+      float4 qS[NS][UF][QVL];
+      float wS[NS][UF][CPL];
       unsigned sidS[QUAD ? NS : 1];  // raw mode: the synapse types of the pass, 8 bits per group (for the weight gradient)
       float acc[BP_];
 #pragma unroll
@@ -975,26 +989,32 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
 #pragma unroll
         for (int u = 0; u < UF; ++u) rec[u] = __ldcs(a.rec_syn8 + min(pr.jb + u * SPG + lsyn, jmax));
       };
-      auto issue_q = [&](const Pass& ps, float4 (&q)[UF][QV], float (&w)[UF], unsigned& sids) {  // Q rows of the pass in rec
+      auto issue_q = [&](const Pass& ps, float4 (&q)[UF][QVL], float (&w)[UF][CPL], unsigned& sids) {  // Q rows of the pass in rec
         if (QUAD) sids = 0u;
 #pragma unroll
         for (int u = 0; u < UF; ++u) {
           const bool in_row = ps.jb + u * SPG + lsyn < ps.j1;
           const unsigned w0 = rec[u].x;
           const unsigned sid = (w0 >> 22) & 127u;
-          unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + (QUAD ? (unsigned)lch : sid);
+          unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + (QUAD ? (unsigned)(lch * CPL) : sid);
           row = in_row ? row : 0u;  // lanes past the end of the row share one request
           const float4* qp = (const float4*)(a.Q + row * (unsigned)QW);  // < 2^31 words, checked by the host
+          if (QVL == 2 && CPL == 2) {
+            load_pair((const float*)qp, q[u][0], q[u][QVL - 1]);  // two channels with one 256-bit load
+          } else if (QVL == 4 && CPL == 4) {
+            load_pair((const float*)qp, q[u][0], q[u][1 % QVL]);
+            load_pair((const float*)(qp + 2), q[u][2 % QVL], q[u][3 % QVL]);
+          } else {
 #pragma unroll
-          for (int v = 0; v < QV; ++v) q[u][v] = __ldcg(qp + v);
-          w[u] = in_row ? __uint_as_float(rec[u].y) : 0.f;
-          if (QUAD) {
-            w[u] *= basis_s[sid * R_ + lch];
-            sids |= sid << (8 * u);
+            for (int v = 0; v < QVL; ++v) q[u][v] = __ldcg(qp + v);
           }
+          const float wt = in_row ? __uint_as_float(rec[u].y) : 0.f;
+#pragma unroll
+          for (int c = 0; c < CPL; ++c) w[u][c] = QUAD ? wt * basis_s[sid * R_ + lch * CPL + c] : wt;
+          if (QUAD) sids |= sid << (8 * u);
         }
       };
-      auto compute = [&](const Pass& ps, const float4 (&q)[UF][QV], const float (&w)[UF], unsigned sids) {
+      auto compute = [&](const Pass& ps, const float4 (&q)[UF][QVL], const float (&w)[UF][CPL], unsigned sids) {
         if (ps.fl & 1) {
 #pragma unroll
           for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
@@ -1003,30 +1023,45 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         if (!zm) {
 #pragma unroll
           for (int u = 0; u < UF; ++u) {
-            float pj[BP_];
-            unpack_row<BP_, PACK>(q[u], pj);
 #pragma unroll
-            for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
+            for (int c = 0; c < CPL; ++c) {
+              float4 one[QV];
+#pragma unroll
+              for (int v = 0; v < QV; ++v) one[v] = q[u][c * QV + v];
+              float pj[BP_];
+              unpack_row<BP_, PACK>(one, pj);
+#pragma unroll
+              for (int b = 0; b < NB; ++b) acc[b] += w[u][c] * pj[b];
+            }
           }
         } else {
           // the source neuron spiked at this step in the batch rows of zm: weight gradient
 #pragma unroll
           for (int u = 0; u < UF; ++u) {
             float pj[BP_];
-            unpack_row<BP_, PACK>(q[u], pj);
+            float dwq = 0.f;  // raw mode: this lane's share of the synapse's weight gradient
 #pragma unroll
-            for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
+            for (int c = 0; c < CPL; ++c) {
+              float4 one[QV];
+#pragma unroll
+              for (int v = 0; v < QV; ++v) one[v] = q[u][c * QV + v];
+              unpack_row<BP_, PACK>(one, pj);
+#pragma unroll
+              for (int b = 0; b < NB; ++b) acc[b] += w[u][c] * pj[b];
+              if (QUAD) {
+                float dws = 0.f;
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+                  if (zm & (1u << b)) dws += pj[b];
+                dwq += dws * basis_s[((sids >> (8 * u)) & 127u) * R_ + lch * CPL + c];
+              }
+            }
             const int j = ps.jb + u * SPG + lsyn;
             if (QUAD) {
-              float dwv = 0.f;
-#pragma unroll
-              for (int b = 0; b < NB; ++b)
-                if (zm & (1u << b)) dwv += pj[b];
-              // contract with the synapse's basis row over the four lanes of the quad
-              dwv *= basis_s[((sids >> (8 * u)) & 127u) * R_ + lch];
-              dwv += __shfl_xor_sync(0xffffffffu, dwv, 1);
-              dwv += __shfl_xor_sync(0xffffffffu, dwv, 2);
-              if (j < ps.j1 && lch == 0) a.dw_rec[j] += dwv;  // this lane is the only writer of the synapse
+              // contract with the synapse's basis row over the lanes that share the synapse
+              if (LPS >= 2) dwq += __shfl_xor_sync(0xffffffffu, dwq, 1);
+              if (LPS == 4) dwq += __shfl_xor_sync(0xffffffffu, dwq, 2);
+              if (j < ps.j1 && lch == 0) a.dw_rec[j] += dwq;  // this lane is the only writer of the synapse
             } else if (j < ps.j1) {
               float dwv = 0.f;
 #pragma unroll
