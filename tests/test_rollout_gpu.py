@@ -364,6 +364,37 @@ def test_bptt_batch_of_five(options):
         assert rel_err(got, want) <= TOL_GRAD
 
 
+def test_forward_rollout_of_more_trials_than_one_launch_takes():
+    """Ten trials (the reference's evaluation batch, ``osi_dsi_estimator.py:424``) run as groups of at most
+    8: spikes equal the oracle's for every trial, the carried state is that of one wide rollout, counts
+    drawn by the library follow the batch row, and a saved rollout of that width is refused."""
+    cfg, dicts, orc, cell = _cells("small", **KW)
+    x, c = make_inputs(cfg, batch=10, seq_len=30)
+    zo, vo, so = orc.rollout(torch.from_numpy(x), torch.from_numpy(c).long())
+    xd, cd = torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda()
+    state = cell.zero_state(10)
+    z, v = cell.rollout(xd, cd, state=state)
+    cell.synchronize()
+    assert torch.equal(z.cpu().float(), zo.detach())
+    assert rel_err(v, vo.detach()) <= TOL_STATE
+    assert torch.equal(state[0].cpu(), so[0].detach()) and rel_err(state[5], so[5].detach()) <= TOL_STATE
+    assert state[6].cpu().tolist() == [30] * 10
+    # continuing from the carried state equals one rollout of both halves
+    z2, _ = cell.rollout(xd, cd, state=state)
+    x2, c2 = np.concatenate([x, x], 1), np.concatenate([c, c], 1)
+    zo2, _, _ = orc.rollout(torch.from_numpy(x2), torch.from_numpy(c2).long())
+    assert torch.equal(z2.cpu().float(), zo2.detach()[:, 30:])
+    # counts drawn inside: the draw of a trial depends on its batch row, not on its place in a group
+    cell.set_noise_seed(5)
+    drawn = cell.sample_bkg_counts(10, 30)
+    za, _ = cell.rollout(xd, drawn)
+    zb, _ = cell.rollout(xd)
+    cell.synchronize()
+    assert torch.equal(za, zb) and not torch.equal(drawn[0], drawn[8])
+    with pytest.raises(ValueError):
+        cell.rollout(xd, cd, save_for_bwd=True)
+
+
 @pytest.mark.parametrize("batch,nrec,options", [
     (3, 4, ()),                      # lane quads over fp32 16-byte rows
     (5, 4, ()),                      # lane quads over 24-bit rows

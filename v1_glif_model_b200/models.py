@@ -517,10 +517,36 @@ class V1Column:
         n = self._n_neurons
         z = torch.empty((b, t_len, n), dtype=torch.uint8, device=self.device) if return_z else None
         v = torch.empty((b, t_len, n), dtype=torch.float32, device=self.device) if return_v else None
+        if b > _lib.MAX_BATCH:
+            return self._rollout_wide(x, bkg_counts, state, z, v, save_for_bwd)
         st = C.byref(self._state_struct(state)) if state is not None else None
         self._saved = (x, bkg_counts) if save_for_bwd else None
         self._check(self._lib.v1g_rollout_fwd(self._libh, b, t_len, _ptr(x), _ptr(bkg_counts), st,
                                               _ptr(z), _ptr(v), int(save_for_bwd), _stream()))
+        return z, v
+
+    def _rollout_wide(self, x, bkg_counts, state, z, v, save_for_bwd):
+        """Forward rollout of more trials than one kernel launch takes (``V1G_MAX_BATCH``; the reference
+        evaluates 10 trials per angle, ``osi_dsi_estimator.py:424``): trials are independent, so the
+        batch runs as consecutive groups of at most 8, each on its rows of the inputs, outputs and state.
+        Counts that the library is to draw are drawn for the whole batch first, so that row ``i`` gets the
+        noise of batch row ``i`` and not that of its position inside a group."""
+        if save_for_bwd:
+            raise ValueError(f"a rollout saved for the backward pass holds at most {_lib.MAX_BATCH} trials per GPU")
+        b, t_len = x.shape[0], x.shape[1]
+        if bkg_counts is None:
+            first = 0
+            if state is not None and len(state) > 6 and isinstance(state[6], torch.Tensor):
+                first = int(state[6][0])
+            bkg_counts = self.sample_bkg_counts(b, t_len, first_step=first)
+        for lo in range(0, b, _lib.MAX_BATCH):
+            hi = min(b, lo + _lib.MAX_BATCH)
+            sub = tuple(s[lo:hi] for s in state) if state is not None else None
+            st = C.byref(self._state_struct(sub)) if sub is not None else None
+            self._check(self._lib.v1g_rollout_fwd(
+                self._libh, hi - lo, t_len, _ptr(x[lo:hi]), _ptr(bkg_counts[lo:hi]), st,
+                _ptr(z[lo:hi]) if z is not None else None, _ptr(v[lo:hi]) if v is not None else None, 0, _stream()))
+        self._saved = None
         return z, v
 
     def rollout_rates(self, rates, lgn_seed, batch_size, bkg_counts=None, state=None, return_z=True,
