@@ -15,7 +15,8 @@
 // with taps outside the frame dropped (they are the zero padding; their weights are stored as 0 and
 // the coordinates clamped, so the inner loop has no branch).  Stencils are sorted by side and stored
 // in groups of 32, one per lane of a warp, tap-major (weight of tap p of lane l at [p][l]), so a warp
-// reads one 128-byte line per tap and its lanes run the same trip count.  A thread block takes two
+// reads one 128-byte line per tap and its lanes run the same trip count; inside a side they are
+// ordered so that the lanes of a group fall on different shared-memory banks.  A thread block takes two
 // frames, interleaved pixel by pixel, into shared memory (two 120 x 240 frames are 225 KB) and
 // evaluates every stencil on both from there: the movie is read from HBM once, a weight fetched from
 // L2 serves two frames, and one 8-byte shared-memory load brings both pixels.  The temporal filter
@@ -248,6 +249,43 @@ extern "C" int v1g_lgn_create(const V1GLgnTables* tb, V1GLgn** out) {
   std::vector<int> order((size_t)2 * U);
   for (int i = 0; i < 2 * U; ++i) order[i] = i;
   std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return sts[a].side < sts[b].side; });
+  // Bank conflicts.  The 32 lanes of a group read the same tap (dy, dx) of 32 different patches, so the
+  // shared-memory bank of a lane is fixed by its patch corner: (y0 * W + x0) modulo M, M = 16 pixel
+  // pairs when two frames are interleaved (a half warp per wavefront), 32 pixels with one frame.
+  // Within a run of equal side the stencils are therefore dealt out round-robin over the M residues,
+  // so that (almost) every M consecutive lanes hit M different banks: an 8-byte load then takes
+  // about 2 wavefronts instead of the 6 that randomly placed patches take (5.7 -> 4.1 ms per 1000
+  // frames of 17,400 units).  Measured on top of it and slower: a branch for groups whose patches
+  // all lie inside the frame (no clamping, tap offsets from a table per side; 4.8 ms, the groups
+  // that cross the edge then cluster), and a warp per stencil with its lanes on consecutive taps
+  // (12.5 ms: one stencil's dependent loads at a time per warp).
+  {
+    cudaDeviceProp prop0;
+    int dev0 = 0;
+    if (cudaGetDevice(&dev0) != cudaSuccess || cudaGetDeviceProperties(&prop0, dev0) != cudaSuccess)
+      return lgn_fail(nullptr, V1G_ECUDA, "v1g_lgn_create: no CUDA device");
+    const int M = 2 * (size_t)H * W * sizeof(float) <= prop0.sharedMemPerBlockOptin ? 16 : 32;
+    std::vector<int> dealt;
+    dealt.reserve(order.size());
+    for (size_t lo = 0; lo < order.size();) {
+      size_t hi = lo;
+      while (hi < order.size() && sts[order[hi]].side == sts[order[lo]].side) ++hi;
+      std::vector<std::vector<int>> bucket((size_t)M);
+      for (size_t i = lo; i < hi; ++i) {
+        const Stencil& st = sts[order[i]];
+        const long long key = (long long)st.y0 * W + st.x0;
+        bucket[(size_t)(((key % M) + M) % M)].push_back(order[i]);
+      }
+      for (size_t round = 0, left = hi - lo; left > 0; ++round)
+        for (int r = 0; r < M; ++r)
+          if (round < bucket[(size_t)r].size()) {
+            dealt.push_back(bucket[(size_t)r][round]);
+            --left;
+          }
+      lo = hi;
+    }
+    order.swap(dealt);
+  }
   const int n_groups = (2 * U + 31) / 32;
   std::vector<int2> grp((size_t)n_groups);
   std::vector<int4> slot((size_t)n_groups * 32, make_int4(0, 0, -1, 0));
