@@ -633,46 +633,66 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           if (b < B) sadd[b] += a.osi_coef[(int64_t)b * N + n];
       }
       float dyv[NBX][R_];  // dy(t-2) of every batch row of this neuron
+      // PRE: the adjoint state lives in a global slab (slices that do not fit in shared memory).  The
+      // loop below stores after every load, and a load may not pass an earlier store to the same
+      // array, so each of the 13 reads of a batch row would wait a full L2 round trip on its own;
+      // with the row's state requested up front they overlap.
+      auto state_update = [&](auto PRE_) {
+        constexpr bool PRE = decltype(PRE_)::value;
 #pragma unroll
-      for (int b = 0; b < NBX; ++b) {
+        for (int b = 0; b < NBX; ++b) {
 #pragma unroll
-        for (int r = 0; r < R_; ++r) dyv[b][r] = 0.f;
-        if (b < B) {
-          const int si = b * chunkP + k;
-          const float v = PAIR ? __uint_as_float(twr[b] & ~3u) : tvC[si];
-          const unsigned zr = PAIR ? (twr[b] & 3u) : (unsigned)tzC[si];
-          const bool free_ = !(zr & 2u);
-          const int64_t oi = ((int64_t)b * T + t) * N + n;
-          float gz = rc + (bin >= 0 ? a.sgrad[b * a.nbins + bin] : 0.f) + (a.g_z ? a.g_z[oi] : 0.f);
-          gz += sadd[b];
-          gz += a.rec_factor * (PAIR ? gzr[b] : gzC[si]);
-          float gv = G_v[si] + (a.g_v ? a.g_v[oi] : 0.f);
-          if (a.volt_coef != 0.f) {
-            // range mode: outside [vlo, 1]; threshold mode: distance from the threshold
-            const float hi = a.volt_threshold_mode ? v - 1.f : fmaxf(v - 1.f, 0.f);
-            const float lo = a.volt_threshold_mode ? 0.f : fmaxf(vlo - v, 0.f);
-            gv += 2.f * a.volt_coef * (hi - lo);
-            volt_loss += hi * hi + lo * lo;
-          }
-          if (free_) gv += gz * pseudo_h(v - 1.f, a);
-          if (a.hard_reset && !free_) gv = 0.f;
-          G_v[si] = k_decay * a.vd_keep * gv;
-          const float gc1 = k_cf * gv;
-          G_a0[si] = k_ad0 * G_a0[si] + gc1;
-          G_a1[si] = k_ad1 * G_a1[si] + gc1;
+          for (int r = 0; r < R_; ++r) dyv[b][r] = 0.f;
+          if (b < B) {
+            const int si = b * chunkP + k;
+            float sv = 0.f, s0 = 0.f, s1 = 0.f, sp[R_], spr[R_];
+            if (PRE) {
+              sv = G_v[si];
+              s0 = G_a0[si];
+              s1 = G_a1[si];
 #pragma unroll
-          for (int r = 0; r < R_; ++r) {
-            const int pi = (r * B + b) * chunkP + k;
-            const float gp = G_p[pi], gpr = G_pr[pi];
-            const float gp1 = a.sd[r] * gp + gc1;                // g_p(t-1)
-            const float gpr1 = a.sd[r] * gpr + a.dtsd[r] * gp;   // g_pr(t-1)
-            G_p[pi] = gp1;
-            G_pr[pi] = gpr1;
-            const float gpr2 = a.sd[r] * gpr1 + a.dtsd[r] * gp1;  // g_pr(t-2)
-            dyv[b][r] = (gpr2 * a.pinit[r]) * a.lr_scale;
+              for (int r = 0; r < R_; ++r) {
+                sp[r] = G_p[(r * B + b) * chunkP + k];
+                spr[r] = G_pr[(r * B + b) * chunkP + k];
+              }
+            }
+            const float v = PAIR ? __uint_as_float(twr[b] & ~3u) : tvC[si];
+            const unsigned zr = PAIR ? (twr[b] & 3u) : (unsigned)tzC[si];
+            const bool free_ = !(zr & 2u);
+            const int64_t oi = ((int64_t)b * T + t) * N + n;
+            float gz = rc + (bin >= 0 ? a.sgrad[b * a.nbins + bin] : 0.f) + (a.g_z ? a.g_z[oi] : 0.f);
+            gz += sadd[b];
+            gz += a.rec_factor * (PAIR ? gzr[b] : gzC[si]);
+            float gv = (PRE ? sv : G_v[si]) + (a.g_v ? a.g_v[oi] : 0.f);
+            if (a.volt_coef != 0.f) {
+              // range mode: outside [vlo, 1]; threshold mode: distance from the threshold
+              const float hi = a.volt_threshold_mode ? v - 1.f : fmaxf(v - 1.f, 0.f);
+              const float lo = a.volt_threshold_mode ? 0.f : fmaxf(vlo - v, 0.f);
+              gv += 2.f * a.volt_coef * (hi - lo);
+              volt_loss += hi * hi + lo * lo;
+            }
+            if (free_) gv += gz * pseudo_h(v - 1.f, a);
+            if (a.hard_reset && !free_) gv = 0.f;
+            G_v[si] = k_decay * a.vd_keep * gv;
+            const float gc1 = k_cf * gv;
+            G_a0[si] = k_ad0 * (PRE ? s0 : G_a0[si]) + gc1;
+            G_a1[si] = k_ad1 * (PRE ? s1 : G_a1[si]) + gc1;
+#pragma unroll
+            for (int r = 0; r < R_; ++r) {
+              const int pi = (r * B + b) * chunkP + k;
+              const float gp = PRE ? sp[r] : G_p[pi], gpr = PRE ? spr[r] : G_pr[pi];
+              const float gp1 = a.sd[r] * gp + gc1;                // g_p(t-1)
+              const float gpr1 = a.sd[r] * gpr + a.dtsd[r] * gp;   // g_pr(t-1)
+              G_p[pi] = gp1;
+              G_pr[pi] = gpr1;
+              const float gpr2 = a.sd[r] * gpr1 + a.dtsd[r] * gp1;  // g_pr(t-2)
+              dyv[b][r] = (gpr2 * a.pinit[r]) * a.lr_scale;
+            }
           }
         }
-      }
+      };
+      if (a.state_in_smem) state_update(std::false_type{});
+      else state_update(std::true_type{});
       if (t >= 2) {
         // one 16/32-byte row per channel, all batch rows of the neuron at once
         float4* qd = (float4*)(Qw + (int64_t)n * C * RS);

@@ -288,13 +288,25 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
       const int n = n0 + k;
       const int si = b * chunkP + k;
       if (consume) finish_input(b, k, slot, cnt_s, I);
+      // The whole state of the entry is read before any of it is written back: a load may not pass
+      // an earlier store to the same array, and when the state lives in a global slab every read that
+      // had to wait for the stores before it cost an L2 round trip of its own.
       const unsigned hist = S_hist[si];
+      float pr_in[R_], p_in[R_];
+#pragma unroll
+      for (int r = 0; r < R_; ++r) {
+        pr_in[r] = S_pr[(r * B + b) * chunkP + k];
+        p_in[r] = S_p[(r * B + b) * chunkP + k];
+      }
+      const float a0 = S_a0[si], a1 = S_a1[si];
+      const float v = S_v[si];
+      const int r_in = (int)S_r[si];
       const float prev_z = (hist & 1u) ? 1.f : 0.f;
       float csum = 0.f;
 #pragma unroll
       for (int r = 0; r < R_; ++r) {
         const int pi = (r * B + b) * chunkP + k;
-        float pr = S_pr[pi], p = S_p[pi];
+        float pr = pr_in[r], p = p_in[r];
         if (consume) {
           pr = pr * a.sd[r] + I[r] * a.pinit[r];  // psc_rise(t-2)
           S_pr[pi] = pr;
@@ -305,14 +317,12 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
         }
         csum = (r == 0) ? p : csum + p;
       }
-      const float a0 = S_a0[si], a1 = S_a1[si];
       S_a0[si] = c_ad0[k] * a0 + prev_z * c_am0[k];
       S_a1[si] = c_ad1[k] * a1 + prev_z * c_am1[k];
       const float c1 = csum + (a0 + a1);
-      const float v = S_v[si];
       const float dv = v * a.vd_keep + v * a.vd_drop;
       float nv = (c_decay[k] * dv + c_cf[k] * c1) - prev_z;
-      int nr = (int)S_r[si] + ((hist & 1u) ? c_tref[k] : 0) - 1;
+      int nr = r_in + ((hist & 1u) ? c_tref[k] : 0) - 1;
       nr = nr > 0 ? nr : 0;
       if (a.hard_reset && nr > 0) nv = 0.f;
       const bool z = ((nv - 1.f) > 0.f) && (nr == 0);
