@@ -725,9 +725,8 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         }
         // background weight gradient of step t-2 for the synapses this thread owns (branch-free:
         // a zero count contributes zero)
-        for (int j = bkptr_s[k]; j < bkptr_s[k + 1]; ++j) {
-          const int pre = bk_pre[j];
-          const float* bs = basis_s + (int)bk_sid[j] * R_;
+        auto bkg_grad = [&](int pre, int sid) {
+          const float* bs = basis_s + sid * R_;
           float bsr[R_];
 #pragma unroll
           for (int r = 0; r < R_; ++r) bsr[r] = bs[r];
@@ -741,7 +740,28 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
               accw += s2 * s_cnt[b * a.n_bkg + pre];
             }
           }
-          if (a.bkg_in_smem || accw != 0.f) bk_dw[j] += accw;
+          return accw;
+        };
+        if (a.bkg_in_smem) {
+          for (int j = bkptr_s[k]; j < bkptr_s[k + 1]; ++j) bk_dw[j] += bkg_grad(bk_pre[j], (int)bk_sid[j]);
+        } else {
+          // tables and accumulators in global memory: four synapses' entries are requested together
+          for (int j0 = bkptr_s[k], j1 = bkptr_s[k + 1]; j0 < j1; j0 += 4) {
+            int pre[4], sid[4];
+            float old[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int j = min(j0 + u, j1 - 1);
+              pre[u] = bk_pre[j];
+              sid[u] = (int)bk_sid[j];
+              old[u] = bk_dw[j];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float accw = bkg_grad(pre[u], sid[u]);
+              if (j0 + u < j1 && accw != 0.f) bk_dw[j0 + u] = old[u] + accw;
+            }
+          }
         }
       }
     }
