@@ -973,172 +973,294 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
         }
       }
     } else if (fast_rows) {
-      // Packed-record path.  The unit of work is a pass: up to UF*32 consecutive synapses of one
-      // row, one 8-byte record per synapse.  Warps draw rows from the queue of row descriptors
-      // written in phase A.  Each warp keeps the records of the pass after next
-      // and the Q rows of the next pass in flight while it accumulates the current one.  Registers
-      // that receive a load are never copied while the load is in flight (a copy would wait for
-      // it): the loop body is written out once per Q buffer, NS buffers in rotation.
-      // The Q row index comes from a per-step table of the D slot bases.  Steps past the end of
-      // the rollout need no test: their ring slots still hold the zeros of the initial clear.
-      // Lanes past the end of a row read a neighbouring record (always inside the array) and get
-      // weight zero.
-      // Raw mode (more than 8 synapse types: the ring holds the R = 4 channels of a neuron as four
-      // consecutive 16-byte rows, one 64-byte half line): LPS lanes share a synapse, each taking
-      // CPL = 4 / LPS channels, so that one load instruction touches one line per synapse instead of
-      // four; a lane accumulates w * basis[sid][c] * Q[post][c][b] over its channels, and the reduction
-      // over the warp at the end of the row sums channels and synapses alike.
-      constexpr bool QUAD = !PROJ;
-      constexpr int LPS = QUAD ? V1G_BWD_RAW_LANES : 1;  // lanes per synapse
-      constexpr int CPL = QUAD ? 4 / LPS : 1;            // channels (16-byte rows) a lane loads
-      constexpr int SPG = 32 / LPS;          // synapses per 32-lane group
-      constexpr int NB = PACK ? 5 : BP_;     // batch values a row really carries
-      constexpr int QV = QW / 4;             // 16-byte words per Q row
-      constexpr int QVL = QV * CPL;          // 16-byte words per lane and synapse
-      constexpr int UF = QUAD ? V1G_BWD_RAW_GROUPS : QV == 1 ? V1G_BWD_GROUPS : 2;  // 32-lane groups per pass
-      static_assert(!QUAD || UF <= 4, "the synapse types of a pass are kept as four 8-bit fields of one word");
-      constexpr int SPP = SPG * UF;          // synapses per pass
-      const int lsyn = lane / LPS, lch = lane % LPS;
-      constexpr int NS = V1G_BWD_STAGES;
-      struct Pass { int jb, j1, kz, fl; };   // kz = row | spike mask << 16; fl: 1 first pass of its row, 4 valid
-      const int jmax = a.rec_nnz - 1;
-      Pass pr{0, 0, 0, 0};
-      Pass ps_[NS];
-      uint2 rec[UF];
-      float4 qS[NS][UF][QVL];
-      float wS[NS][UF][CPL];
-      unsigned sidS[QUAD ? NS : 1];  // raw mode: the synapse types of the pass, 8 bits per group (for the weight gradient)
-      float acc[BP_];
+      // Two forms of the same pipeline, chosen at compile time.  The projected one (one lane per
+      // synapse, one 16/32-byte row) is kept apart from the raw one (lanes sharing a synapse):
+      // written as one generic body the projected kernel ran 0.3 % slower.
+      if (PROJ) {
+        // Packed-record path.  The unit of work is a pass: up to UF*32 consecutive synapses of one
+        // row, one 8-byte record per synapse.  Warps draw rows from the queue of row descriptors
+        // written in phase A.  Each warp keeps the records of the pass after next
+        // and the Q rows of the next pass in flight while it accumulates the current one.  Registers
+        // that receive a load are never copied while the load is in flight (a copy would wait for
+        // it): the loop body is written out once per Q buffer, NS buffers in rotation.
+        // The Q row index comes from a per-step table of the D slot bases.  Steps past the end of
+        // the rollout need no test: their ring slots still hold the zeros of the initial clear.
+        // Lanes past the end of a row read a neighbouring record (always inside the array) and get
+        // weight zero.
+        constexpr int NB = PACK ? 5 : BP_;     // batch values a row really carries
+        constexpr int QV = QW / 4;             // 16-byte words per Q row
+        constexpr int UF = QV == 1 ? V1G_BWD_GROUPS : 2;  // 32-synapse groups per pass
+        constexpr int NS = V1G_BWD_STAGES;
+        struct Pass { int jb, j1, kz, fl; };   // kz = row | spike mask << 16; fl: 1 first pass of its row, 4 valid
+        const int jmax = a.rec_nnz - 1;
+        Pass pr{0, 0, 0, 0};
+        Pass ps_[NS];
+        uint2 rec[UF];
+        float4 qS[NS][UF][QV];
+        float wS[NS][UF];
+        float acc[BP_];
 #pragma unroll
-      for (int i = 0; i < NS; ++i) ps_[i] = Pass{0, 0, 0, 0};
+        for (int i = 0; i < NS; ++i) ps_[i] = Pass{0, 0, 0, 0};
 #pragma unroll
-      for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
-      auto issue_rec = [&]() {  // advance pr to the following pass and request its records
-        if (pr.fl && pr.jb + SPP < pr.j1) {
-          pr.jb += SPP;
-          pr.fl = 4;
-        } else {
-          const int q = pop_row();  // warps that drew long rows, or rows with spikes, take fewer
-          if (q < nq) {
-            const int4 d = rowd_s[q];
-            pr = Pass{d.x, d.y, d.z, 5};
+        for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
+        auto issue_rec = [&]() {  // advance pr to the following pass and request its records
+          if (pr.fl && pr.jb + 32 * UF < pr.j1) {
+            pr.jb += 32 * UF;
+            pr.fl = 4;
           } else {
-            pr = Pass{0, 0, 0, 0};
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < UF; ++u) rec[u] = __ldcs(a.rec_syn8 + min(pr.jb + u * SPG + lsyn, jmax));
-      };
-      auto issue_q = [&](const Pass& ps, float4 (&q)[UF][QVL], float (&w)[UF][CPL], unsigned& sids) {  // Q rows of the pass in rec
-        if (QUAD) sids = 0u;
-#pragma unroll
-        for (int u = 0; u < UF; ++u) {
-          const bool in_row = ps.jb + u * SPG + lsyn < ps.j1;
-          const unsigned w0 = rec[u].x;
-          const unsigned sid = (w0 >> 22) & 127u;
-          unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + (QUAD ? (unsigned)(lch * CPL) : sid);
-          row = in_row ? row : 0u;  // lanes past the end of the row share one request
-          const float4* qp = (const float4*)(a.Q + row * (unsigned)QW);  // < 2^31 words, checked by the host
-          if (QVL == 2 && CPL == 2) {
-            load_pair((const float*)qp, q[u][0], q[u][QVL - 1]);  // two channels with one 256-bit load
-          } else if (QVL == 4 && CPL == 4) {
-            load_pair((const float*)qp, q[u][0], q[u][1 % QVL]);
-            load_pair((const float*)(qp + 2), q[u][2 % QVL], q[u][3 % QVL]);
-          } else {
-#pragma unroll
-            for (int v = 0; v < QVL; ++v) q[u][v] = __ldcg(qp + v);
-          }
-          const float wt = in_row ? __uint_as_float(rec[u].y) : 0.f;
-#pragma unroll
-          for (int c = 0; c < CPL; ++c) w[u][c] = QUAD ? wt * basis_s[sid * R_ + lch * CPL + c] : wt;
-          if (QUAD) sids |= sid << (8 * u);
-        }
-      };
-      auto compute = [&](const Pass& ps, const float4 (&q)[UF][QVL], const float (&w)[UF][CPL], unsigned sids) {
-        if (ps.fl & 1) {
-#pragma unroll
-          for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
-        }
-        const unsigned zm = (unsigned)ps.kz >> 16;
-        if (!zm) {
-#pragma unroll
-          for (int u = 0; u < UF; ++u) {
-#pragma unroll
-            for (int c = 0; c < CPL; ++c) {
-              float4 one[QV];
-#pragma unroll
-              for (int v = 0; v < QV; ++v) one[v] = q[u][c * QV + v];
-              float pj[BP_];
-              unpack_row<BP_, PACK>(one, pj);
-#pragma unroll
-              for (int b = 0; b < NB; ++b) acc[b] += w[u][c] * pj[b];
+            const int q = pop_row();  // warps that drew long rows, or rows with spikes, take fewer
+            if (q < nq) {
+              const int4 d = rowd_s[q];
+              pr = Pass{d.x, d.y, d.z, 5};
+            } else {
+              pr = Pass{0, 0, 0, 0};
             }
           }
-        } else {
-          // the source neuron spiked at this step in the batch rows of zm: weight gradient
+#pragma unroll
+          for (int u = 0; u < UF; ++u) rec[u] = __ldcs(a.rec_syn8 + min(pr.jb + u * 32 + lane, jmax));
+        };
+        auto issue_q = [&](const Pass& ps, float4 (&q)[UF][QV], float (&w)[UF]) {  // Q rows of the pass in rec
 #pragma unroll
           for (int u = 0; u < UF; ++u) {
-            float pj[BP_];
-            float dwq = 0.f;  // raw mode: this lane's share of the synapse's weight gradient
+            const bool in_row = ps.jb + u * 32 + lane < ps.j1;
+            const unsigned w0 = rec[u].x;
+            unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + ((w0 >> 22) & 127u);
+            row = in_row ? row : 0u;  // lanes past the end of the row share one request
+            const float4* qp = (const float4*)(a.Q + row * (unsigned)QW);  // < 2^31 words, checked by the host
 #pragma unroll
-            for (int c = 0; c < CPL; ++c) {
-              float4 one[QV];
+            for (int v = 0; v < QV; ++v) q[u][v] = __ldcg(qp + v);
+            w[u] = in_row ? __uint_as_float(rec[u].y) : 0.f;
+          }
+        };
+        auto compute = [&](const Pass& ps, const float4 (&q)[UF][QV], const float (&w)[UF]) {
+          if (ps.fl & 1) {
 #pragma unroll
-              for (int v = 0; v < QV; ++v) one[v] = q[u][c * QV + v];
-              unpack_row<BP_, PACK>(one, pj);
+            for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
+          }
+          const unsigned zm = (unsigned)ps.kz >> 16;
+          if (!zm) {
 #pragma unroll
-              for (int b = 0; b < NB; ++b) acc[b] += w[u][c] * pj[b];
-              if (QUAD) {
-                float dws = 0.f;
+            for (int u = 0; u < UF; ++u) {
+              float pj[BP_];
+              unpack_row<BP_, PACK>(q[u], pj);
+#pragma unroll
+              for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
+            }
+          } else {
+            // the source neuron spiked at this step in the batch rows of zm: weight gradient
+#pragma unroll
+            for (int u = 0; u < UF; ++u) {
+              float pj[BP_];
+              unpack_row<BP_, PACK>(q[u], pj);
+#pragma unroll
+              for (int b = 0; b < NB; ++b) acc[b] += w[u] * pj[b];
+              const int j = ps.jb + u * 32 + lane;
+              if (j < ps.j1) {
+                float dwv = 0.f;
 #pragma unroll
                 for (int b = 0; b < NB; ++b)
-                  if (zm & (1u << b)) dws += pj[b];
-                dwq += dws * basis_s[((sids >> (8 * u)) & 127u) * R_ + lch * CPL + c];
+                  if (zm & (1u << b)) dwv += pj[b];
+                a.dw_rec[j] += dwv;  // this lane is the only writer of the synapse
               }
             }
-            const int j = ps.jb + u * SPG + lsyn;
-            if (QUAD) {
-              // contract with the synapse's basis row over the lanes that share the synapse
-              if (LPS >= 2) dwq += __shfl_xor_sync(0xffffffffu, dwq, 1);
-              if (LPS == 4) dwq += __shfl_xor_sync(0xffffffffu, dwq, 2);
-              if (j < ps.j1 && lch == 0) a.dw_rec[j] += dwq;  // this lane is the only writer of the synapse
-            } else if (j < ps.j1) {
-              float dwv = 0.f;
+          }
+          if (ps.jb + 32 * UF >= ps.j1) reduce_store(acc, ps.kz & 0xffff);
+        };
+        // one turn of the pipeline with buffer I: false when the warp has no further pass
+        auto turn = [&](auto I) -> bool {
+          constexpr int i = decltype(I)::value;
+          if (!pr.fl) {
+            // accumulate what is still in flight, oldest first
 #pragma unroll
-              for (int b = 0; b < NB; ++b)
-                if (zm & (1u << b)) dwv += pj[b];
-              a.dw_rec[j] += dwv;  // this lane is the only writer of the synapse
+            for (int o = 1; o < NS; ++o)
+              if (ps_[(i + o) % NS].fl) compute(ps_[(i + o) % NS], qS[(i + o) % NS], wS[(i + o) % NS]);
+            return false;
+          }
+          ps_[i] = pr;
+          issue_q(ps_[i], qS[i], wS[i]);
+          issue_rec();
+          constexpr int x = (i + 1) % NS;  // the oldest pass
+          if (ps_[x].fl) {
+            compute(ps_[x], qS[x], wS[x]);
+            ps_[x].fl = 0;
+          }
+          return true;
+        };
+        issue_rec();
+        for (;;) {
+          if (!turn(std::integral_constant<int, 0>{})) break;
+          if (!turn(std::integral_constant<int, 1 % NS>{})) break;
+          if (NS > 2 && !turn(std::integral_constant<int, 2 % NS>{})) break;
+          if (NS > 3 && !turn(std::integral_constant<int, 3 % NS>{})) break;
+        }
+      } else {
+        // Packed-record path.  The unit of work is a pass: up to UF*32 consecutive synapses of one
+        // row, one 8-byte record per synapse.  Warps draw rows from the queue of row descriptors
+        // written in phase A.  Each warp keeps the records of the pass after next
+        // and the Q rows of the next pass in flight while it accumulates the current one.  Registers
+        // that receive a load are never copied while the load is in flight (a copy would wait for
+        // it): the loop body is written out once per Q buffer, NS buffers in rotation.
+        // The Q row index comes from a per-step table of the D slot bases.  Steps past the end of
+        // the rollout need no test: their ring slots still hold the zeros of the initial clear.
+        // Lanes past the end of a row read a neighbouring record (always inside the array) and get
+        // weight zero.
+        // Raw mode (more than 8 synapse types: the ring holds the R = 4 channels of a neuron as four
+        // consecutive 16-byte rows, one 64-byte half line): LPS lanes share a synapse, each taking
+        // CPL = 4 / LPS channels, so that one load instruction touches one line per synapse instead of
+        // four; a lane accumulates w * basis[sid][c] * Q[post][c][b] over its channels, and the reduction
+        // over the warp at the end of the row sums channels and synapses alike.
+        constexpr bool QUAD = !PROJ;
+        constexpr int LPS = QUAD ? V1G_BWD_RAW_LANES : 1;  // lanes per synapse
+        constexpr int CPL = QUAD ? 4 / LPS : 1;            // channels (16-byte rows) a lane loads
+        constexpr int SPG = 32 / LPS;          // synapses per 32-lane group
+        constexpr int NB = PACK ? 5 : BP_;     // batch values a row really carries
+        constexpr int QV = QW / 4;             // 16-byte words per Q row
+        constexpr int QVL = QV * CPL;          // 16-byte words per lane and synapse
+        constexpr int UF = QUAD ? V1G_BWD_RAW_GROUPS : QV == 1 ? V1G_BWD_GROUPS : 2;  // 32-lane groups per pass
+        static_assert(!QUAD || UF <= 4, "the synapse types of a pass are kept as four 8-bit fields of one word");
+        constexpr int SPP = SPG * UF;          // synapses per pass
+        const int lsyn = lane / LPS, lch = lane % LPS;
+        constexpr int NS = V1G_BWD_STAGES;
+        struct Pass { int jb, j1, kz, fl; };   // kz = row | spike mask << 16; fl: 1 first pass of its row, 4 valid
+        const int jmax = a.rec_nnz - 1;
+        Pass pr{0, 0, 0, 0};
+        Pass ps_[NS];
+        uint2 rec[UF];
+        float4 qS[NS][UF][QVL];
+        float wS[NS][UF][CPL];
+        unsigned sidS[QUAD ? NS : 1];  // raw mode: the synapse types of the pass, 8 bits per group (for the weight gradient)
+        float acc[BP_];
+#pragma unroll
+        for (int i = 0; i < NS; ++i) ps_[i] = Pass{0, 0, 0, 0};
+#pragma unroll
+        for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
+        auto issue_rec = [&]() {  // advance pr to the following pass and request its records
+          if (pr.fl && pr.jb + SPP < pr.j1) {
+            pr.jb += SPP;
+            pr.fl = 4;
+          } else {
+            const int q = pop_row();  // warps that drew long rows, or rows with spikes, take fewer
+            if (q < nq) {
+              const int4 d = rowd_s[q];
+              pr = Pass{d.x, d.y, d.z, 5};
+            } else {
+              pr = Pass{0, 0, 0, 0};
             }
           }
-        }
-        if (ps.jb + SPP >= ps.j1) reduce_store(acc, ps.kz & 0xffff);
-      };
-      // one turn of the pipeline with buffer I: false when the warp has no further pass
-      auto turn = [&](auto I) -> bool {
-        constexpr int i = decltype(I)::value;
-        if (!pr.fl) {
-          // accumulate what is still in flight, oldest first
 #pragma unroll
-          for (int o = 1; o < NS; ++o)
-            if (ps_[(i + o) % NS].fl) compute(ps_[(i + o) % NS], qS[(i + o) % NS], wS[(i + o) % NS], sidS[QUAD ? (i + o) % NS : 0]);
-          return false;
-        }
-        ps_[i] = pr;
-        issue_q(ps_[i], qS[i], wS[i], sidS[QUAD ? i : 0]);
+          for (int u = 0; u < UF; ++u) rec[u] = __ldcs(a.rec_syn8 + min(pr.jb + u * SPG + lsyn, jmax));
+        };
+        auto issue_q = [&](const Pass& ps, float4 (&q)[UF][QVL], float (&w)[UF][CPL], unsigned& sids) {  // Q rows of the pass in rec
+          if (QUAD) sids = 0u;
+#pragma unroll
+          for (int u = 0; u < UF; ++u) {
+            const bool in_row = ps.jb + u * SPG + lsyn < ps.j1;
+            const unsigned w0 = rec[u].x;
+            const unsigned sid = (w0 >> 22) & 127u;
+            unsigned row = (unsigned)slot_s[w0 >> 29] + (w0 & 0x3fffffu) * (unsigned)C + (QUAD ? (unsigned)(lch * CPL) : sid);
+            row = in_row ? row : 0u;  // lanes past the end of the row share one request
+            const float4* qp = (const float4*)(a.Q + row * (unsigned)QW);  // < 2^31 words, checked by the host
+            if (QVL == 2 && CPL == 2) {
+              load_pair((const float*)qp, q[u][0], q[u][QVL - 1]);  // two channels with one 256-bit load
+            } else if (QVL == 4 && CPL == 4) {
+              load_pair((const float*)qp, q[u][0], q[u][1 % QVL]);
+              load_pair((const float*)(qp + 2), q[u][2 % QVL], q[u][3 % QVL]);
+            } else {
+#pragma unroll
+              for (int v = 0; v < QVL; ++v) q[u][v] = __ldcg(qp + v);
+            }
+            const float wt = in_row ? __uint_as_float(rec[u].y) : 0.f;
+#pragma unroll
+            for (int c = 0; c < CPL; ++c) w[u][c] = QUAD ? wt * basis_s[sid * R_ + lch * CPL + c] : wt;
+            if (QUAD) sids |= sid << (8 * u);
+          }
+        };
+        auto compute = [&](const Pass& ps, const float4 (&q)[UF][QVL], const float (&w)[UF][CPL], unsigned sids) {
+          if (ps.fl & 1) {
+#pragma unroll
+            for (int b = 0; b < BP_; ++b) acc[b] = 0.f;
+          }
+          const unsigned zm = (unsigned)ps.kz >> 16;
+          if (!zm) {
+#pragma unroll
+            for (int u = 0; u < UF; ++u) {
+#pragma unroll
+              for (int c = 0; c < CPL; ++c) {
+                float4 one[QV];
+#pragma unroll
+                for (int v = 0; v < QV; ++v) one[v] = q[u][c * QV + v];
+                float pj[BP_];
+                unpack_row<BP_, PACK>(one, pj);
+#pragma unroll
+                for (int b = 0; b < NB; ++b) acc[b] += w[u][c] * pj[b];
+              }
+            }
+          } else {
+            // the source neuron spiked at this step in the batch rows of zm: weight gradient
+#pragma unroll
+            for (int u = 0; u < UF; ++u) {
+              float pj[BP_];
+              float dwq = 0.f;  // raw mode: this lane's share of the synapse's weight gradient
+#pragma unroll
+              for (int c = 0; c < CPL; ++c) {
+                float4 one[QV];
+#pragma unroll
+                for (int v = 0; v < QV; ++v) one[v] = q[u][c * QV + v];
+                unpack_row<BP_, PACK>(one, pj);
+#pragma unroll
+                for (int b = 0; b < NB; ++b) acc[b] += w[u][c] * pj[b];
+                if (QUAD) {
+                  float dws = 0.f;
+#pragma unroll
+                  for (int b = 0; b < NB; ++b)
+                    if (zm & (1u << b)) dws += pj[b];
+                  dwq += dws * basis_s[((sids >> (8 * u)) & 127u) * R_ + lch * CPL + c];
+                }
+              }
+              const int j = ps.jb + u * SPG + lsyn;
+              if (QUAD) {
+                // contract with the synapse's basis row over the lanes that share the synapse
+                if (LPS >= 2) dwq += __shfl_xor_sync(0xffffffffu, dwq, 1);
+                if (LPS == 4) dwq += __shfl_xor_sync(0xffffffffu, dwq, 2);
+                if (j < ps.j1 && lch == 0) a.dw_rec[j] += dwq;  // this lane is the only writer of the synapse
+              } else if (j < ps.j1) {
+                float dwv = 0.f;
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+                  if (zm & (1u << b)) dwv += pj[b];
+                a.dw_rec[j] += dwv;  // this lane is the only writer of the synapse
+              }
+            }
+          }
+          if (ps.jb + SPP >= ps.j1) reduce_store(acc, ps.kz & 0xffff);
+        };
+        // one turn of the pipeline with buffer I: false when the warp has no further pass
+        auto turn = [&](auto I) -> bool {
+          constexpr int i = decltype(I)::value;
+          if (!pr.fl) {
+            // accumulate what is still in flight, oldest first
+#pragma unroll
+            for (int o = 1; o < NS; ++o)
+              if (ps_[(i + o) % NS].fl) compute(ps_[(i + o) % NS], qS[(i + o) % NS], wS[(i + o) % NS], sidS[QUAD ? (i + o) % NS : 0]);
+            return false;
+          }
+          ps_[i] = pr;
+          issue_q(ps_[i], qS[i], wS[i], sidS[QUAD ? i : 0]);
+          issue_rec();
+          constexpr int x = (i + 1) % NS;  // the oldest pass
+          if (ps_[x].fl) {
+            compute(ps_[x], qS[x], wS[x], sidS[QUAD ? x : 0]);
+            ps_[x].fl = 0;
+          }
+          return true;
+        };
         issue_rec();
-        constexpr int x = (i + 1) % NS;  // the oldest pass
-        if (ps_[x].fl) {
-          compute(ps_[x], qS[x], wS[x], sidS[QUAD ? x : 0]);
-          ps_[x].fl = 0;
+        for (;;) {
+          if (!turn(std::integral_constant<int, 0>{})) break;
+          if (!turn(std::integral_constant<int, 1 % NS>{})) break;
+          if (NS > 2 && !turn(std::integral_constant<int, 2 % NS>{})) break;
+          if (NS > 3 && !turn(std::integral_constant<int, 3 % NS>{})) break;
         }
-        return true;
-      };
-      issue_rec();
-      for (;;) {
-        if (!turn(std::integral_constant<int, 0>{})) break;
-        if (!turn(std::integral_constant<int, 1 % NS>{})) break;
-        if (NS > 2 && !turn(std::integral_constant<int, 2 % NS>{})) break;
-        if (NS > 3 && !turn(std::integral_constant<int, 3 % NS>{})) break;
       }
     } else
     for (;;) {
