@@ -6,6 +6,8 @@ plainly when TensorFlow is absent."""
 import os
 import re
 
+import pytest
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SHIM = os.path.join(ROOT, "v1_glif_model_b200", "tf_shim")
 
@@ -67,3 +69,21 @@ def test_build_step_reports_missing_tensorflow(capsys):
     if not have_tf:
         assert build_tf_shim.build() is None
         assert "TensorFlow: unavailable on this box" in capsys.readouterr().out
+
+
+def test_shim_source_type_checks_against_the_c_abi():
+    """``g++ -fsyntax-only`` over the shim with the real ``include/v1g.h`` and CUDA runtime header, and
+    declaration-only stand-ins for the TensorFlow headers (``tests/tf_stub``): every C-ABI call in the
+    shim is checked for argument TYPES (pointer constness, integer widths, the state and loss structs),
+    not only for its name and argument count."""
+    import shutil
+    import subprocess
+    gxx = shutil.which("g++")
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    if gxx is None or not os.path.exists(os.path.join(cuda_inc, "cuda_runtime.h")):
+        pytest.skip("needs g++ and the CUDA runtime header")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "v1_glif_model_b200", "tf_shim", "v1g_tf_ops.cc")
+    r = subprocess.run([gxx, "-std=c++17", "-fsyntax-only", "-Wall", "-Werror", "-I", os.path.join(root, "tests", "tf_stub"),
+                        "-I", os.path.join(root, "include"), "-I", cuda_inc, src], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
