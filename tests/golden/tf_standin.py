@@ -199,8 +199,8 @@ def custom_gradient(f):
                 return out
 
             @staticmethod
-            def backward(ctx, dy):
-                grads = ctx.grad_fn_(dy)
+            def backward(ctx, *dys):
+                grads = ctx.grad_fn_(*dys)
                 grads = list(grads) if isinstance(grads, (list, tuple)) else [grads]
                 return tuple(grads[i] for i in t_pos)
 
