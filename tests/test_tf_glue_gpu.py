@@ -79,6 +79,32 @@ class OpsInPython:
         return d
 
 
+    # state tensors in the reference's order: z_buf, v, r (int8), asc, psc_rise, psc
+    def _state(self, t):
+        from v1_glif_model_b200 import _lib
+        return _lib.V1GState(*[x.data_ptr() for x in t], None)
+
+    def v1g_step(self, z_buf, v, r, asc, psc_rise, psc, rec_inputs, handle):
+        ins = [x.contiguous() for x in (z_buf, v, r, asc, psc_rise, psc)]
+        outs = [torch.empty_like(x) for x in ins]
+        z = torch.empty_like(ins[1])
+        rec_inputs = rec_inputs.contiguous()
+        s_in, s_out = self._state(ins), self._state(outs)
+        self._ok(self.lib.v1g_step_fwd(C.c_void_p(handle), ins[1].shape[0], C.byref(s_in), _p(rec_inputs), C.byref(s_out),
+                                       _p(z), _stream()), handle)
+        return outs + [z]
+
+    def v1g_step_grad(self, g_z_buf, g_v, g_r, g_asc, g_psc_rise, g_psc, g_z, g_v_out, new_v, new_r, handle):
+        gs = [x.contiguous() for x in (g_z_buf, g_v, g_r, g_asc, g_psc_rise, g_psc)]
+        outs = [torch.empty_like(x) for x in gs]
+        d_rec = torch.empty_like(gs[5])
+        keep = [x.contiguous() for x in (g_z, g_v_out, new_v, new_r)]
+        s_out, s_in = self._state(gs), self._state(outs)
+        self._ok(self.lib.v1g_step_bwd(C.c_void_p(handle), gs[1].shape[0], C.byref(s_out), _p(keep[0]), _p(keep[1]),
+                                       _p(keep[2]), _p(keep[3]), C.byref(s_in), _p(d_rec), _stream()), handle)
+        return outs + [d_rec]
+
+
 @pytest.fixture()
 def glue():
     golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -165,3 +191,39 @@ def test_rollout_returns_float_spikes_and_weight_gradients(glue):
     ((zo * g_z).sum() + (vo * g_v).sum()).backward()
     for got, want in zip(ws, (orc.recurrent_weight_values, orc.input_weight_values, orc.bkg_input_weights)):
         assert rel_err(got.grad, want.grad) <= TOL_GRAD
+
+
+def test_dense_update_step_and_its_adjoint(glue):
+    """``dense_update`` = ``_dense_update_impl`` + ``spike_function`` + the tail of ``call`` as one op with the
+    adjoint of ``v1g_step_bwd``: new state and spikes against the oracle, gradients of a random cotangent
+    against autograd through the oracle's step (stop-gradients of ``models.py:994, 1010-1018``)."""
+    from oracle.cell_torch import SpikeFunction
+    cfg, dicts, orc, cell = make_cells("small", dampening_factor=0.5, pseudo_width=0.5)
+    n, d, r = cfg.n_neurons, orc.max_delay, orc._n_syn_basis
+    g = torch.Generator().manual_seed(8)
+    b = 2
+    z_buf = (torch.rand(b, n * d, generator=g) < 0.1).float()
+    leaves = [t.requires_grad_(True) for t in (torch.randn(b, n, generator=g) * 0.5 + 0.6,
+                                               torch.randn(b, n * 2, generator=g), torch.randn(b, n * r, generator=g),
+                                               torch.randn(b, n * r, generator=g), torch.randn(b, n * r, generator=g))]
+    v, asc, psc_rise, psc, rec_inputs = leaves
+    rr = torch.randint(0, 2, (b, n), generator=g)
+    nv, nr, nasc, npr, npsc = orc._dense_update_impl(b, z_buf[:, :n], v, rr, asc, psc_rise, psc, rec_inputs)
+    z = SpikeFunction.apply(nv - 1.0, 0.5, 0.5, None)
+    z = torch.where(nr > 0, torch.zeros_like(z), z)
+    cot = [torch.randn(t.shape, generator=g) for t in (nv, nasc, npr, npsc, z)]
+    want = torch.autograd.grad(sum((t * c).sum() for t, c in zip((nv, nasc, npr, npsc, z), cot)), leaves)
+
+    dv = [t.detach().cuda().requires_grad_(True) for t in leaves]
+    fn = glue.dense_update(_handle(cell))
+    out = fn(z_buf.cuda(), dv[0], rr.to(torch.int8).cuda(), dv[1], dv[2], dv[3], dv[4])
+    new_z_buf, new_v, new_r, new_asc, new_pr, new_psc, z_dev = out
+    assert torch.equal(new_v.detach().cpu(), nv.detach()) and torch.equal(new_r.cpu().long(), nr)
+    assert torch.equal(z_dev.detach().cpu(), z.detach())
+    assert torch.equal(new_z_buf.detach().cpu()[:, :n], z.detach()) and \
+        torch.equal(new_z_buf.detach().cpu()[:, n:], z_buf[:, :-n])
+    loss = sum((t * c.cuda()).sum() for t, c in zip((new_v, new_asc, new_pr, new_psc, z_dev), cot))
+    loss.backward()
+    for got, w in zip(dv, want):
+        assert rel_err(got.grad, w) <= TOL_GRAD
+
