@@ -7,7 +7,7 @@ and the largest ring), a ``max_delay`` argument below the largest delay in the d
 LGN synapses are not delayed, ``models.py:531-535, 715-718``), refractory periods of a single step
 (which block nothing, ``models.py:1018, 1113-1114``) and of many, source neurons without any
 outgoing synapse, a step at which every neuron fires, hard reset, 4 and 5 receptor channels and a
-dense basis with negative entries.
+dense basis with negative entries over 7 or 12 synapse types (projected and raw backward ring).
 """
 import dataclasses
 
@@ -36,7 +36,7 @@ def nets(draw):
         t_ref=draw(st.sampled_from(["one_step", "mixed", "long"])),
         mute=draw(st.booleans()), burst=draw(st.booleans()), hard_reset=draw(st.booleans()),
         dense_basis=draw(st.booleans()), n_lgn=draw(st.integers(1, 20)), n_bkg=draw(st.integers(1, 8)),
-        pair_rows=draw(st.booleans()))
+        pair_rows=draw(st.booleans()), many_types=draw(st.booleans()))
 
 
 def _build(p):
@@ -63,7 +63,9 @@ def _build(p):
             syn[k] = syn[k][keep]
         net["n_edges"] = int(keep.sum())
     if p["dense_basis"]:
-        s_types = 7
+        # 7 types: the backward ring holds one projected row per type; 12 types: it holds the raw channels
+        # and the gather contracts them (lanes sharing a synapse with 4 channels, plain arrays with 5)
+        s_types = 12 if p["many_types"] else 7
         net["synaptic_basis_weights"] = rng.normal(0.3, 0.6, (s_types, cfg.n_receptors)).astype(np.float32)
         for d in (net["synapses"], lgn, bkg):
             d["syn_ids"] = rng.integers(0, s_types, d["syn_ids"].shape[0]).astype(np.uint8)
