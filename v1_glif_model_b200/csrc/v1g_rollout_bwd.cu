@@ -423,6 +423,12 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
       const int k = k0 + tid;
       const bool act = k < cn;
       const int n = n0 + (act ? k : 0);
+      // the row's bounds do not depend on the tape: requested first, they arrive together with it
+      int rj0 = 0, rj1 = 0;
+      if (queue && fast_rows && act) {
+        rj0 = rpx[k * D];
+        rj1 = rpx[k * D + D];
+      }
       // all tape loads of the neuron are issued before any of them is used
       float vv[NBX];
       unsigned zz[NBX];
@@ -464,7 +470,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
           const int qpos = base + __popc(wm & ((1u << lane) - 1u));
           rowq_s[qpos] = (uint16_t)k;
           if (fast_rows) {
-            const int j0 = rpx[k * D], j1 = rpx[k * D + D];
+            const int j0 = rj0, j1 = rj1;
             rowd_s[qpos] = make_int4(j0, j1, k | (int)(zm << 16), 0);
             c_rows += (unsigned long long)D;
             c_events += (unsigned long long)(j1 - j0);
