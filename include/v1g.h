@@ -464,6 +464,16 @@ int v1g_set_option(V1GHandle* h, const char* name, long long value);
  * kernel has finished.  No counterpart in the reference. */
 int v1g_last_kernel_ms(V1GHandle* h, int which, float* ms);
 
+/* Slices of equal scatter work for the forward rollout.  Each thread block of the rollout kernels
+ * owns a contiguous slice of neurons; with equal slices the blocks whose neurons fire most set the
+ * pace of every step.  This call re-cuts the slices of the one-neuron-per-thread forward kernel so
+ * that cost_host[n] (host, [n_neurons], >= 0; e.g. expected spikes x out-degree) sums to about the
+ * same in every slice; with cost_host == NULL the cost is taken from the spike counts of the last
+ * rollout that was saved for the backward pass.  Results do not depend on the slicing (up to the
+ * summation order of the currents).  Connectivity changes and the "rollout_chunk" option reset it.
+ * No counterpart in the reference. */
+int v1g_balance_slices(V1GHandle* h, const float* cost_host, void* stream);
+
 /* Number of CUDA kernels this library has launched in the process so far (all handles).  No
  * counterpart in the reference. */
 long long v1g_launch_count(void);

@@ -364,6 +364,38 @@ def test_bptt_batch_of_five(options):
         assert rel_err(got, want) <= TOL_GRAD
 
 
+def test_balanced_slices_do_not_change_the_results():
+    """``v1g_balance_slices`` re-cuts the blocks' slices of the one-neuron-per-thread forward kernel by
+    scatter work: with costs from the last saved rollout, with heavily skewed explicit costs (slices from
+    a handful of neurons to the 512-neuron cap) and after a reset, spikes stay those of the oracle and
+    the backward pass over the saved rollout gives the same gradients."""
+    cfg, dicts, orc, cell = _cells("small", (("rollout_chunk", 32),), **KW)     # 19 blocks of 32 neurons
+    x, c = make_inputs(cfg)
+    zo, lo, go = _oracle_grads(orc, cfg, x, c, cell.voltage_scale, torch.float32)
+    xd, cd = torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda()
+    tgt = torch.from_numpy(synth.make_rate_targets(cfg)).cuda() / 1000.0
+    vlo = torch.from_numpy((-20.0 / cell.voltage_scale).astype(np.float32)).cuda()
+    with pytest.raises(ValueError):
+        cell.balance_slices()                                  # nothing saved yet
+    skew = np.ones(cfg.n_neurons, dtype=np.float32)
+    skew[:40] = 500.0
+    for step, cost in enumerate(("saved", skew, skew[::-1].copy())):
+        z, _ = cell.rollout(xd, cd, save_for_bwd=True)
+        assert torch.equal(z.cpu().float(), zo)
+        grads = cell.backward(dict(LOSS, rate_target=tgt, v_lo=vlo))
+        cell.synchronize()
+        for got, want in zip(grads[:3], go):
+            assert rel_err(got, want) <= TOL_GRAD
+        cell.balance_slices(None if isinstance(cost, str) else cost)
+    z, _ = cell.rollout(xd, cd)
+    assert torch.equal(z.cpu().float(), zo)
+    with pytest.raises(ValueError):
+        cell.balance_slices(-skew)
+    cell.set_option("rollout_chunk", 64)                       # another slicing: the balanced cut is dropped
+    z, _ = cell.rollout(xd, cd)
+    assert torch.equal(z.cpu().float(), zo)
+
+
 def test_forward_rollout_of_more_trials_than_one_launch_takes():
     """Ten trials (the reference's evaluation batch, ``osi_dsi_estimator.py:424``) run as groups of at most
     8: spikes equal the oracle's for every trial, the carried state is that of one wide rollout, counts

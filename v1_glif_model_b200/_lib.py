@@ -102,6 +102,7 @@ SIGNATURES = {
     "v1g_rollout_bwd": (C.c_int, [_P, C.POINTER(V1GLossSpec), _P, _P, _P, _P, _P, _P, _P]),
     "v1g_expadam_update": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64, C.c_float, C.c_float,
                                      C.c_float, C.c_float, C.c_int64, C.c_float, _P]),
+    "v1g_balance_slices": (C.c_int, [_P, _P, _P]),
     "v1g_train_layout": (C.c_int, [_P, _P]),
     "v1g_rollout_bwd_internal": (C.c_int, [_P, C.POINTER(V1GLossSpec), _P, _P, _P, _P, _P]),
     "v1g_expadam_update_internal": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_float, C.c_float,

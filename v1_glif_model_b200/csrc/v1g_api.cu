@@ -139,6 +139,7 @@ extern "C" int v1g_destroy(V1GHandle* h) {
   cudaFree(h->lgn_entries);
   cudaFree(h->lgn_ent4);
   cudaFree(h->tape_stats);
+  cudaFree(h->fwd_slice);
   cudaFree(h->rate_scratch);
   cudaFree(h->reg_scratch);
   cudaFree(h->sync_scratch);
@@ -305,6 +306,7 @@ extern "C" int v1g_set_connectivity(V1GHandle* h, int source, int64_t nnz,
   V1G_CUDA(h, cudaMemset(s.w, 0, std::max<size_t>((size_t)nnz, 1) * sizeof(float)));
   V1G_CUDA(h, cudaMemset(s.w_ref, 0, std::max<size_t>((size_t)nnz, 1) * sizeof(float)));
   h->tape_valid = false;
+  h->fwd_slice_host.clear();
   return V1G_OK;
 }
 
@@ -588,6 +590,7 @@ extern "C" int v1g_set_option(V1GHandle* h, const char* name, long long value) {
     if (value < 0 || (value % 32) != 0)
       return v1g_fail(h, V1G_EINVAL, "rollout_chunk must be 0 or a multiple of 32");
     h->opt_chunk = (int)value;
+    h->fwd_slice_host.clear();  // balanced slices belong to one slicing of the neurons
   } else if (!strcmp(name, "state_in_global")) {
     h->opt_force_global = value != 0;
   } else if (!strcmp(name, "force_smem_kernel")) {

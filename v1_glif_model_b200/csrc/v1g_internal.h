@@ -116,6 +116,10 @@ struct V1GHandle {
   // (all batch rows and steps) followed by [T*B] population spikes per (step, batch row)
   int32_t* tape_stats = nullptr;
   int64_t tape_stats_cap = 0;
+  // forward slices balanced by scatter work (v1g_balance_slices): first neuron of every block's slice,
+  // [grid + 1], on the device and on the host; empty = equal slices
+  int32_t* fwd_slice = nullptr;
+  std::vector<int32_t> fwd_slice_host;
   const int32_t* tape_counts = nullptr;  // background counts of the saved rollout (= tape_counts_buf)
   int32_t* tape_counts_buf = nullptr;    // handle-owned copy [B][T][n_bkg]
   int64_t tape_counts_cap = 0;

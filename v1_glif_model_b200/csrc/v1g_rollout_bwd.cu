@@ -357,7 +357,9 @@ __global__ void __launch_bounds__(NT, 1) rollout_bwd_kernel(const BwdArgs a) {
   unsigned long long ph_a = 0, ph_b = 0, ph_c = 0;
   const bool prof = a.phase_ns != nullptr && tid == 0;
   const unsigned long long ph_start = prof ? gtime_b() : 0;
-  const int gw = blockIdx.x * NW + warp, gnw = gridDim.x * NW;
+  // LGN events are dealt out block by block (event i to block i mod grid), so that every block carries
+  // its share of a step's few hundred events; first warps first: the last warp watches the barrier
+  const int gw = warp * gridDim.x + blockIdx.x, gnw = gridDim.x * NW;
 
   // Weight gradient of the LGN events of step tt from Q(tt).  One warp per event; the (up to 128)
   // synapses of a pass are loaded together so that the three dependent accesses (record, Q row,

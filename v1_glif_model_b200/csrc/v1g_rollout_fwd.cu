@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_kernel(const FwdArgs a) {
     v1g_walk_rec<R_>(a, basis_s, lane, b, a.rec_rowptr + (int64_t)n * D, te, c_rec_ev);
   };
   auto scatter_lgn = [&](int tt) {
-    v1g_scatter_lgn<R_>(a, basis_s, lane, blockIdx.x * NW + warp, gridDim.x * NW, v1g_lgn_begin(a, tt),
+    v1g_scatter_lgn<R_>(a, basis_s, lane, (NW - 1 - warp) * gridDim.x + blockIdx.x, gridDim.x * NW, v1g_lgn_begin(a, tt),
                         v1g_lgn_begin(a, tt + 1), tt % a.K, c_lgn_rows, c_lgn_ev);
   };
 
@@ -582,6 +582,12 @@ static int rollout_fwd_impl(V1GHandle* h, int32_t batch, int32_t n_steps, const 
     const int a0 = g * plan.chunk, a1 = std::min(N, a0 + plan.chunk);
     bkg_cap = std::max(bkg_cap, bk.in_ptr_host[a1] - bk.in_ptr_host[a0]);
   }
+  // balanced slices (register-resident kernel only): valid for this grid, at most V1G_NT_REG neurons each
+  const bool sliced = (int)h->fwd_slice_host.size() == plan.grid + 1 && h->fwd_slice != nullptr;
+  int bkg_cap_sliced = 0;
+  if (sliced)
+    for (int g = 0; g < plan.grid; ++g)
+      bkg_cap_sliced = std::max(bkg_cap_sliced, bk.in_ptr_host[h->fwd_slice_host[g + 1]] - bk.in_ptr_host[h->fwd_slice_host[g]]);
   auto al = [](size_t b) { return (b + 15) & ~(size_t)15; };
   size_t smem = 7 * al(sizeof(float) * plan.chunkP) + al(sizeof(int) * (plan.chunkP + 1)) +
                 al(sizeof(float) * c.n_syn_types * R) + al(sizeof(uint32_t) * B * plan.chunkP) +
@@ -677,7 +683,12 @@ static int rollout_fwd_impl(V1GHandle* h, int32_t batch, int32_t n_steps, const 
   const bool reg_ok = !h->opt_force_smem_kernel && !h->opt_force_global && plan.chunk <= V1G_NT_REG &&
                       (R == 4 || R == 5) && B <= 6 &&
                       v1g_fwd_reg_smem(h, B, plan.chunkP, bkg_cap) <= limit;
-  if (reg_ok) {
+  a.slice = nullptr;
+  if (reg_ok && sliced && v1g_fwd_reg_smem(h, B, plan.chunkP, bkg_cap_sliced) <= limit) {
+    a.slice = h->fwd_slice;
+    a.bkg_cap = bkg_cap_sliced;
+    rc = v1g_launch_fwd_reg(h, a, R, plan.grid, v1g_fwd_reg_smem(h, B, plan.chunkP, bkg_cap_sliced), st);
+  } else if (reg_ok) {
     rc = v1g_launch_fwd_reg(h, a, R, plan.grid, v1g_fwd_reg_smem(h, B, plan.chunkP, bkg_cap), st);
   } else
   switch (R) {
@@ -706,6 +717,86 @@ static int rollout_fwd_impl(V1GHandle* h, int32_t batch, int32_t n_steps, const 
     h->tape_counts = h->tape_counts_buf;
   }
   if (state && state->noise_step) return v1g_advance_noise_step(h, state->noise_step, B, T, st);
+  return V1G_OK;
+}
+
+// Slices of equal scatter work for the register-resident forward kernel.  The dense part costs the
+// same whatever a block's slice holds (one neuron per thread, at most V1G_NT_REG), while the scatter
+// costs one walk of a neuron's out-synapses per spike, and networks are ordered by cell type, so with
+// equal slices the blocks that own the most active types set the pace of every step and the others
+// wait.  cost[n] = spikes of neuron n x its out-degree (+ 2 % of the mean so that silent stretches are
+// shared out too); boundaries by bisection on the largest slice cost, greedy from the left.
+extern "C" int v1g_balance_slices(V1GHandle* h, const float* cost_host, void* stream) {
+  if (!h) return V1G_EINVAL;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int N = h->cfg.n_neurons, D = h->cfg.max_delay;
+  V1GRolloutPlan plan;
+  v1g_plan_rollout(h, 1, 0, 0, 0, &plan);
+  h->fwd_slice_host.clear();
+  if (plan.chunk > V1G_NT_REG || plan.grid < 2) return V1G_OK;  // the general kernel keeps equal slices
+  std::vector<double> cost((size_t)N);
+  if (cost_host) {
+    for (int n = 0; n < N; ++n) {
+      if (!(cost_host[n] >= 0.f)) return v1g_fail(h, V1G_EINVAL, "v1g_balance_slices: cost[%d] is negative or not a number", n);
+      cost[(size_t)n] = cost_host[n];
+    }
+  } else {
+    const V1GSource& rs = h->src[V1G_SRC_REC];
+    if (!h->tape_valid || !h->tape_stats || rs.rowptr_host.size() < (size_t)N * D + 1)
+      return v1g_fail(h, V1G_EINVAL, "v1g_balance_slices without costs needs a rollout saved for the backward pass");
+    std::vector<int32_t> spikes((size_t)N);
+    V1G_CUDA(h, cudaMemcpyAsync(spikes.data(), h->tape_stats, sizeof(int32_t) * (size_t)N, cudaMemcpyDeviceToHost, st));
+    V1G_CUDA(h, cudaStreamSynchronize(st));
+    for (int n = 0; n < N; ++n)
+      cost[(size_t)n] = (double)spikes[(size_t)n] * (double)(rs.rowptr_host[(size_t)(n + 1) * D] - rs.rowptr_host[(size_t)n * D]);
+  }
+  double total = 0.0, largest = 0.0;
+  for (double c : cost) total += c;
+  const double floor_cost = total > 0.0 ? 0.02 * total / N : 1.0;
+  total = 0.0;
+  for (double& c : cost) {
+    c += floor_cost;
+    total += c;
+    largest = std::max(largest, c);
+  }
+  const int G = plan.grid, cap = V1G_NT_REG;
+  auto cut = [&](double limit, std::vector<int32_t>* out) {  // greedy slices of cost <= limit and size <= cap
+    int slices = 0, size = 0;
+    double acc = 0.0;
+    if (out) out->assign(1, 0);
+    for (int n = 0; n < N; ++n) {
+      if (size > 0 && (size == cap || acc + cost[(size_t)n] > limit)) {
+        ++slices;
+        if (out) out->push_back(n);
+        size = 0;
+        acc = 0.0;
+      }
+      ++size;
+      acc += cost[(size_t)n];
+    }
+    if (out) out->push_back(N);
+    return slices + 1;
+  };
+  if (cut(total, nullptr) > G) return V1G_OK;  // more than cap neurons per block on average: cannot happen with chunk <= cap
+  double lo = largest, hi = total;
+  for (int it = 0; it < 50; ++it) {
+    const double mid = 0.5 * (lo + hi);
+    if (cut(mid, nullptr) <= G) hi = mid; else lo = mid;
+  }
+  std::vector<int32_t> bounds;
+  cut(hi, &bounds);
+  while ((int)bounds.size() < G + 1) {  // fewer slices than blocks: halve the widest until every block has one
+    size_t widest = 0;
+    for (size_t g = 0; g + 1 < bounds.size(); ++g)
+      if (bounds[g + 1] - bounds[g] > bounds[widest + 1] - bounds[widest]) widest = g;
+    if (bounds[widest + 1] - bounds[widest] < 2) return V1G_OK;  // fewer neurons than blocks
+    bounds.insert(bounds.begin() + (long)widest + 1, (bounds[widest] + bounds[widest + 1]) / 2);
+  }
+  if (!h->fwd_slice) V1G_CUDA(h, cudaMalloc((void**)&h->fwd_slice, sizeof(int32_t) * 1024));
+  if (G + 1 > 1024) return V1G_OK;
+  V1G_CUDA(h, cudaMemcpyAsync(h->fwd_slice, bounds.data(), sizeof(int32_t) * (size_t)(G + 1), cudaMemcpyHostToDevice, st));
+  V1G_CUDA(h, cudaStreamSynchronize(st));
+  h->fwd_slice_host = bounds;
   return V1G_OK;
 }
 

@@ -33,6 +33,8 @@ struct FwdArgs {
   // spike statistics for the loss terms (with the tape, else NULL): spikes per neuron, population
   // spikes per (step, batch row)
   int32_t *stat_neuron, *stat_pop;
+  // first neuron of every block's slice [grid + 1] (register-resident kernel), or NULL for equal slices
+  const int32_t* slice;
   // state (reference layouts, all NULL = zero state / no write-back)
   V1GState st;
   float* state_ws;

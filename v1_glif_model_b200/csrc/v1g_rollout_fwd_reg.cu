@@ -26,8 +26,9 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int D = a.D, K = a.K, N = a.N, Np = a.Np;
-  const int n0 = blockIdx.x * a.chunk;
-  const int cn = min(a.chunk, N - n0);
+  // equal slices, or slices of equal scatter work (at most one neuron per thread either way)
+  const int n0 = a.slice ? a.slice[blockIdx.x] : blockIdx.x * a.chunk;
+  const int cn = a.slice ? a.slice[blockIdx.x + 1] - n0 : min(a.chunk, N - n0);
   const bool active = tid < cn;
   const int n = n0 + (active ? tid : 0);
   const int nb = B_ * a.n_bkg;
@@ -99,7 +100,10 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
 
   unsigned long long c_spikes = 0, c_rec_ev = 0, c_lgn_rows = 0, c_lgn_ev = 0, c_bkg_ev = 0,
                      c_bkg_rows = 0;
-  const int gw = blockIdx.x * NW + warp, gnw = gridDim.x * NW;
+  // LGN events are dealt out over the grid's warps block by block (event i to block i mod grid), the
+  // last warps of a block first: numbered block-major, the few hundred events of a step all fell on
+  // the first third of the blocks, which then set the pace of every step
+  const int gw = (NW - 1 - warp) * gridDim.x + blockIdx.x, gnw = gridDim.x * NW;
 
   // ---- prologue: pending deliveries of the initial spike buffer, LGN events of step 0 ----
   if (have_state) {

@@ -223,6 +223,17 @@ class V1Column:
         self._check(self._lib.v1g_last_kernel_ms(self._libh, which, C.byref(ms)))
         return ms.value
 
+    def balance_slices(self, cost=None):
+        """Re-cut the thread blocks' slices of the forward rollout so that every slice carries about the
+        same scatter work (``v1g_balance_slices``): ``cost`` = per-neuron weights (NumPy ``[n_neurons]``),
+        or ``None`` to use the spike counts of the last rollout saved for the backward pass."""
+        ptr = None
+        if cost is not None:
+            cost = np.ascontiguousarray(cost, dtype=np.float32)
+            assert cost.shape == (self._n_neurons,)
+            ptr = cost.ctypes.data
+        self._check(self._lib.v1g_balance_slices(self._libh, ptr, _stream()))
+
     def phase_times(self):
         """Per-block (dense, scatter, barrier, total) nanoseconds of the last rollout kernel
         (needs ``set_option('phase_timers', 1)``)."""
