@@ -408,6 +408,12 @@ def run_ours(args):
     checks = gradient_checks(bench)
     if world > 1:
         checks["reduce_check"] = reduce_check(bench)
+        # the two rollout kernels' durations on every rank (each rank has its own inputs; a step ends when
+        # the slowest rank reaches the all-reduce)
+        mine = torch.tensor([fwd_ms, bwd_ms], device=dev)
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        checks["kernel_ms_by_rank"] = [[round(float(v), 3) for v in t.tolist()] for t in every]
 
     stress = None
     if world > 1 and not args.no_stress and args.config == "C4":
