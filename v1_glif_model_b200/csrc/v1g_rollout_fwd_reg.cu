@@ -202,6 +202,15 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
       for (int i = tid; i < nb; i += NT) c_bkg_rows += cnt_s[i] > 0 ? 1 : 0;
     int* nspk_p = &s_misc[2 + (t & 1)];
 
+#ifndef V1G_FWD_NO_ROW_PREFETCH
+    // the same for the LGN event this warp scatters after the dense phase (fetched an iteration ago)
+    if (lane == 0 && lgn8 && t + 1 < a.T) {
+      const uint4 ent = lgn_ent_s[((t + 1) & 1) * NW + warp];
+      const char* p0 = (const char*)(a.lgn_syn8 + ent.y);
+      const char* p1 = (const char*)(a.lgn_syn8 + ent.z);
+      for (const char* p = p0; p < p1; p += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+    }
+#endif
     // ---------------- dense phase ----------------
     if (active) {
       // ring values of batch row b+1 are requested while row b is processed
@@ -258,7 +267,19 @@ __global__ void __launch_bounds__(NT, 1) rollout_fwd_reg_kernel(const FwdArgs a)
           // the voltage with its two lowest mantissa bits replaced by (spiked, refractory)
           __stcs(a.tape_v + ti, __uint_as_float((__float_as_uint(nv) & ~3u) | (z ? 1u : 0u) | (nr > 0 ? 2u : 0u)));
         }
-        if (z) spk_list[atomicAdd(nspk_p, 1)] = ((uint32_t)b << 24) | (uint32_t)tid;
+        if (z) {
+          spk_list[atomicAdd(nspk_p, 1)] = ((uint32_t)b << 24) | (uint32_t)tid;
+#ifndef V1G_FWD_NO_ROW_PREFETCH
+          // the scatter phase will walk this neuron's out-synapses: ask L2 for their records now, so that
+          // they are on their way from HBM while the rest of the dense phase runs
+          if (a.rec_syn8) {
+            const int2 rb = rowb_s[tid];
+            const char* p0 = (const char*)(a.rec_syn8 + rb.x);
+            const char* p1 = (const char*)(a.rec_syn8 + rb.y);
+            for (const char* p = p0; p < p1; p += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+          }
+#endif
+        }
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
