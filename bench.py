@@ -780,8 +780,8 @@ def load_traffic(t_len=1):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 10; 5 for the CPU arm)")
+    ap.add_argument("--warmup", type=int, default=None, help="untimed steps before them (default 5; 3 for the CPU arm)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="C4", choices=["C4", "C5", "C2"],
                     help="C4 = the metric's configuration (default); C5 = 230,924-neuron stress; C2 = 5,000 neurons")
@@ -802,6 +802,10 @@ def main():
     ap.add_argument("--lib-option", action="append", default=[], metavar="NAME=VALUE",
                     help="library tuning option for the training cell, e.g. pair_rows=1 (repeatable)")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 5 if args.impl == "reference" else 10
+    if args.warmup is None:
+        args.warmup = 3 if args.impl == "reference" else 5
     if args.impl == "reference":
         run_reference(args)
     else:
